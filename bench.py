@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  The headline workload is BASELINE config 2:
+``hgemm`` fp16, M=N=K=8192, NN, alpha=1, beta=0, A,B ~ N(0,1)*0.05 (seed 1), fp32
+accumulate, fp16 output.  A "step" is one full GEMM.  With N > 1 GPUs the same GEMM is
+column-sharded (N-split) across the ranks, one process per GPU, with no collective on the
+data path (strong scaling: total work fixed).
+
+``value``   : device-resident TFLOP/s (inputs in HBM, CUDA events, max over ranks).
+``e2e``     : the same metric through the public operator API with HOST buffers: per step
+              pinned-host -> device copies of A and B, the GEMM, and the device -> host copy of C.
+``roofline``: tensor-core roofline of the GEMM kernel (2*m*n*k FLOPs per launch / event time).
+``cpu_baseline``: torch.matmul fp32 on the host cores over a bounded row sample (rank 0, N=1).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (operator, kind, transa, transb, m, n, k, alpha, beta, scaleA, scaleB, seed)
+    "hgemm_8192_nn": ("hgemm", "fp16", 0, 0, 8192, 8192, 8192, 1.0, 0.0, 0.05, 0.05, 1),
+    "bfgemm_mlp_nt": ("bfgemm", "bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 1.0, 0.02, 2),
+    "tf32gemm_skinny_tn": ("tf32gemm", "tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
+    "tf32gemm_8192_tn": ("tf32gemm", "tf32", 1, 0, 8192, 8192, 8192, 1.5, 0.5, 0.577, 0.577, 4),
+    "sgemm_512_nn": ("sgemm", "fp32", 0, 0, 512, 512, 512, 1.0, 0.0, 0.577, 0.577, 0),
+}
+HEADLINE = "hgemm_8192_nn"
+FALLBACK_TENSOR_PEAK = 1590.0  # TFLOP/s, earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_TENSOR_PEAK, "fallback"
+
+
+def ncu_traffic(workload):
+    """DRAM bytes per launch from the committed ncu summary, if one exists for this workload."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return json.load(f).get(workload)
+    except (OSError, ValueError):
+        return None
+
+
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch_device_index, period=0.002):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period, self._stop, self._thread, self.h = period, threading.Event(), None, None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = getattr(torch.cuda.get_device_properties(torch_device_index), "uuid", None)
+            if uuid is not None:
+                try:
+                    self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+                except Exception:
+                    self.h = None
+            if self.h is None:
+                vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+                idx = int(vis.split(",")[torch_device_index]) if vis and vis.split(",")[0].isdigit() else torch_device_index
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.h = None
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.h is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the path on the host cores (torch.matmul fp32 over a bounded row sample)."""
+    if rank != 0:
+        return
+    from oracle import cpu_baseline
+
+    op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
+    per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    vals, rows, threads = [], 0, 1
+    for i in range(args.warmup + args.steps):
+        tf, rows, secs, threads = cpu_baseline.time_dense_rows(m, n, k, ta, tb, target_seconds=per_step, seed=seed, scale=sa)
+        if i >= args.warmup:
+            vals.append((tf, secs))
+    tf = sum(v[0] for v in vals) / len(vals)
+    sample = "torch.matmul fp32, %d of %d output rows of %s per step (inputs upcast)" % (rows, m, args.workload)
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(v[1] for v in vals) / len(vals),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    import flagblas_b200 as fb
+    from flagblas_b200 import dist as fbdist
+
+    assert torch.cuda.is_available(), "bench.py measures the CUDA path; no GPU visible"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as tdist
+
+        tdist.init_process_group("nccl", device_id=dev)
+
+    op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
+    dt = {"fp16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32, "fp32": torch.float32}[kind]
+    g = torch.Generator(device=dev).manual_seed(seed)  # same seed on every rank: A and B are replicated
+    A = (torch.randn((k, m) if ta else (m, k), generator=g, device=dev) * sa).to(dt)
+    B = (torch.randn((n, k) if tb else (k, n), generator=g, device=dev) * sb).to(dt)
+    C = (torch.randn(m, n, generator=g, device=dev) * 0.02).to(dt) if beta != 0 else torch.full((m, n), float("nan"), device=dev, dtype=dt)
+    lda, ldb, ldc = A.shape[1], B.shape[1], n
+    n0, n1 = fbdist.column_ranges(n, world)[rank]
+
+    def step():
+        fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+        if use_dist and args.gather:
+            fbdist.all_gather_columns(C, m, n, ldc, rank, world)
+
+    def barrier():
+        if use_dist:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert fb.device_status() == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if use_dist:
+        t = torch.tensor([ms_total], device=dev)
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    flops = 2.0 * m * n * k
+    value = flops / (ms_step * 1e-3) / 1e12
+    status = fb.device_status()
+
+    # ---- end to end: host buffers in, host buffer out, through the operator API
+    esz = A.element_size()
+    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
+    hC = torch.empty((m, max(n1 - n0, 1)), dtype=dt).pin_memory()
+    B2 = B.view(-1)[: (n if tb else k) * ldb].view(-1, ldb)
+    hB2 = hB.view(-1, ldb)
+    C2 = C.view(m, ldc)
+
+    def e2e_step():
+        A.copy_(hA, non_blocking=True)
+        if tb:
+            B2[n0:n1].copy_(hB2[n0:n1], non_blocking=True)
+        else:
+            B2[:, n0:n1].copy_(hB2[:, n0:n1], non_blocking=True)
+        fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+        hC[:, : n1 - n0].copy_(C2[:, n0:n1], non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+    if use_dist:
+        t = torch.tensor([e2e_ms], device=dev)
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = (A.numel() + (n1 - n0) * k) * esz
+    d2h = m * (n1 - n0) * esz
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        traffic = ncu_traffic(args.workload) if world == 1 else None
+        line = {
+            "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": {"fp16": "f16", "bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[kind],
+            "data": "synthetic",
+            "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb,
+                       "alpha": alpha, "beta": beta, "accumulate": "f32",
+                       "parallelism": "single GPU" if world == 1 else "N-split of C columns over %d GPUs, no collective%s" % (world, " + all-gather" if args.gather else ""),
+                       "l2": "inputs (%.0f MiB) larger than L2; no flush between steps" % ((A.numel() + B.numel() + C.numel()) * esz / 2**20)},
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                         "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
+                         "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps,
+            "clocks": clk.summary(),
+            "device_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import cpu_baseline
+
+            tf, rows, secs, threads = cpu_baseline.time_dense_rows(m, n, k, ta, tb, target_seconds=12.0, seed=seed, scale=sa)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": "torch.matmul fp32 on %d of %d output rows of %s (inputs upcast), %.1f s" % (rows, m, args.workload, secs)}
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        tdist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

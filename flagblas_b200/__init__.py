@@ -1,0 +1,24 @@
+"""flagblas_b200 -- B200 (sm_100a) implementation of FlagBLAS's GEMM family.
+
+Exports the same operator names as ``flag_blas`` for this path (``sgemm``, ``hgemm``,
+``bfgemm``, ``group_bfgemm``, ``group_hgemm``, ``group_tf32gemm``, ``group_mm``) plus the
+dense ``tf32gemm`` and the ``group_gemm`` convenience wrapper, the ``CUBLAS_OP_*``
+constants, ``device`` / ``vendor_name``, ``testing`` and ``runtime.device``.
+Importing it loads the native library; there is no CPU or eager fallback.
+"""
+from . import runtime, testing  # noqa: F401
+from . import _lib
+from .ops import *  # noqa: F401,F403
+from .ops import __all__ as _ops_all
+from ._lib import FlagBlasError, device_status  # noqa: F401
+
+# ``flag_blas.c_operators`` is the name the reference reserves for a compiled
+# extension (src/flag_blas/config.py:35-41); here it is the loaded C-ABI library.
+c_operators = _lib.lib
+
+device = runtime.device.name
+vendor_name = runtime.device.vendor_name
+__version__ = "0.1.0"
+
+__all__ = list(_ops_all) + ["runtime", "testing", "device", "vendor_name", "c_operators", "FlagBlasError",
+                            "device_status"]

@@ -1,0 +1,84 @@
+"""ctypes binding of ``libflagblas_b200.so`` -- the C ABI declared in ``include/flagblas_b200.h``.
+
+There is no fallback: if the shared library is missing (and cannot be built
+because ``nvcc`` is absent) importing this module raises, and every operator
+raises :class:`FlagBlasError` when the library reports a non-zero status.
+"""
+import ctypes
+import os
+
+from . import build as _build
+
+FB_F32, FB_TF32, FB_F16, FB_BF16 = 0, 1, 2, 3
+FB_OK = 0
+
+
+class FlagBlasError(RuntimeError):
+    """A non-zero status from the native library (host-side code or device status word)."""
+
+    def __init__(self, status, where=""):
+        self.status = status
+        text = lib.fb_status_string(status).decode() if lib is not None else "?"
+        extra = ""
+        if status == -3 and lib is not None:
+            extra = " (cudaError %d)" % lib.fb_last_cuda_error()
+        super().__init__("flagblas_b200 %s: status %d: %s%s" % (where, status, text, extra))
+
+
+def _load():
+    path = _build.LIB_PATH
+    if not os.path.exists(path):
+        # Source checkout without a built library: build it once (needs nvcc, not a GPU).
+        _build.build()
+    handle = ctypes.CDLL(path)
+    c = ctypes
+    i64, f32, vp, sz, i32 = c.c_int64, c.c_float, c.c_void_p, c.c_size_t, c.c_int
+    handle.fb_gemm.restype = i32
+    handle.fb_gemm.argtypes = [i32, i32, i32, i64, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
+    handle.fb_gemm_workspace_bytes.restype = sz
+    handle.fb_gemm_workspace_bytes.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64]
+    handle.fb_group_gemm.restype = i32
+    handle.fb_group_gemm.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp, sz, vp]
+    handle.fb_group_mm.restype = i32
+    handle.fb_group_mm.argtypes = [i32, i32, vp, i64, vp, i64, i64, vp, i64, vp, i32, i64, i64, vp, sz, vp]
+    handle.fb_group_workspace_bytes.restype = sz
+    handle.fb_group_workspace_bytes.argtypes = [i32]
+    handle.fb_status_string.restype = c.c_char_p
+    handle.fb_status_string.argtypes = [i32]
+    handle.fb_device_status.restype = i32
+    handle.fb_device_status.argtypes = [i32]
+    handle.fb_last_cuda_error.restype = i32
+    handle.fb_last_cuda_error.argtypes = []
+    handle.fb_sm_count.restype = i32
+    handle.fb_sm_count.argtypes = []
+    handle.fb_selftest_bounded_wait.restype = i32
+    handle.fb_selftest_bounded_wait.argtypes = [i64, vp]
+    return handle
+
+
+lib = None
+lib = _load()
+
+# Every symbol include/flagblas_b200.h declares; tests check the library exports them all.
+EXPORTED_SYMBOLS = (
+    "fb_gemm",
+    "fb_gemm_workspace_bytes",
+    "fb_group_gemm",
+    "fb_group_mm",
+    "fb_group_workspace_bytes",
+    "fb_status_string",
+    "fb_device_status",
+    "fb_last_cuda_error",
+    "fb_sm_count",
+    "fb_selftest_bounded_wait",
+)
+
+
+def check(status, where=""):
+    if status != FB_OK:
+        raise FlagBlasError(status, where)
+
+
+def device_status(reset=True):
+    """Synchronise and return the device status word (0 = healthy)."""
+    return lib.fb_device_status(1 if reset else 0)

@@ -1,0 +1,60 @@
+"""Build recipe for the native library: one nvcc invocation, sm_100a only.
+
+The shared object is written next to this file (``libflagblas_b200.so``) so that
+it is found in-tree by :mod:`flagblas_b200._lib`.  ``python -m flagblas_b200.build``
+rebuilds it.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libflagblas_b200.so")
+_SRC = os.path.join(_HERE, "csrc", "flagblas_b200.cu")
+_DEPS = [
+    _SRC,
+    os.path.join(_HERE, "csrc", "fb_ptx.cuh"),
+    os.path.join(_HERE, "csrc", "fb_gemm_tc.cuh"),
+    os.path.join(_HERE, "csrc", "fb_group_setup.cuh"),
+    os.path.join(_HERE, "csrc", "fb_sgemm_simt.cuh"),
+    os.path.join(_HERE, "csrc", "fb_no_alloc.cuh"),
+    os.path.join(os.path.dirname(_HERE), "include", "flagblas_b200.h"),
+]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def _nvcc():
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; the native library cannot be built")
+    return exe
+
+
+def up_to_date():
+    if not os.path.exists(LIB_PATH):
+        return False
+    t = os.path.getmtime(LIB_PATH)
+    return all(not os.path.exists(d) or os.path.getmtime(d) <= t for d in _DEPS)
+
+
+def build(force=False, verbose=False):
+    """Compile ``csrc/flagblas_b200.cu`` into ``libflagblas_b200.so`` (no GPU needed)."""
+    if not force and up_to_date():
+        return LIB_PATH
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH, _SRC]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if verbose:
+        sys.stderr.write(res.stderr)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose="-v" in sys.argv))

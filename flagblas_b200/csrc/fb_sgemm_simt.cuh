@@ -1,0 +1,174 @@
+// IEEE fp32 GEMM on the CUDA cores (FFMA), for the `sgemm` entry point whose
+// contract is true single precision (no TF32 rounding of the inputs).
+//
+//   C[m,n] = alpha * op(A) * op(B) + beta * C      (row-major, any ld / alignment)
+//
+// Classic register-tiled design: a BM x BN tile per 256-thread CTA, BK-deep
+// k-slices double buffered through shared memory (k-major, so each thread
+// reads its A and B fragments with 128-bit loads), (BM/16) x (BN/16) outputs
+// per thread.  Operands are read in whichever orientation they are stored:
+// an operand whose contiguous dimension is M/N goes straight to shared memory
+// with 128-bit stores, one whose contiguous dimension is K is transposed on
+// the way in.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fb {
+
+struct SimtParams {
+  int m, n, k;
+  float alpha, beta;
+  const float* A;
+  long long lda;
+  const float* B;
+  long long ldb;
+  float* C;
+  long long ldc;
+  int a_mn_contig;  // 1: A stored [k, lda] (transa = T); 0: stored [m, lda]
+  int b_mn_contig;  // 1: B stored [k, ldb] (transb = N); 0: stored [n, ldb]
+  int a_vec, b_vec, c_vec;  // 16-byte aligned base and leading dimension
+  int tiles_n;
+};
+
+// Fetch this thread's 4 elements of a (TILE_MN x BK) operand slice.
+//  mn-contiguous storage [k][mn]: thread -> (k = tid / (TILE_MN/4), mn = 4*(tid % (TILE_MN/4)))
+//  k-contiguous  storage [mn][k]: thread -> (mn = tid / (BK/4),     k  = 4*(tid % (BK/4)))
+template <int TILE_MN, int BK>
+__device__ __forceinline__ void simt_fetch(const float* __restrict__ base, long long ld, int mn_contig, int vec,
+                                           int mn0, int k0, int mn_lim, int k_lim, int tid, float (&r)[4]) {
+  if (mn_contig) {
+    const int kk = k0 + tid / (TILE_MN / 4);
+    const int mn = mn0 + 4 * (tid % (TILE_MN / 4));
+    const float* src = base + static_cast<long long>(kk) * ld + mn;
+    if (kk < k_lim && mn + 3 < mn_lim && vec) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = (kk < k_lim && mn + j < mn_lim) ? __ldg(src + j) : 0.f;
+    }
+  } else {
+    const int mn = mn0 + tid / (BK / 4);
+    const int kk = k0 + 4 * (tid % (BK / 4));
+    const float* src = base + static_cast<long long>(mn) * ld + kk;
+    if (mn < mn_lim && kk + 3 < k_lim && vec) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = (mn < mn_lim && kk + j < k_lim) ? __ldg(src + j) : 0.f;
+    }
+  }
+}
+
+template <int TILE_MN, int BK, int LDS>
+__device__ __forceinline__ void simt_stash(float* __restrict__ s, int mn_contig, int tid, const float (&r)[4]) {
+  if (mn_contig) {
+    const int kk = tid / (TILE_MN / 4);
+    const int mn = 4 * (tid % (TILE_MN / 4));
+    *reinterpret_cast<float4*>(s + kk * LDS + mn) = make_float4(r[0], r[1], r[2], r[3]);
+  } else {
+    const int mn = tid / (BK / 4);
+    const int kk = 4 * (tid % (BK / 4));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[(kk + j) * LDS + mn] = r[j];
+  }
+}
+
+template <int BM, int BN, int BK>
+__global__ void __launch_bounds__(256) sgemm_simt_kernel(const SimtParams p) {
+  static_assert(BM * BK == 1024 && BN * BK == 1024, "each thread moves exactly 4 elements per operand");
+  constexpr int TM = BM / 16, TN = BN / 16;  // outputs per thread
+  constexpr int RG = TM / 4, CG = TN / 4;    // 4-wide fragment groups
+  constexpr int LDA = BM + 4, LDB = BN + 4;  // padded so the transposing stores spread over banks
+  __shared__ __align__(16) float As[2][BK * LDA];
+  __shared__ __align__(16) float Bs[2][BK * LDB];
+
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int tile_m = blockIdx.x / p.tiles_n, tile_n = blockIdx.x % p.tiles_n;
+  const int m0 = tile_m * BM, n0 = tile_n * BN;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+  float ra[4], rb[4];
+  const int k_iters = (p.k + BK - 1) / BK;
+  simt_fetch<BM, BK>(p.A, p.lda, p.a_mn_contig, p.a_vec, m0, 0, p.m, p.k, tid, ra);
+  simt_fetch<BN, BK>(p.B, p.ldb, p.b_mn_contig, p.b_vec, n0, 0, p.n, p.k, tid, rb);
+  simt_stash<BM, BK, LDA>(As[0], p.a_mn_contig, tid, ra);
+  simt_stash<BN, BK, LDB>(Bs[0], p.b_mn_contig, tid, rb);
+  __syncthreads();
+
+  for (int it = 0; it < k_iters; ++it) {
+    const int cur = it & 1;
+    if (it + 1 < k_iters) {
+      simt_fetch<BM, BK>(p.A, p.lda, p.a_mn_contig, p.a_vec, m0, (it + 1) * BK, p.m, p.k, tid, ra);
+      simt_fetch<BN, BK>(p.B, p.ldb, p.b_mn_contig, p.b_vec, n0, (it + 1) * BK, p.n, p.k, tid, rb);
+    }
+    const float* as = As[cur];
+    const float* bs = Bs[cur];
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float af[TM], bf[TN];
+#pragma unroll
+      for (int g = 0; g < RG; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(as + kk * LDA + g * (BM / RG) + ty * 4);
+        af[g * 4 + 0] = v.x; af[g * 4 + 1] = v.y; af[g * 4 + 2] = v.z; af[g * 4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int g = 0; g < CG; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(bs + kk * LDB + g * (BN / CG) + tx * 4);
+        bf[g * 4 + 0] = v.x; bf[g * 4 + 1] = v.y; bf[g * 4 + 2] = v.z; bf[g * 4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(af[i], bf[j], acc[i][j]);
+    }
+    if (it + 1 < k_iters) {
+      simt_stash<BM, BK, LDA>(As[cur ^ 1], p.a_mn_contig, tid, ra);
+      simt_stash<BN, BK, LDB>(Bs[cur ^ 1], p.b_mn_contig, tid, rb);
+    }
+    __syncthreads();
+  }
+
+  // epilogue: alpha * acc + beta * C, C never read when beta == 0
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int row = m0 + (i / 4) * (BM / RG) + ty * 4 + (i % 4);
+    if (row >= p.m) continue;
+#pragma unroll
+    for (int g = 0; g < CG; ++g) {
+      const int col = n0 + g * (BN / CG) + tx * 4;
+      if (col >= p.n) continue;
+      float* dst = p.C + static_cast<long long>(row) * p.ldc + col;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = p.alpha * acc[i][g * 4 + j];
+      if (p.c_vec && col + 3 < p.n) {
+        if (p.beta != 0.f) {
+          const float4 c = *reinterpret_cast<const float4*>(dst);
+          v[0] += p.beta * c.x; v[1] += p.beta * c.y; v[2] += p.beta * c.z; v[3] += p.beta * c.w;
+        }
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (col + j < p.n) {
+            float r = v[j];
+            if (p.beta != 0.f) r += p.beta * dst[j];
+            dst[j] = r;
+          }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace fb

@@ -1,0 +1,540 @@
+// C ABI of the B200 GEMM back end (see include/flagblas_b200.h) and the host
+// logic behind it: argument checks, operand geometry, tensor-map encoding,
+// tile-shape choice and kernel launches.  Single translation unit.
+#include "../../include/flagblas_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+namespace fb {
+__device__ int g_fb_status = 0;
+}
+
+#include "fb_gemm_tc.cuh"
+#include "fb_group_setup.cuh"
+#include "fb_sgemm_simt.cuh"
+
+namespace fb {
+
+static thread_local int t_last_cuda_error = 0;
+
+#define FB_CUDA_OK(expr)                                   \
+  do {                                                     \
+    cudaError_t e__ = (expr);                              \
+    if (e__ != cudaSuccess) {                              \
+      t_last_cuda_error = static_cast<int>(e__);           \
+      return FB_ERR_LAUNCH;                                \
+    }                                                      \
+  } while (0)
+
+// ---------------------------------------------------------------- device info
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  bool ready = false;
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_dev_mu;
+
+static const DeviceInfo* device_info() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+    if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
+    d.ready = true;
+  }
+  return &d;
+}
+
+// ------------------------------------------------------- tensor-map encoding
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+static int elem_size(int dtype) { return (dtype == FB_F16 || dtype == FB_BF16) ? 2 : 4; }
+
+static CUtensorMapDataType map_dtype(int dtype) {
+  switch (dtype) {
+    case FB_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case FB_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  }
+}
+
+// 2-D row-major view: `inner` contiguous elements per row, `outer` rows `pitch_bytes` apart.
+// `atom32`: 128-byte swizzle with 32-byte atoms (MN-major operands of 32-bit types).
+static int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+                     uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FB_ERR_DRIVER;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, map_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    t_last_cuda_error = static_cast<int>(r);
+    return FB_ERR_DRIVER;
+  }
+  return FB_OK;
+}
+
+// Geometry of one operand's pipeline stage.  `tile_mn` rows/cols of the tile,
+// `mn_contig`: the operand's contiguous dimension is M (resp. N), not K.
+static OperandGeom make_geom(int esz, int tile_mn, bool mn_contig) {
+  OperandGeom g{};
+  const uint32_t span = kSwizzleBytes / esz;  // elements per 128-byte row
+  const uint32_t block_k = span;
+  if (mn_contig) {
+    g.mn_major = 1;
+    g.boxes = tile_mn / span;
+    g.box_bytes = block_k * kSwizzleBytes;
+    g.box_mn_step = span;
+    g.lbo = block_k * kSwizzleBytes;  // next 128-byte chunk of MN = next box
+    g.sbo = (esz == 4 ? 4 : 8) * kSwizzleBytes;  // next group of k-rows (4 with 32-byte atoms, else 8)
+    g.k_adv_bytes = (32 / esz) * kSwizzleBytes;  // one MMA consumes 32 bytes' worth of K = that many rows
+    g.layout = esz == 4 ? kLayoutSw128Base32 : kLayoutSw128;
+  } else {
+    g.mn_major = 0;
+    g.boxes = 1;
+    g.box_bytes = tile_mn * kSwizzleBytes;
+    g.box_mn_step = 0;
+    g.lbo = 16;
+    g.sbo = 8 * kSwizzleBytes;  // next group of 8 rows
+    g.k_adv_bytes = 32;
+    g.layout = kLayoutSw128;
+  }
+  return g;
+}
+
+static int idesc_fmt(int dtype) { return dtype == FB_F16 ? 0 : (dtype == FB_BF16 ? 1 : 2); }
+
+// ------------------------------------------------------------ small kernels
+template <class T>
+__global__ void scale_kernel(T* c, long long ldc, int m, int n, float beta) {
+  const long long total = static_cast<long long>(m) * n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / n, col = i - r * n;
+    T* p = c + r * ldc + col;
+    *p = beta == 0.f ? from_f32<T>(0.f) : from_f32<T>(beta * to_f32(*p));
+  }
+}
+
+// Copy a [rows, cols] view with row pitch ld_src into a dense-pitched buffer (ld_dst).
+template <class T>
+__global__ void pack_kernel(const T* __restrict__ src, long long ld_src, T* __restrict__ dst, long long ld_dst,
+                            long long rows, long long cols) {
+  const long long total = rows * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    dst[r * ld_dst + c] = src[r * ld_src + c];
+  }
+}
+
+__global__ void bounded_wait_selftest_kernel(long long limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    // Same loop shape as mbar_wait, with a caller-chosen limit.
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done) {
+      if (mbar_try_wait(&bar, 0)) break;  // never: nothing arrives on this barrier
+      if (clock64() - t0 > limit) {
+        abort_flag = 1;
+        atomicCAS(&g_fb_status, 0, DEV_TIMEOUT_TEST_FLAG);
+        done = true;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------- tile choice
+static int choose_block_n(long long m, long long n, int sms) {
+  const long long tm = (m + kBlockM - 1) / kBlockM;
+  double best = 1e300;
+  int best_bn = 256;
+  const int cand[3] = {256, 128, 64};
+  const double eff[3] = {1.0, 0.88, 0.62};  // relative main-loop efficiency of the narrower tiles
+  for (int i = 0; i < 3; ++i) {
+    const long long tiles = tm * ((n + cand[i] - 1) / cand[i]);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * cand[i] / eff[i];
+    if (cost < best) { best = cost; best_bn = cand[i]; }
+  }
+  return best_bn;
+}
+
+template <int KIND, int BLOCK_N>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, int grid,
+                     cudaStream_t stream) {
+  using Cfg = TcCfg<KIND, BLOCK_N>;
+  auto kern = gemm_tc_kernel<KIND, BLOCK_N>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev]) {
+    FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  kern<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+static int dispatch_tc(int dtype, int block_n, const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p,
+                       int grid, cudaStream_t stream) {
+#define FB_CASE(KIND)                                                           \
+  switch (block_n) {                                                            \
+    case 256: return launch_tc<KIND, 256>(ma, mb, p, grid, stream);             \
+    case 128: return launch_tc<KIND, 128>(ma, mb, p, grid, stream);             \
+    default: return launch_tc<KIND, 64>(ma, mb, p, grid, stream);               \
+  }
+  if (dtype == FB_F16) { FB_CASE(0) }
+  if (dtype == FB_BF16) { FB_CASE(1) }
+  FB_CASE(2)
+#undef FB_CASE
+}
+
+static bool aligned16(const void* p, long long ld, int esz) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && ((ld * esz) & 15) == 0;
+}
+static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct PackPlan {
+  bool pack_a = false, pack_b = false;
+  long long a_rows = 0, a_cols = 0, a_ld = 0;
+  long long b_rows = 0, b_cols = 0, b_ld = 0;
+  size_t a_bytes = 0, b_bytes = 0;
+};
+
+static PackPlan plan_pack(int dtype, int transa, int transb, long long m, long long n, long long k, const void* A,
+                          long long lda, const void* B, long long ldb) {
+  PackPlan pl;
+  if (dtype == FB_F32) return pl;
+  const int esz = elem_size(dtype);
+  const long long per16 = 16 / esz;
+  pl.a_rows = transa ? k : m; pl.a_cols = transa ? m : k;
+  pl.b_rows = transb ? n : k; pl.b_cols = transb ? k : n;
+  pl.pack_a = !aligned16(A, lda, esz);
+  pl.pack_b = !aligned16(B, ldb, esz);
+  pl.a_ld = (pl.a_cols + per16 - 1) / per16 * per16;
+  pl.b_ld = (pl.b_cols + per16 - 1) / per16 * per16;
+  pl.a_bytes = pl.pack_a ? round_up(static_cast<size_t>(pl.a_rows) * pl.a_ld * esz, 256) : 0;
+  pl.b_bytes = pl.pack_b ? round_up(static_cast<size_t>(pl.b_rows) * pl.b_ld * esz, 256) : 0;
+  return pl;
+}
+
+template <class T>
+static int run_pack(const void* src, long long ld_src, void* dst, long long ld_dst, long long rows, long long cols,
+                    cudaStream_t stream) {
+  const long long total = rows * cols;
+  if (total == 0) return FB_OK;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pack_kernel<T><<<static_cast<int>(blocks), threads, 0, stream>>>(static_cast<const T*>(src), ld_src,
+                                                                   static_cast<T*>(dst), ld_dst, rows, cols);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+template <class T>
+static int run_scale(void* C, long long ldc, long long m, long long n, float beta, cudaStream_t stream) {
+  if (beta == 1.f || m == 0 || n == 0) return FB_OK;
+  const long long total = m * n;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  scale_kernel<T><<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<T*>(C), ldc, static_cast<int>(m),
+                                                                static_cast<int>(n), beta);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+static int run_sgemm_simt(int transa, int transb, long long m, long long n, long long k, float alpha, const float* A,
+                          long long lda, const float* B, long long ldb, float beta, float* C, long long ldc, int sms,
+                          cudaStream_t stream) {
+  SimtParams p{};
+  p.m = static_cast<int>(m); p.n = static_cast<int>(n); p.k = static_cast<int>(k);
+  p.alpha = alpha; p.beta = beta;
+  p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
+  p.a_mn_contig = transa ? 1 : 0;
+  p.b_mn_contig = transb ? 0 : 1;
+  p.a_vec = aligned16(A, lda, 4); p.b_vec = aligned16(B, ldb, 4); p.c_vec = aligned16(C, ldc, 4);
+  const long long big_tiles = ((m + 127) / 128) * ((n + 127) / 128);
+  if (big_tiles >= 2LL * sms) {
+    p.tiles_n = static_cast<int>((n + 127) / 128);
+    sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(big_tiles), 256, 0, stream>>>(p);
+  } else {
+    p.tiles_n = static_cast<int>((n + 63) / 64);
+    const long long tiles = ((m + 63) / 64) * p.tiles_n;
+    sgemm_simt_kernel<64, 64, 16><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
+  }
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
+                               int64_t lda, const void* B, int64_t ldb) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
+  return pl.a_bytes + pl.b_bytes;
+}
+
+int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, float alpha, const void* A,
+            int64_t lda, const void* B, int64_t ldb, float beta, void* C, int64_t ldc, void* workspace,
+            size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (dtype < FB_F32 || dtype > FB_BF16) return FB_ERR_INVALID_ARG;
+  if ((transa != FB_OP_N && transa != FB_OP_T) || (transb != FB_OP_N && transb != FB_OP_T)) return FB_ERR_INVALID_ARG;
+  if (m < 0 || n < 0 || k < 0) return FB_ERR_INVALID_ARG;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return FB_OK;
+  if (!C || ldc < n) return FB_ERR_INVALID_ARG;
+
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+
+  if (k == 0 || alpha == 0.f) {
+    switch (dtype) {
+      case FB_F16: return run_scale<__half>(C, ldc, m, n, beta, stream);
+      case FB_BF16: return run_scale<__nv_bfloat16>(C, ldc, m, n, beta, stream);
+      default: return run_scale<float>(C, ldc, m, n, beta, stream);
+    }
+  }
+  if (!A || !B) return FB_ERR_INVALID_ARG;
+  if (lda < (transa ? m : k) || ldb < (transb ? k : n)) return FB_ERR_INVALID_ARG;
+
+  if (dtype == FB_F32)
+    return run_sgemm_simt(transa, transb, m, n, k, alpha, static_cast<const float*>(A), lda,
+                          static_cast<const float*>(B), ldb, beta, static_cast<float*>(C), ldc, di->sm_count, stream);
+
+  const int esz = elem_size(dtype);
+  // Operands that TMA cannot address in place are packed to a 16-byte pitched copy first.
+  const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
+  if (pl.pack_a || pl.pack_b) {
+    if (!workspace || workspace_bytes < pl.a_bytes + pl.b_bytes || (reinterpret_cast<uintptr_t>(workspace) & 255))
+      return FB_ERR_WORKSPACE;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    if (pl.pack_a) {
+      int rc = esz == 2 ? run_pack<uint16_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream)
+                        : run_pack<uint32_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream);
+      if (rc) return rc;
+      A = ws; lda = pl.a_ld; ws += pl.a_bytes;
+    }
+    if (pl.pack_b) {
+      int rc = esz == 2 ? run_pack<uint16_t>(B, ldb, ws, pl.b_ld, pl.b_rows, pl.b_cols, stream)
+                        : run_pack<uint32_t>(B, ldb, ws, pl.b_ld, pl.b_rows, pl.b_cols, stream);
+      if (rc) return rc;
+      B = ws; ldb = pl.b_ld;
+    }
+  }
+
+  const int block_n = choose_block_n(m, n, di->sm_count);
+  const uint32_t span = kSwizzleBytes / esz;
+  const bool a_mn = transa == FB_OP_T;  // stored [k, m]: M contiguous
+  const bool b_mn = transb == FB_OP_N;  // stored [k, n]: N contiguous
+
+  CUtensorMap ma, mb;
+  int rc;
+  const bool atom32 = esz == 4;  // MN-major fp32 operands use the 32-byte-atom swizzle
+  if (a_mn) rc = encode_2d(&ma, dtype, A, m, k, lda * esz, span, span, atom32);
+  else rc = encode_2d(&ma, dtype, A, k, m, lda * esz, span, kBlockM);
+  if (rc) return rc;
+  if (b_mn) rc = encode_2d(&mb, dtype, B, n, k, ldb * esz, span, span, atom32);
+  else rc = encode_2d(&mb, dtype, B, k, n, ldb * esz, span, block_n);
+  if (rc) return rc;
+
+  TcGemmParams p{};
+  p.prob.m = static_cast<int>(m); p.prob.n = static_cast<int>(n);
+  p.prob.out = C; p.prob.ldo = ldc; p.prob.cin = C; p.prob.ldcin = ldc;
+  p.prob.vec_ok = aligned16(C, ldc, esz) ? 1 : 0;
+  p.k = static_cast<int>(k);
+  p.tiles_m = static_cast<int>((m + kBlockM - 1) / kBlockM);
+  p.tiles_n = static_cast<int>((n + block_n - 1) / block_n);
+  p.group_m = 16;
+  p.alpha = alpha; p.beta = beta;
+  p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, kBlockM, block_n);
+  p.block_k = span;
+  p.a = make_geom(esz, kBlockM, a_mn);
+  p.b = make_geom(esz, block_n, b_mn);
+  p.num_groups = 0;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int grid = static_cast<int>(tiles < di->sm_count ? tiles : di->sm_count);
+  return dispatch_tc(dtype, block_n, ma, mb, p, grid, stream);
+}
+
+size_t fb_group_workspace_bytes(int group_count) {
+  if (group_count <= 0) return 0;
+  return round_up(sizeof(GroupRec) * static_cast<size_t>(group_count), 256) + 256 +
+         sizeof(CUtensorMap) * 2 * static_cast<size_t>(group_count);
+}
+
+static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long n_hint,
+                       void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+  const int G = ga.num_groups;
+  if (!workspace || workspace_bytes < fb_group_workspace_bytes(G) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return FB_ERR_WORKSPACE;
+  const int esz = elem_size(dtype);
+  const uint32_t span = kSwizzleBytes / esz;
+  const int block_n = (n_hint > 0 && n_hint <= 64) ? 64 : ((n_hint > 0 && n_hint <= 128) ? 128 : 256);
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  ga.recs = reinterpret_cast<GroupRec*>(ws);
+  ga.total_tiles = reinterpret_cast<int*>(ws + round_up(sizeof(GroupRec) * static_cast<size_t>(G), 256));
+  ga.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ga.total_tiles) + 256);
+  ga.b_k_contig = b_k_contig;
+  ga.esz = esz;
+  ga.block_n = block_n;
+
+  // Templates carry everything the device does not patch: dtype, box, swizzle.
+  // Their address/extents are placeholders (the workspace itself, a valid 256-byte aligned range).
+  CUtensorMap ta, tb;
+  int rc = encode_2d(&ta, dtype, ws, span, kBlockM, kSwizzleBytes, span, kBlockM);
+  if (rc) return rc;
+  if (b_k_contig) rc = encode_2d(&tb, dtype, ws, span, block_n, kSwizzleBytes, span, block_n);
+  else rc = encode_2d(&tb, dtype, ws, span, span, kSwizzleBytes, span, span, esz == 4);
+  if (rc) return rc;
+
+  group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(ta, tb, ga);
+  FB_CUDA_OK(cudaGetLastError());
+
+  TcGemmParams p{};
+  p.alpha = alpha; p.beta = beta;
+  p.idesc = make_idesc(idesc_fmt(dtype), 0, b_k_contig ? 0 : 1, kBlockM, block_n);
+  p.block_k = span;
+  p.a = make_geom(esz, kBlockM, false);
+  p.b = make_geom(esz, block_n, !b_k_contig);
+  p.num_groups = G;
+  p.groups = ga.recs;
+  p.total_tiles = ga.total_tiles;
+  p.group_maps = ga.maps;
+  return dispatch_tc(dtype, block_n, ta, tb, p, di->sm_count, stream);
+}
+
+int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                  const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                  const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count, int64_t m_hint,
+                  int64_t n_hint, int64_t k_hint, float alpha, float beta, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  (void)m_hint;
+  (void)k_hint;
+  if (dtype != FB_TF32 && dtype != FB_F16 && dtype != FB_BF16) return FB_ERR_INVALID_ARG;
+  if (group_count < 0) return FB_ERR_INVALID_ARG;
+  if (group_count == 0) return FB_OK;
+  if (!d_a || !d_b || !d_out || !d_m || !d_n || !d_k || !d_lda || !d_ldb || !d_ldc) return FB_ERR_INVALID_ARG;
+  if (beta != 0.f && !d_c) return FB_ERR_INVALID_ARG;
+  GroupSetupArgs ga{};
+  ga.mode = 0;
+  ga.a_ptrs = reinterpret_cast<const long long*>(d_a);
+  ga.b_ptrs = reinterpret_cast<const long long*>(d_b);
+  ga.c_ptrs = reinterpret_cast<const long long*>(d_c ? d_c : d_out);
+  ga.out_ptrs = reinterpret_cast<const long long*>(d_out);
+  ga.m_sizes = d_m; ga.n_sizes = d_n; ga.k_sizes = d_k;
+  ga.ldas = d_lda; ga.ldbs = d_ldb; ga.ldcs = d_ldc;
+  ga.num_groups = group_count;
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, alpha, beta, n_hint, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const void* B, int64_t ldb,
+                int64_t b_group_stride, void* C, int64_t ldc, const int32_t* d_offs, int group_count, int64_t n,
+                int64_t k, void* workspace, size_t workspace_bytes, void* stream) {
+  if (dtype != FB_F16 && dtype != FB_BF16 && dtype != FB_TF32) return FB_ERR_INVALID_ARG;
+  if (group_count < 0 || n < 0 || k < 0) return FB_ERR_INVALID_ARG;
+  if (n > 0x7fffffffLL || k > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (group_count == 0 || n == 0) return FB_OK;
+  if (!A || !B || !C || !d_offs) return FB_ERR_INVALID_ARG;
+  if (lda < k || ldc < n || ldb < (b_k_contiguous ? k : n)) return FB_ERR_INVALID_ARG;
+  GroupSetupArgs ga{};
+  ga.mode = 1;
+  ga.offs = d_offs;
+  ga.a_base = A; ga.b_base = B; ga.out_base = C;
+  ga.mm_lda = lda; ga.mm_ldb = ldb; ga.mm_b_group_stride = b_group_stride; ga.mm_ldo = ldc;
+  ga.mm_n = static_cast<int>(n); ga.mm_k = static_cast<int>(k);
+  ga.num_groups = group_count;
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, 1.f, 0.f, n, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+const char* fb_status_string(int status) {
+  switch (status) {
+    case FB_OK: return "ok";
+    case FB_ERR_INVALID_ARG: return "invalid argument";
+    case FB_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case FB_ERR_LAUNCH: return "CUDA error at launch";
+    case FB_ERR_UNSUPPORTED: return "unsupported device or size";
+    case FB_ERR_DRIVER: return "tensor-map encoding failed";
+    case FB_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+    case DEV_TIMEOUT_PRODUCER_EMPTY: return "device: TMA producer timed out waiting for a free stage";
+    case DEV_TIMEOUT_MMA_FULL: return "device: MMA issuer timed out waiting for operand data";
+    case DEV_TIMEOUT_MMA_TMEM_EMPTY: return "device: MMA issuer timed out waiting for a free accumulator";
+    case DEV_TIMEOUT_EPI_TMEM_FULL: return "device: epilogue timed out waiting for an accumulator";
+    case DEV_TIMEOUT_TEST_FLAG: return "device: self-test wait timed out (expected)";
+    case DEV_TIMEOUT_PEER: return "device: CTA-pair handshake timed out";
+    case DEV_GROUP_MISALIGNED: return "device: a group's A/B is not 16-byte aligned; group skipped";
+    default: return "unknown status";
+  }
+}
+
+int fb_device_status(int reset) {
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return FB_ERR_LAUNCH;
+  if (cudaMemcpyFromSymbol(&v, g_fb_status, sizeof(int)) != cudaSuccess) return FB_ERR_LAUNCH;
+  if (reset && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_fb_status, &zero, sizeof(int)) != cudaSuccess) return FB_ERR_LAUNCH;
+  }
+  return v;
+}
+
+int fb_last_cuda_error(void) { return t_last_cuda_error; }
+
+int fb_sm_count(void) {
+  const DeviceInfo* di = device_info();
+  return di ? di->sm_count : 0;
+}
+
+int fb_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 4000000000LL) return FB_ERR_INVALID_ARG;
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles);
+  FB_CUDA_OK(cudaGetLastError());
+  return fb_device_status(1);
+}
+
+}  // extern "C"

@@ -1,0 +1,11 @@
+"""Operator exports: the GEMM names and BLAS constants of ``flag_blas.ops``
+(reference: ``src/flag_blas/ops/__init__.py:35-43,75-94``)."""
+from ._constants import CUBLAS_OP_C, CUBLAS_OP_N, CUBLAS_OP_T
+from .level3 import (bfgemm, group_bfgemm, group_gemm, group_hgemm, group_mm, group_tf32gemm, hgemm, sgemm,
+                     tf32gemm)
+
+__all__ = [
+    "CUBLAS_OP_N", "CUBLAS_OP_T", "CUBLAS_OP_C",
+    "sgemm", "hgemm", "bfgemm", "tf32gemm",
+    "group_bfgemm", "group_hgemm", "group_tf32gemm", "group_mm", "group_gemm",
+]

@@ -1,0 +1,150 @@
+"""Grouped GEMM operators: ``group_bfgemm``, ``group_hgemm``, ``group_tf32gemm``,
+``group_mm`` and the convenience wrapper ``group_gemm``.
+
+Signatures follow the reference (``src/flag_blas/ops/level3/group_gemm.py:221-262``,
+``:380-421``, ``:540-581``, ``:689-717``): every pointer / size / stride array is a
+*device* tensor that is never read on the host; ``alpha`` / ``beta`` are shared by
+all groups; the result is written through ``d_output_ptrs`` and ``group_out`` is
+returned.  ``group_tf32gemm`` expects each ``B_g`` stored ``[n_g, k_g]``
+(``group_gemm.py:488-504``), the 16-bit flavours ``[k_g, n_g]``.
+
+``group_gemm(group_A, group_B, group_C, offs_table, alpha=, beta=)`` is the
+signature the reference's ``tests/test_group_gemm.py:60-119`` calls but the
+reference never defines; it is provided here on top of the grouped kernels.
+"""
+import torch
+
+from ... import _lib
+
+_lib_handle = _lib.lib
+
+
+def _workspace(device, groups):
+    nbytes = _lib_handle.fb_group_workspace_bytes(groups)
+    # tile table + per-group tensor maps, from torch's caching allocator (stream ordered)
+    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
+
+
+def _group(code, b_k_contig, name, group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes,
+           d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta):
+    alpha = alpha.item() if isinstance(alpha, torch.Tensor) else float(alpha)
+    beta = beta.item() if isinstance(beta, torch.Tensor) else float(beta)
+    if group_size == 0:
+        return group_out
+    for t in (d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs):
+        assert t.dtype == torch.int64 and t.is_cuda and t.is_contiguous() and t.numel() >= group_size
+    for t in (d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs):
+        assert t.dtype == torch.int32 and t.is_cuda and t.is_contiguous() and t.numel() >= group_size
+    dev = d_a_ptrs.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream().cuda_stream
+        ws, nbytes = _workspace(dev, group_size)
+        _lib.check(
+            _lib_handle.fb_group_gemm(code, b_k_contig, d_a_ptrs.data_ptr(), d_b_ptrs.data_ptr(), d_c_ptrs.data_ptr(),
+                                      d_output_ptrs.data_ptr(), d_m_sizes.data_ptr(), d_n_sizes.data_ptr(),
+                                      d_k_sizes.data_ptr(), d_ldas.data_ptr(), d_ldbs.data_ptr(), d_ldcs.data_ptr(),
+                                      group_size, int(M), int(N), int(K), alpha, beta, ws.data_ptr(), nbytes, stream),
+            name,
+        )
+    return group_out
+
+
+def group_bfgemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas,
+                 d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
+    """bf16 grouped GEMM (reference: ops/level3/group_gemm.py:221-262).
+
+    ``use_small_m`` is accepted for compatibility; one kernel serves every m_g.
+    """
+    return _group(_lib.FB_BF16, 0, "group_bfgemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+
+
+def group_hgemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas,
+                d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
+    """fp16 grouped GEMM (reference: ops/level3/group_gemm.py:380-421)."""
+    return _group(_lib.FB_F16, 0, "group_hgemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+
+
+def group_tf32gemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas,
+                   d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
+    """fp32-storage / TF32 grouped GEMM, B_g stored [n_g, k_g] (reference: group_gemm.py:540-581)."""
+    return _group(_lib.FB_TF32, 1, "group_tf32gemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+
+
+_CODES = {torch.bfloat16: _lib.FB_BF16, torch.float16: _lib.FB_F16}
+
+
+def group_mm(A: torch.Tensor, B: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
+    """``C[o_{g-1}:o_g] = A[o_{g-1}:o_g] @ B[g]`` (reference: ops/level3/group_gemm.py:689-717).
+
+    ``offs`` holds int32 cumulative end rows on the device.  Rows of ``C`` beyond
+    ``offs[-1]`` are left uninitialised, as in the reference (``new_empty``).
+    """
+    assert A.dim() == 2
+    assert B.dim() == 3
+    M, K = A.shape
+    num_groups, BK, N = B.shape
+    assert num_groups == offs.numel()
+    assert BK == K
+    assert A.dtype == B.dtype and A.dtype in _CODES
+    assert A.is_cuda and B.is_cuda and offs.is_cuda
+    if A.stride(1) != 1:
+        A = A.contiguous()
+    if B.stride(2) == 1:
+        b_k_contig, ldb = 0, B.stride(1)
+    elif B.stride(1) == 1:
+        b_k_contig, ldb = 1, B.stride(2)
+    else:
+        B = B.contiguous()
+        b_k_contig, ldb = 0, B.stride(1)
+    if offs.dtype != torch.int32:
+        offs = offs.to(torch.int32)
+    offs = offs.contiguous()
+    C = A.new_empty(M, N)
+    if M == 0 or N == 0 or num_groups == 0:
+        return C
+    with torch.cuda.device(A.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        ws, nbytes = _workspace(A.device, num_groups)
+        _lib.check(
+            _lib_handle.fb_group_mm(_CODES[A.dtype], b_k_contig, A.data_ptr(), A.stride(0), B.data_ptr(), ldb,
+                                    B.stride(0), C.data_ptr(), C.stride(0), offs.data_ptr(), num_groups, N, K,
+                                    ws.data_ptr(), nbytes, stream),
+            "group_mm",
+        )
+    return C
+
+
+def group_gemm(group_A, group_B, group_C, offs_table, alpha=1.0, beta=0.0):
+    """``out_g = alpha * A_g @ B_g + beta * C_g`` over row segments (bf16 / fp16).
+
+    ``offs_table[g] = [m_g, n, k, start_M, start_K, start_C]`` (a host list, as in
+    the reference's ``tests/test_group_gemm.py:60-69``): ``A_g`` = ``m_g`` rows of
+    ``group_A [sum m, k]`` from row ``start_M``, ``B_g`` = ``k`` rows of
+    ``group_B [E*k, n]`` from row ``start_K``, ``C_g`` / ``out_g`` = ``m_g`` rows from
+    row ``start_C``.  Returns a new tensor shaped like ``group_C``.
+    """
+    assert group_A.dtype == group_B.dtype == group_C.dtype and group_A.dtype in _CODES
+    assert group_A.is_contiguous() and group_B.is_contiguous() and group_C.is_contiguous()
+    dev = group_A.device
+    out = torch.empty_like(group_C)
+    G = len(offs_table)
+    if G == 0:
+        return out
+    esz = group_A.element_size()
+    lda, ldb, ldc = group_A.shape[1], group_B.shape[1], group_C.shape[1]
+    rows = [[int(v) for v in r] for r in offs_table]
+    ptrs = torch.tensor(
+        [[group_A.data_ptr() + r[3] * lda * esz for r in rows],
+         [group_B.data_ptr() + r[4] * ldb * esz for r in rows],
+         [group_C.data_ptr() + r[5] * ldc * esz for r in rows],
+         [out.data_ptr() + r[5] * ldc * esz for r in rows]], dtype=torch.int64).to(dev)
+    sizes = torch.tensor(
+        [[r[0] for r in rows], [r[1] for r in rows], [r[2] for r in rows],
+         [lda] * G, [ldb] * G, [ldc] * G], dtype=torch.int32).to(dev)
+    fn = group_bfgemm if group_A.dtype == torch.bfloat16 else group_hgemm
+    fn(out, ptrs[0], ptrs[1], ptrs[2], ptrs[3], sizes[0], sizes[1], sizes[2], sizes[3], sizes[4], sizes[5], G,
+       sum(r[0] for r in rows), rows[0][1], rows[0][2], alpha, beta)
+    return out

@@ -1,0 +1,153 @@
+/*
+ * flagblas_b200 -- C ABI of the B200 (sm_100a) GEMM back end.
+ *
+ * Plain pointers and sizes only: every entry point can be bound from C, ctypes,
+ * pybind11 or cgo without any tensor library.  All matrices are ROW-MAJOR with
+ * `ld*` = row stride in elements, exactly as in the reference's Python
+ * operators.  Every function returns 0 (FB_OK) or a negative FB_ERR_* code; none
+ * throws, aborts or synchronises the device.  Work is enqueued on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) of the
+ * CUDA device that is current on the calling thread.
+ *
+ * Each declaration cites the reference interface it stands in for, by the
+ * reference project's own paths.
+ */
+#ifndef FLAGBLAS_B200_H_
+#define FLAGBLAS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+enum {
+  FB_OK = 0,
+  FB_ERR_INVALID_ARG = -1,   /* bad enum, negative size, ld too small, NULL pointer */
+  FB_ERR_WORKSPACE = -2,     /* workspace missing or smaller than fb_*_workspace_bytes() */
+  FB_ERR_LAUNCH = -3,        /* CUDA reported an error at launch (see fb_last_cuda_error) */
+  FB_ERR_UNSUPPORTED = -4,   /* device is not sm_100, or size beyond 2^31-1 */
+  FB_ERR_DRIVER = -5,        /* tensor-map encoder unavailable / rejected the arguments */
+  FB_ERR_TOO_LARGE = -6      /* request exceeds a fixed capacity (see the entry point) */
+};
+
+/* ---- element / arithmetic types ----------------------------------------- */
+enum {
+  FB_F32 = 0,   /* fp32 storage, IEEE FFMA on the CUDA cores          (sgemm)     */
+  FB_TF32 = 1,  /* fp32 storage, TF32 tensor-core multiply, fp32 acc  (tf32gemm)  */
+  FB_F16 = 2,   /* fp16 storage, fp32 accumulate, one rounding        (hgemm)     */
+  FB_BF16 = 3   /* bf16 storage, fp32 accumulate, one rounding        (bfgemm)    */
+};
+
+/* transposition flags: same numeric values as the reference's
+ * CUBLAS_OP_N / CUBLAS_OP_T (src/flag_blas/ops/level3/sgemm.py:30-32). */
+enum { FB_OP_N = 0, FB_OP_T = 1 };
+
+/*
+ * Dense GEMM:  C[m,n] <- alpha * op(A) * op(B) + beta * C      (in place on C)
+ *
+ *   transa = N: A stored [m, lda>=k];   transa = T: A stored [k, lda>=m]
+ *   transb = N: B stored [k, ldb>=n];   transb = T: B stored [n, ldb>=k]
+ *   C stored [m, ldc>=n].  C is never read when beta == 0.
+ *   m == 0 or n == 0: nothing is done.  k == 0 or alpha == 0: the m x n block
+ *   of C is scaled by beta.
+ *
+ * Replaces the bodies of
+ *   sgemm   src/flag_blas/ops/level3/sgemm.py:421-477
+ *           (+ src/flag_blas/runtime/backend/_nvidia/hopper/ops/sgemm.py:1512-1662)
+ *   hgemm   src/flag_blas/ops/level3/hgemm.py:473-529
+ *           (+ .../hopper/ops/hgemm.py:2279-2422)
+ *   bfgemm  src/flag_blas/ops/level3/bfgemm.py:473-529
+ *           (+ .../hopper/ops/bfgemm.py:1048-1268)
+ * and provides the dense TF32 flavour the reference only has in grouped form
+ * (src/flag_blas/ops/level3/group_gemm.py:427-581).
+ *
+ * Tensor-core types need A and B with 16-byte aligned base and row pitch to be
+ * fetched in place; otherwise the operand is first packed into `workspace`
+ * (size from fb_gemm_workspace_bytes, 256-byte aligned device memory).  FB_F32
+ * never needs a workspace.
+ */
+int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, float alpha, const void* A,
+            int64_t lda, const void* B, int64_t ldb, float beta, void* C, int64_t ldc, void* workspace,
+            size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace fb_gemm needs for these arguments (0 when none). */
+size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
+                               int64_t lda, const void* B, int64_t ldb);
+
+/*
+ * Grouped GEMM:  for g in [0, group_count):
+ *     out_g[m_g,n_g] <- alpha * A_g[m_g,k_g] * B_g + beta * C_g
+ *
+ * Every array argument is DEVICE memory and is only read on the device:
+ *   d_a/d_b/d_c/d_out : int64 addresses of A_g, B_g, C_g, out_g
+ *   d_m/d_n/d_k       : int32 sizes;   d_lda/d_ldb/d_ldc : int32 row strides
+ *   (out_g and C_g share d_ldc, as in the reference).
+ *   b_k_contiguous = 0: B_g stored [k_g, ldb>=n_g]  (group_bfgemm / group_hgemm)
+ *   b_k_contiguous = 1: B_g stored [n_g, ldb>=k_g]  (group_tf32gemm)
+ * A_g, B_g need 16-byte aligned base and row pitch; a group that violates
+ * this is skipped and reported through fb_device_status().
+ * Groups with m_g == 0 or n_g == 0 produce no work.
+ *
+ * Replaces group_bfgemm / group_hgemm / group_tf32gemm,
+ *   src/flag_blas/ops/level3/group_gemm.py:221-262, 380-421, 540-581
+ *   (+ src/flag_blas/runtime/backend/_nvidia/hopper/ops/group_gemm.py:699-891).
+ * dtype is FB_BF16, FB_F16 or FB_TF32.  m_hint / n_hint / k_hint are the
+ * reference's M, N, K arguments: host-side hints (typical sizes) that only
+ * steer the tile shape; 0 = unknown.  `workspace` holds the device-built
+ * tile table and tensor maps: fb_group_workspace_bytes(group_count) bytes,
+ * 256-byte aligned; it may be reused by the next call on the same stream.
+ */
+int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                  const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                  const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count, int64_t m_hint,
+                  int64_t n_hint, int64_t k_hint, float alpha, float beta, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/*
+ * Grouped matmul over row segments of one matrix:
+ *     C[o_{g-1}:o_g, :] <- A[o_{g-1}:o_g, :] @ B[g]        (o_{-1} = 0)
+ *   A [M, lda>=k]; B[g] at b + g*b_group_stride with rows `ldb` apart, stored
+ *   [k, n] (b_k_contiguous = 0) or [n, k] (b_k_contiguous = 1); C [M, ldc>=n];
+ *   d_offs = int32 DEVICE array of cumulative end rows.  dtype FB_BF16 / FB_F16.
+ * Replaces group_mm, src/flag_blas/ops/level3/group_gemm.py:689-717
+ *   (+ .../hopper/ops/group_gemm.py:894-943).
+ */
+int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const void* B, int64_t ldb,
+                int64_t b_group_stride, void* C, int64_t ldc, const int32_t* d_offs, int group_count, int64_t n,
+                int64_t k, void* workspace, size_t workspace_bytes, void* stream);
+
+size_t fb_group_workspace_bytes(int group_count);
+
+/* ---- diagnostics -------------------------------------------------------- */
+
+/* Human-readable text for an FB_* code or a device status. */
+const char* fb_status_string(int status);
+
+/*
+ * Device-side status word of the current device: 0, or the code left by a
+ * kernel that gave up on a bounded wait (1xx) or skipped a misaligned group
+ * (2xx).  Synchronises the device.  `reset` != 0 clears the word.
+ */
+int fb_device_status(int reset);
+
+/* cudaError_t (as int) of the last failed CUDA call made by this library on this thread. */
+int fb_last_cuda_error(void);
+
+/* Number of SMs the persistent kernels size their grids with on the current device. */
+int fb_sm_count(void);
+
+/*
+ * Self-test of the bounded-wait path: one CTA waits on an mbarrier that nothing
+ * ever completes, with a limit of `limit_cycles` SM clocks, and must come back
+ * with the time-out status.  Returns that device status (105 when the path works).
+ * Synchronises the device; leaves the status word cleared.
+ */
+int fb_selftest_bounded_wait(int64_t limit_cycles, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAGBLAS_B200_H_ */

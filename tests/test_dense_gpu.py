@@ -1,0 +1,240 @@
+"""Parity of the dense CUDA path (through the flag_blas operator API -> C ABI) against the
+CPU oracle on identical seeded inputs, against the reference-made golden vectors, and --
+at the benchmark's full sizes -- through size-independent properties.
+
+Tolerances (|got-ref| <= rtol*scale + rtol*|ref|, scale = |alpha|*sqrt(k)*rms(A)*rms(B)):
+  fp16 / bf16 1e-2, tf32 1e-3, fp32 (sgemm) 1e-5.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flagblas_b200 as fb
+from flagblas_b200.ops import CUBLAS_OP_N, CUBLAS_OP_T
+from tests.helpers import KINDS, assert_parity, make_dense, oracle_dense, result_scale
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TRANS = [(0, 0), (0, 1), (1, 0), (1, 1)]
+
+
+def _run(kind, ta, tb, m, n, k, alpha, beta, pad=0, seed=0, scale=1.0, c_nan=False):
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, pad=pad, seed=seed, scale=scale, c_nan=c_nan)
+    ref = oracle_dense(kind, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
+    Ad, Bd, Cd = A.to(DEV), B.to(DEV), C.to(DEV)
+    getattr(fb, KINDS[kind][1])(ta, tb, m, n, k, alpha, Ad, lda, Bd, ldb, beta, Cd, ldc)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    got = Cd.float().cpu()
+    sc = result_scale(k, A, B, alpha) + abs(beta) * (0.0 if c_nan else 1.0)
+    what = "%s ta=%d tb=%d %dx%dx%d a=%g b=%g pad=%d" % (kind, ta, tb, m, n, k, alpha, beta, pad)
+    assert_parity(got, ref, KINDS[kind][2], sc, what)
+    if kind == "tf32":
+        # The tensor core truncates fp32 operands to TF32; the reference's Triton lowering rounds
+        # them to nearest (cvt.rna).  The two stay within the same 1e-3 bound of each other.
+        ref_rna = oracle_dense(kind, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, tf32_mode="rna")
+        assert_parity(got, ref_rna, KINDS[kind][2], sc, what + " (vs round-to-nearest inputs)")
+    return got, ref
+
+
+# shapes: tile-exact, multi-tile, ragged m/n/k, skinny, k tails; (m, n, k)
+SHAPES = [(128, 256, 64), (256, 512, 256), (64, 64, 64), (130, 270, 100), (512, 384, 1000), (1, 8, 8), (8, 1, 32),
+          (33, 1025, 72), (1000, 72, 4100), (2048, 2048, 512)]
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+@pytest.mark.parametrize("ta,tb", TRANS)
+def test_shapes_alpha_beta(kind, ta, tb):
+    ab = (2.5, 0.5) if kind == "fp32" else (1.5, 0.5)   # the reference tests' pairs
+    for i, (m, n, k) in enumerate(SHAPES):
+        _run(kind, ta, tb, m, n, k, ab[0], ab[1], seed=i)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+@pytest.mark.parametrize("ta,tb", TRANS)
+def test_padded_leading_dims_leave_padding_untouched(kind, ta, tb):
+    pad = 8 if kind in ("bf16", "fp16") else 4           # keeps rows 16-byte aligned: in-place TMA path
+    m, n, k = 200, 328, 136
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, pad=pad, seed=3)
+    Cd = C.to(DEV)
+    getattr(fb, KINDS[kind][1])(ta, tb, m, n, k, 1.0, A.to(DEV), lda, B.to(DEV), ldb, 1.0, Cd, ldc)
+    torch.cuda.synchronize()
+    assert torch.equal(Cd.cpu()[:, n:], C[:, n:])
+    ref = oracle_dense(kind, ta, tb, m, n, k, 1.0, A, lda, B, ldb, 1.0, C, ldc)
+    assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], result_scale(k, A, B, 1.0) + 1.0, "padded %s" % kind)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+@pytest.mark.parametrize("ta,tb", TRANS)
+def test_unaligned_shapes(kind, ta, tb):
+    """Odd sizes with ld == size: rows are not 16-byte aligned (the reference's 511/1023 class)."""
+    for (m, n, k) in [(511, 511, 511), (129, 67, 255), (63, 1023, 77)]:
+        _run(kind, ta, tb, m, n, k, 1.5, 0.5, seed=7)
+    _run(kind, ta, tb, 70, 130, 45, 1.0, 0.0, pad=3, seed=8, c_nan=True)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+def test_misaligned_base_pointers(kind):
+    dt = KINDS[kind][0]
+    m, n, k = 96, 80, 72
+    g = torch.Generator().manual_seed(5)
+    bufA = torch.randn(m * k + 8, generator=g).to(dt).to(DEV)
+    bufB = torch.randn(k * n + 8, generator=g).to(dt).to(DEV)
+    bufC = torch.randn(m * n + 8, generator=g).to(dt).to(DEV)
+    for off in (1, 3):
+        A, B, C = bufA[off:off + m * k], bufB[off:off + k * n], bufC[off:off + m * n].clone()
+        Ch = C.float().cpu().numpy().copy()
+        from oracle import gemm_oracle as go
+        go.gemm(kind, 0, 0, m, n, k, 1.5, A.float().cpu().numpy(), k, B.float().cpu().numpy(), n, 0.5, Ch, n,
+                tf32_mode="trunc")
+        Cv = bufC[off:off + m * n]
+        getattr(fb, KINDS[kind][1])(0, 0, m, n, k, 1.5, A, k, B, n, 0.5, Cv, n)
+        torch.cuda.synchronize()
+        assert_parity(Cv.float().cpu(), torch.from_numpy(Ch), KINDS[kind][2],
+                      result_scale(k, A.cpu(), B.cpu(), 1.5) + 0.5, "misaligned base %s off=%d" % (kind, off))
+
+
+# ------------------------------------------------------------------ edge cases (reference tests/test_sgemm.py:148-245)
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+def test_alpha_zero_scales_c(kind):
+    A, lda, B, ldb, C, ldc = make_dense(kind, 0, 0, 64, 64, 64, seed=1)
+    Cd = C.to(DEV)
+    getattr(fb, KINDS[kind][1])(0, 0, 64, 64, 64, 0.0, A.to(DEV), lda, B.to(DEV), ldb, 0.5, Cd, ldc)
+    ref = oracle_dense(kind, 0, 0, 64, 64, 64, 0.0, A, lda, B, ldb, 0.5, C, ldc)
+    assert torch.equal(Cd.float().cpu(), ref)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+@pytest.mark.parametrize("ta,tb", TRANS)
+def test_beta_zero_never_reads_c(kind, ta, tb):
+    got_nan, _ = _run(kind, ta, tb, 192, 320, 96, 2.5, 0.0, seed=2, c_nan=True)
+    assert not torch.isnan(got_nan).any()
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, 192, 320, 96, seed=2)
+    Cz = torch.zeros_like(C).to(DEV)
+    getattr(fb, KINDS[kind][1])(ta, tb, 192, 320, 96, 2.5, A.to(DEV), lda, B.to(DEV), ldb, 0.0, Cz, ldc)
+    assert torch.equal(Cz.float().cpu(), got_nan)   # NaN-filled and zero-filled C give identical bits
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+@pytest.mark.parametrize("m,n,k", [(0, 64, 64), (64, 0, 64), (64, 64, 0)])
+def test_empty_dims_scale_whole_c(kind, m, n, k):
+    dt = KINDS[kind][0]
+    g = torch.Generator().manual_seed(4)
+    A = torch.randn(max(m, 1) * max(k, 1), generator=g).to(dt)
+    B = torch.randn(max(k, 1) * max(n, 1), generator=g).to(dt)
+    C = torch.randn(max(m, 1), max(n, 1), generator=g).to(dt)   # e.g. (1 x 64) for m == 0
+    Cd = C.to(DEV)
+    getattr(fb, KINDS[kind][1])(0, 0, m, n, k, 2.5, A.to(DEV), max(k, 1), B.to(DEV), max(n, 1), 0.5, Cd, max(n, 1))
+    ref = oracle_dense(kind, 0, 0, m, n, k, 2.5, A, max(k, 1), B, max(n, 1), 0.5, C, max(n, 1))
+    assert torch.equal(Cd.float().cpu(), ref)
+    Cd = C.to(DEV)
+    getattr(fb, KINDS[kind][1])(0, 0, m, n, k, 2.5, A.to(DEV), max(k, 1), B.to(DEV), max(n, 1), 0.0, Cd, max(n, 1))
+    assert torch.count_nonzero(Cd) == 0
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32", "fp32"])
+def test_alpha_beta_pairs_and_tensor_scalars(kind):
+    for alpha, beta in [(1.0, 0.0), (0.0, 1.0), (1.0, 1.0), (-1.0, 0.5), (2.5, -0.5)]:
+        _run(kind, 0, 0, 256, 256, 256, alpha, beta, seed=9)
+    A, lda, B, ldb, C, ldc = make_dense(kind, 0, 1, 128, 128, 128, seed=10)
+    C1, C2 = C.to(DEV), C.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    op(0, 1, 128, 128, 128, 1.5, A.to(DEV), lda, B.to(DEV), ldb, 0.5, C1, ldc)
+    op(0, 1, 128, 128, 128, torch.tensor(1.5, device=DEV), A.to(DEV), lda, B.to(DEV), ldb, torch.tensor(0.5), C2, ldc)
+    assert torch.equal(C1, C2)
+
+
+# ------------------------------------------------------------------ reference-made golden vectors on the GPU
+@pytest.mark.parametrize("kind", ["fp32", "fp16"])
+def test_golden_dense_on_gpu(golden_dir, kind):
+    z = np.load(os.path.join(golden_dir, "dense_%s.npz" % kind))
+    dt = KINDS[kind][0]
+    for key in sorted(k[:-2] for k in z.files if k.endswith("_p")):
+        ta, tb, m, n, k, lda, ldb, ldc, alpha, beta = z[key + "_p"]
+        ta, tb, m, n, k, lda, ldb, ldc = (int(v) for v in (ta, tb, m, n, k, lda, ldb, ldc))
+        A = torch.from_numpy(z[key + "_A"]).to(dt).to(DEV)
+        B = torch.from_numpy(z[key + "_B"]).to(dt).to(DEV)
+        C = torch.from_numpy(z[key + "_C0"]).to(dt).to(DEV)
+        getattr(fb, KINDS[kind][1])(ta, tb, m, n, k, float(alpha), A, lda, B, ldb, float(beta), C, ldc)
+        ref = torch.from_numpy(z[key + "_C"])
+        got = C.float().cpu()
+        assert torch.equal(got[:, n:], ref[:, n:])
+        assert_parity(got[:, :n], ref[:, :n], KINDS[kind][2], result_scale(k, A.cpu(), B.cpu(), alpha) + abs(beta),
+                      "golden %s %s" % (kind, key))
+
+
+def test_golden_config1_sgemm512(golden_dir):
+    z = np.load(os.path.join(golden_dir, "config1_sgemm512.npz"))
+    g = torch.Generator(device="cpu").manual_seed(0)
+    A = torch.rand(512, 512, generator=g) * 2 - 1
+    B = torch.rand(512, 512, generator=g) * 2 - 1
+    C = torch.full((512, 512), float("nan"), device=DEV)
+    fb.sgemm(CUBLAS_OP_N, CUBLAS_OP_N, 512, 512, 512, 1.0, A.to(DEV), 512, B.to(DEV), 512, 0.0, C, 512)
+    got = C.cpu()
+    ref = torch.from_numpy(z["C_sub"])
+    assert_parity(got[::4, ::4], ref, 1e-5, result_scale(512, A, B, 1.0), "config1")
+    assert abs(float(got.double().sum()) - float(z["C_sum"])) < 1e-2
+
+
+# ------------------------------------------------------------------ full benchmark sizes, size-independent properties
+def _cublas(kind, ta, tb, A, B):
+    opA = A.t() if ta else A
+    opB = B.t() if tb else B
+    return (opA.float() @ opB.float()) if kind != "fp32" else opA @ opB
+
+
+@pytest.mark.parametrize("cfg", ["C2_hgemm_8192", "C3_bfgemm_mlp", "C5_tf32_skinny", "C5_tf32_4096_TN"])
+def test_full_size_properties(cfg):
+    """At sizes the CPU oracle cannot finish: (1) a row/column sample against the fp64 oracle,
+    (2) linearity in alpha, (3) NaN-C is never read when beta == 0."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    if cfg == "C2_hgemm_8192":
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "fp16", 0, 0, 8192, 8192, 8192, 1.0, 0.0, 0.05, 0.05, 1
+    elif cfg == "C3_bfgemm_mlp":
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 1.0, 0.02, 2
+    elif cfg == "C5_tf32_skinny":
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4
+    else:
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "tf32", 1, 0, 4096, 4096, 4096, 1.5, 0.5, 0.577, 0.577, 4
+    dt, opname, rtol = KINDS[kind]
+    op = getattr(fb, opname)
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    A = (torch.randn((k, m) if ta else (m, k), generator=g, device=DEV) * sa).to(dt)
+    B = (torch.randn((n, k) if tb else (k, n), generator=g, device=DEV) * sb).to(dt)
+    C0 = (torch.randn(m, n, generator=g, device=DEV) * 0.02).to(dt)
+    if beta == 0.0:
+        C0.fill_(float("nan"))
+    C = C0.clone()
+    op(ta, tb, m, n, k, alpha, A, A.shape[1], B, B.shape[1], beta, C, n)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    assert not torch.isnan(C).any()
+    # (1) sampled rows and columns against fp64 on the host
+    rows = torch.tensor(sorted({0, 1, 127, 128, m // 2 + 3, m - 1}), device=DEV)
+    cols = torch.tensor(sorted({0, 255, 256, n // 2 + 5, n - 1}), device=DEV)
+    opA = (A.t() if ta else A)
+    opB = (B.t() if tb else B)
+    if kind == "tf32":
+        trunc = lambda x: (x.view(torch.int32) & ~0x1FFF).view(torch.float32)  # noqa: E731
+        opA, opB = trunc(opA.contiguous()), trunc(opB.contiguous())
+    sc = abs(alpha) * (k ** 0.5) * sa * sb + abs(beta) * 0.02
+    ref_rows = alpha * (opA[rows].double().cpu() @ opB.double().cpu())
+    ref_cols = alpha * (opA.double().cpu() @ opB[:, cols].double().cpu())
+    if beta != 0.0:
+        ref_rows += beta * C0[rows].double().cpu()
+        ref_cols += beta * C0[:, cols].double().cpu()
+    assert_parity(C[rows].float().cpu(), ref_rows.float(), rtol, sc, cfg + " rows")
+    assert_parity(C[:, cols].float().cpu(), ref_cols.float(), rtol, sc, cfg + " cols")
+    # (2) linearity: doubling alpha (beta = 0) doubles the result exactly (power-of-two scaling)
+    C1 = torch.empty_like(C)
+    C2 = torch.empty_like(C)
+    op(ta, tb, m, n, k, 1.0, A, A.shape[1], B, B.shape[1], 0.0, C1, n)
+    op(ta, tb, m, n, k, 2.0, A, A.shape[1], B, B.shape[1], 0.0, C2, n)
+    assert torch.equal(C1.float() * 2.0, C2.float())
+    # (3) independent cross-check of the whole result: cuBLAS through torch on the same data
+    if m * n <= 8192 * 8192:
+        refc = _cublas(kind, ta, tb, A, B)
+        d = (C1.float() - refc).abs().max().item()
+        assert d <= 2 * rtol * (k ** 0.5) * sa * sb + rtol * refc.abs().max().item(), d

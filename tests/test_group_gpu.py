@@ -1,0 +1,194 @@
+"""Parity of the grouped CUDA path against the CPU oracle and the reference-made golden vectors."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flagblas_b200 as fb
+from oracle import gemm_oracle as go
+from tests.helpers import KINDS, assert_parity
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FN = {"bf16": "group_bfgemm", "fp16": "group_hgemm", "tf32": "group_tf32gemm"}
+
+
+def _i64(v):
+    return torch.tensor(v, dtype=torch.int64, device=DEV)
+
+
+def _i32(v):
+    return torch.tensor(v, dtype=torch.int32, device=DEV)
+
+
+def _run_group(kind, ms, K, N, alpha, beta, seed=0, var_nk=False):
+    """Mirror of the reference tests' set-up (tests/test_group_bfgemm.py:99-160): one A buffer of
+    stacked rows, per-group B, raw device pointer / size arrays."""
+    dt = KINDS[kind][0]
+    nk = kind == "tf32"                      # group_tf32gemm stores B_g as [n, k]
+    E = len(ms)
+    g = torch.Generator().manual_seed(seed)
+    ks = [K - 8 * (i % 3) for i in range(E)] if var_nk else [K] * E
+    ns = [N - 8 * (i % 2) for i in range(E)] if var_nk else [N] * E
+    A = torch.randn(sum(ms), K, generator=g).to(dt)
+    Bs = [(torch.randn(ks[i], ns[i], generator=g) * K ** -0.5).to(dt) for i in range(E)]
+    C = torch.randn(sum(ms), N, generator=g).to(dt)
+    out = torch.full_like(C, float("nan"))
+    Ad, Cd, outd = A.to(DEV), C.to(DEV), out.to(DEV)
+    Bd = [(b.t().contiguous() if nk else b).to(DEV) for b in Bs]
+    es = A.element_size()
+    ap, bp, cp, op, s = [], [], [], [], 0
+    for i, mg in enumerate(ms):
+        ap.append(Ad.data_ptr() + s * K * es)
+        cp.append(Cd.data_ptr() + s * N * es)
+        op.append(outd.data_ptr() + s * N * es)
+        bp.append(Bd[i].data_ptr())
+        s += mg
+    ldb = [ks[i] if nk else ns[i] for i in range(E)]
+    ret = getattr(fb, FN[kind])(outd, _i64(ap), _i64(bp), _i64(cp), _i64(op), _i32(ms), _i32(ns), _i32(ks), _i32([K] * E),
+                                _i32(ldb), _i32([N] * E), E, sum(ms), N, K, alpha, beta)
+    assert ret is outd
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    a_list, b_list, c_list, s = [], [], [], 0
+    for i, mg in enumerate(ms):
+        a_list.append(A[s:s + mg, :ks[i]].float().numpy())
+        b_list.append(Bs[i].float().numpy())
+        c_list.append(C[s:s + mg, :ns[i]].float().numpy())
+        s += mg
+    refs = go.group_gemm(kind, a_list, b_list, c_list, alpha, beta, tf32_mode="trunc")
+    got = outd.float().cpu()
+    s = 0
+    for i, mg in enumerate(ms):
+        if mg:
+            assert_parity(got[s:s + mg, :ns[i]], torch.from_numpy(refs[i]), KINDS[kind][2], abs(alpha) * 1.0 + abs(beta),
+                          "%s group %d m=%d" % (kind, i, mg))
+            if ns[i] < N:   # columns beyond n_g are never written
+                assert torch.isnan(got[s:s + mg, ns[i]:]).all()
+        s += mg
+    return got
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_ragged(kind):
+    _run_group(kind, [5, 0, 70, 33, 300, 128, 129, 1], 512, 384, 1.5, 0.5, seed=1)
+    _run_group(kind, [128, 256], 256, 256, 1.0, 0.0, seed=2)
+    _run_group(kind, [0, 0, 17], 64, 128, 1.0, 0.0, seed=3)
+    _run_group(kind, [40, 200, 64], 200, 136, 1.5, 0.5, seed=4, var_nk=True)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_reference_shapes(kind):
+    """A few of the reference's (k, e, n) grid (tests/accuracy_utils.py:299-330), m_g in [1, 512]."""
+    import random
+    rnd = random.Random(50)
+    for (K, E, N) in [(64, 16, 128), (1024, 32, 512), (2048, 16, 1536)]:
+        ms = [rnd.randint(1, 512) for _ in range(E)]
+        _run_group(kind, ms, K, N, 1.5, 0.5, seed=K)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_alpha_zero_and_beta_zero(kind):
+    got = _run_group(kind, [33, 64], 128, 128, 0.0, 0.5, seed=5)      # out = 0.5 * C
+    assert not torch.isnan(got).any()
+    got = _run_group(kind, [33, 64], 128, 128, 1.0, 0.0, seed=6)      # C pointers never dereferenced
+    assert not torch.isnan(got).any()
+
+
+def test_grouped_many_groups():
+    _run_group("bf16", [((7 * i) % 90) for i in range(600)], 128, 256, 1.0, 0.0, seed=7)
+
+
+def test_group_mm_and_group_gemm():
+    g = torch.Generator().manual_seed(8)
+    for dt, kind in ((torch.float16, "fp16"), (torch.bfloat16, "bf16")):
+        A = torch.randn(432, 256, generator=g).to(dt)
+        B = (torch.randn(4, 256, 320, generator=g) / 16).to(dt)
+        offs = torch.tensor([20, 20, 300, 432], dtype=torch.int32)
+        C = fb.group_mm(A.to(DEV), B.to(DEV), offs.to(DEV))
+        ref = go.group_mm(kind, A.float().numpy(), B.float().numpy(), offs.numpy())
+        assert_parity(C.float().cpu(), torch.from_numpy(ref), 1e-2, 1.0, "group_mm " + kind)
+        # B given as a transposed view ([G, N, K] storage)
+        Bt = B.transpose(1, 2).contiguous().transpose(1, 2)
+        C2 = fb.group_mm(A.to(DEV), Bt.to(DEV), offs.to(DEV))
+        assert_parity(C2.float().cpu(), torch.from_numpy(ref), 1e-2, 1.0, "group_mm K-contiguous B " + kind)
+        # group_gemm: offs_table rows = [m, n, k, start_M, start_K, start_C]
+        ms = [20, 0, 280, 132]
+        table, s = [], 0
+        for i, mg in enumerate(ms):
+            table.append([mg, 320, 256, s, i * 256, s])
+            s += mg
+        Cin = torch.randn(432, 320, generator=g).to(dt)
+        out = fb.group_gemm(A.to(DEV), B.reshape(4 * 256, 320).to(DEV), Cin.to(DEV), table, alpha=1.5, beta=0.5)
+        a_list, c_list, s = [], [], 0
+        for mg in ms:
+            a_list.append(A[s:s + mg].float().numpy()); c_list.append(Cin[s:s + mg].float().numpy()); s += mg
+        refs = go.group_gemm(kind, a_list, [B[i].float().numpy() for i in range(4)], c_list, 1.5, 0.5)
+        assert_parity(out.float().cpu(), torch.from_numpy(np.concatenate(refs, 0)), 1e-2, 2.0, "group_gemm " + kind)
+
+
+def test_golden_grouped_on_gpu(golden_dir):
+    z = np.load(os.path.join(golden_dir, "grouped.npz"))
+    for name, kind in (("h", "fp16"), ("tf32", "tf32")):
+        for tag in ("ab", "b0"):
+            pre = "g%s_%s_" % (name, tag)
+            p = z[pre + "p"]
+            ms = [int(v) for v in p[:4]]
+            K, N, al, be = int(p[4]), int(p[5]), float(p[6]), float(p[7])
+            dt = KINDS[kind][0]
+            nk = kind == "tf32"
+            A = torch.from_numpy(z[pre + "A"]).to(dt).to(DEV)
+            B = torch.from_numpy(z[pre + "B"]).to(dt)
+            Bd = [(B[i * K:(i + 1) * K].t().contiguous() if nk else B[i * K:(i + 1) * K].contiguous()).to(DEV) for i in range(4)]
+            C = torch.from_numpy(z[pre + "C"]).to(dt).to(DEV)
+            out = torch.full_like(C, float("nan"))
+            es = A.element_size()
+            ap, cp, op, s = [], [], [], 0
+            for mg in ms:
+                ap.append(A.data_ptr() + s * K * es); cp.append(C.data_ptr() + s * N * es); op.append(out.data_ptr() + s * N * es); s += mg
+            getattr(fb, FN[kind])(out, _i64(ap), _i64([b.data_ptr() for b in Bd]), _i64(cp), _i64(op), _i32(ms), _i32([N] * 4),
+                                  _i32([K] * 4), _i32([K] * 4), _i32([K if nk else N] * 4), _i32([N] * 4), 4, sum(ms), N, K, al, be)
+            ref = torch.from_numpy(z[pre + "out"])
+            assert_parity(out.float().cpu(), ref, KINDS[kind][2], abs(al) + abs(be), "golden " + pre)
+    A = torch.from_numpy(z["mm_A"]).half().to(DEV)
+    B = torch.from_numpy(z["mm_B"]).half().to(DEV)
+    C = fb.group_mm(A, B, torch.from_numpy(z["mm_offs"]).to(DEV))
+    assert_parity(C.float().cpu()[:108], torch.from_numpy(z["mm_C"])[:108], 1e-2, 8.0, "golden group_mm")
+
+
+def test_moe_config4_properties():
+    """BASELINE config 4 at full size: 64 experts, K=4096, N=1536, Zipf(1.2) token counts (zeros allowed)."""
+    E, K, N, T = 64, 4096, 1536, 32768
+    g = torch.Generator().manual_seed(3)
+    w = torch.arange(1, E + 1, dtype=torch.float64) ** -1.2
+    ms = torch.multinomial(w / w.sum(), T, replacement=True, generator=g).bincount(minlength=E).tolist()
+    gd = torch.Generator(device=DEV).manual_seed(3)
+    A = torch.randn(T, K, generator=gd, device=DEV).bfloat16()
+    B = (torch.randn(E * K, N, generator=gd, device=DEV) * 0.02).bfloat16()
+    out = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ap, bp, op, s = [], [], [], 0
+    for i, mg in enumerate(ms):
+        ap.append(A.data_ptr() + s * K * 2); bp.append(B.data_ptr() + i * K * N * 2); op.append(out.data_ptr() + s * N * 2); s += mg
+    fb.group_bfgemm(out, _i64(ap), _i64(bp), _i64(op), _i64(op), _i32(ms), _i32([N] * E), _i32([K] * E), _i32([K] * E),
+                    _i32([N] * E), _i32([N] * E), E, T, N, K, 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    assert not torch.isnan(out).any()
+    sc = (K ** 0.5) * 0.02
+    s = 0
+    for i, mg in enumerate(ms):
+        if mg:
+            rows = sorted({s, s + mg // 2, s + mg - 1})
+            ref = A[rows].double() @ B[i * K:(i + 1) * K].double()
+            assert_parity(out[rows].float().cpu(), ref.float().cpu(), 1e-2, sc, "moe expert %d" % i)
+        s += mg
+
+
+def test_bounded_wait_reports_timeout():
+    """A wait on a barrier nothing completes gives up after its limit and reports it; the
+    context stays usable afterwards."""
+    assert fb.c_operators.fb_selftest_bounded_wait(20_000_000, None) == 105
+    assert fb.device_status() == 0
+    x = torch.ones(8, device=DEV)
+    assert float(x.sum()) == 8.0
