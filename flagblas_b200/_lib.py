@@ -51,6 +51,8 @@ def _load():
     handle.fb_last_cuda_error.argtypes = []
     handle.fb_sm_count.restype = i32
     handle.fb_sm_count.argtypes = []
+    handle.fb_debug_set_profile_buffer.restype = None
+    handle.fb_debug_set_profile_buffer.argtypes = [vp]
     handle.fb_selftest_bounded_wait.restype = i32
     handle.fb_selftest_bounded_wait.argtypes = [i64, vp]
     return handle
@@ -71,6 +73,7 @@ EXPORTED_SYMBOLS = (
     "fb_last_cuda_error",
     "fb_sm_count",
     "fb_selftest_bounded_wait",
+    "fb_debug_set_profile_buffer",
 )
 
 

@@ -3,10 +3,10 @@
 //   C[m,n] = alpha * op(A)[m,k] * op(B)[k,n] + beta * Cin[m,n]      (row-major)
 //
 // Roles inside a 256-thread CTA
-//   warp 0      : TMA producer  (global -> 128B-swizzled shared memory ring)
+//   warp 0      : TMA producer for A (arms each stage's barrier)
 //   warp 1      : MMA issuer    (one thread, tcgen05.mma into TMEM)
 //   warp 2      : TMEM allocator / deallocator
-//   warp 3      : idle
+//   warp 3      : TMA producer for B
 //   warps 4..7  : epilogue      (tcgen05.ld -> alpha/beta -> cast -> global)
 //
 // The accumulator is double buffered in TMEM (2 x BLOCK_N fp32 columns), so the
@@ -31,14 +31,25 @@ constexpr int kEpiWarp0 = 4;        // first epilogue warp (must be a multiple o
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory
 
 // How one operand's pipeline stage is fetched and described to the MMA.
+//
+// A stage holds `TcGemmParams::ks` k-slabs; a k-slab is the operand tile restricted to the
+// 128 bytes of K that one swizzle row spans (64 16-bit or 32 fp32 elements).
+//   K-major operand : slab = [tile rows][128 B]; slabs of a stage lie one after the other.
+//   MN-major operand: [128-byte chunk of MN][k rows of the whole stage][128 B].
+// With `use3d` one 3-D TMA instruction fetches the operand's whole stage; otherwise
+// `boxes` 2-D boxes per slab do (the fallback when an extent is not a multiple of the
+// slab width, and the grouped path).
 struct OperandGeom {
-  uint32_t boxes;        // TMA boxes per stage
-  uint32_t box_bytes;    // bytes per box
-  uint32_t box_mn_step;  // MN elements between successive boxes (MN-major only)
-  uint32_t mn_major;     // 1: tensor-map x is the MN coordinate; 0: x is K
-  uint32_t lbo, sbo;     // descriptor byte offsets
-  uint32_t k_adv_bytes;  // descriptor start-address advance per MMA K step
-  uint32_t layout;       // descriptor swizzle/layout code (kLayoutSw128 or kLayoutSw128Base32)
+  uint32_t mn_major;      // 1: the operand's contiguous dimension is M (or N), not K
+  uint32_t use3d;         // 1: one 3-D copy per stage
+  uint32_t boxes;         // 2-D path: boxes per k-slab
+  uint32_t box_bytes;     // 2-D path: bytes per box
+  uint32_t box_mn_step;   // 2-D path, MN-major: MN elements between successive boxes
+  uint32_t span;          // elements per 128 bytes
+  uint32_t lbo, sbo;      // descriptor byte offsets
+  uint32_t k_adv_bytes;   // descriptor start-address advance per MMA inside a k-slab
+  uint32_t slab_adv_bytes;  // descriptor start-address advance from one k-slab to the next
+  uint32_t layout;        // descriptor swizzle/layout code (kLayoutSw128 or kLayoutSw128Base32)
 };
 
 // One GEMM problem as the epilogue sees it.
@@ -71,13 +82,19 @@ struct TcGemmParams {
   int group_m;  // grouped-M swizzle width (tiles)
   float alpha, beta;
   uint32_t idesc;
-  uint32_t block_k;  // elements of K per pipeline stage
+  uint32_t block_k;  // elements of K per pipeline stage (= ks slabs)
+  uint32_t ks;       // k-slabs per stage (1 or 2)
   OperandGeom a, b;
   // grouped mode (num_groups > 0): table + per-group tensor maps in global memory
   int num_groups;
   const GroupRec* groups;
   const int* total_tiles;        // device scalar written by the table builder
   const CUtensorMap* group_maps;  // [2 * num_groups]: A_g, B_g
+  // Profiling switches (results are meaningless when set): bit 0 = issue no MMA, bit 1 = issue no TMA copy.
+  int debug;
+  int stages;  // pipeline stages actually used (<= the compiled maximum)
+  // Optional cycle accounting (profiling builds of a call): 16 counters written by CTA 0, or null.
+  long long* prof;
 };
 
 template <int KIND> struct OutOf { using T = float; };
@@ -163,10 +180,18 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   }
 }
 
-template <int KIND, int BLOCK_N>
+// PAIR = true: two CTAs of a cluster work on one 256 x BLOCK_N tile with
+// tcgen05 cta_group::2.  Each CTA fetches its own 128 rows of A and its own half
+// of the B tile into its own shared memory, the leader CTA (cluster rank 0)
+// issues every MMA for both, and each CTA's TMEM ends up with its 128 rows of
+// the accumulator.  Per CTA that is a third less operand traffic and shared
+// memory per K step than a 128 x BLOCK_N tile, so the same shared memory holds a
+// deeper prefetch ring.
+template <int KIND, int BLOCK_N, bool PAIR>
 struct TcCfg {
   static constexpr int kABytes = kBlockM * kSwizzleBytes;
-  static constexpr int kBBytes = BLOCK_N * kSwizzleBytes;
+  static constexpr int kBRows = PAIR ? BLOCK_N / 2 : BLOCK_N;  // B-tile rows this CTA holds
+  static constexpr int kBBytes = kBRows * kSwizzleBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kCtlBytes = 1024;
   static constexpr int kStages = (kSmemLimit - 1024 - kCtlBytes) / kStageBytes > 8
@@ -174,15 +199,16 @@ struct TcCfg {
                                      : (kSmemLimit - 1024 - kCtlBytes) / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kCtlBytes + 1024;
   static constexpr int kTmemCols = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+  static constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;  // rows of C per scheduled tile
 };
 
 // g_fb_status (the device status word) is defined by the including translation unit.
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const TcGemmParams p) {
-  using Cfg = TcCfg<KIND, BLOCK_N>;
+  using Cfg = TcCfg<KIND, BLOCK_N, PAIR>;
   using OutT = typename OutOf<KIND>::T;
   constexpr bool kTf32 = (KIND == 2);
   constexpr int kStages = Cfg::kStages;
@@ -205,16 +231,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const WaitCtl wctl{abort_flag, &g_fb_status};
   const bool grouped = p.num_groups > 0;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&full_bar[s], 1);   // the (leader's) producer arrival + transaction bytes
+      mbar_init(&empty_bar[s], 1);  // one tcgen05.commit arrival
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], 4);
+      mbar_init(&tmem_empty_bar[a], PAIR ? 8 : 4);  // epilogue warps of every CTA that reads this accumulator
     }
     fence_mbar_init();
     if (!grouped) {
@@ -223,27 +252,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
   if (warp == 2) {
-    tmem_alloc(tmem_holder, Cfg::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_holder, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_holder, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) {
+    // barriers of both CTAs must be initialised before either touches the other's
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == 3) {
+    // ----------------------------------------------------------- TMA producers
+    // Two issuing threads so that the copies of one stage are not serialised behind each
+    // other: warp 0 arms the stage's barrier and fetches A, warp 3 fetches B.
     if (lane == 0) {
+      const bool load_a = warp == 0;
+      const OperandGeom& og = load_a ? p.a : p.b;
       int stage = 0;
       uint32_t phase = 0;
       int g = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      long long prof_wait = 0, prof_issue = 0;
+      for (int t = worker; t < num_tiles && ok; t += num_workers) {
         int tm, tn, kk_total;
-        const CUtensorMap* ma = &tmA;
-        const CUtensorMap* mb = &tmB;
+        const CUtensorMap* map = load_a ? &tmA : &tmB;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           const GroupRec& gr = p.groups[g];
@@ -251,74 +295,152 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tm = lt / gr.tiles_n;
           tn = lt - tm * gr.tiles_n;
           kk_total = gr.k;
-          ma = &p.group_maps[2 * g];
-          mb = &p.group_maps[2 * g + 1];
-          fence_tensormap_acquire(ma);
-          fence_tensormap_acquire(mb);
+          map = &p.group_maps[2 * g + (load_a ? 0 : 1)];
+          fence_tensormap_acquire(map);
         } else {
           swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
           kk_total = p.k;
         }
-        const int m0 = tm * kBlockM, n0 = tn * BLOCK_N;
+        // first row (A) / first column (B) of the operand slab this CTA fetches
+        const int mn0 = load_a ? tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
+                               : tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const long long c0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const long long c1 = p.prof ? clock64() : 0;
+          prof_wait += c1 - c0;
           const int k0 = kb * static_cast<int>(p.block_k);
-          uint8_t* sa = smem_a + stage * Cfg::kABytes;
-          uint8_t* sb = smem_b + stage * Cfg::kBBytes;
-          for (uint32_t bx = 0; bx < p.a.boxes; ++bx) {
-            if (p.a.mn_major) tma_load_2d(sa + bx * p.a.box_bytes, ma, &full_bar[stage], m0 + bx * p.a.box_mn_step, k0);
-            else tma_load_2d(sa, ma, &full_bar[stage], k0, m0);
+          const uint32_t a_stage_bytes = p.ks * Cfg::kABytes, b_stage_bytes = p.ks * Cfg::kBBytes;
+          uint8_t* dst = load_a ? smem_a + stage * a_stage_bytes : smem_b + stage * b_stage_bytes;
+          const uint32_t slab_bytes = load_a ? Cfg::kABytes : Cfg::kBBytes;
+          uint32_t bar = smem_u32(&full_bar[stage]);
+          if constexpr (PAIR) bar = mapa_shared(bar, 0);  // both CTAs' copies are credited to the leader's barrier
+          if (load_a && cta_rank == 0) {
+            if (p.debug & 2) mbar_arrive(&full_bar[stage]);
+            else mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (a_stage_bytes + b_stage_bytes));
           }
-          for (uint32_t bx = 0; bx < p.b.boxes; ++bx) {
-            if (p.b.mn_major) tma_load_2d(sb + bx * p.b.box_bytes, mb, &full_bar[stage], n0 + bx * p.b.box_mn_step, k0);
-            else tma_load_2d(sb, mb, &full_bar[stage], k0, n0);
+          if (!(p.debug & 2)) {
+            if (og.use3d) {
+              // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row
+              const int y = og.mn_major ? k0 : mn0;
+              const int z = og.mn_major ? mn0 / static_cast<int>(og.span) : k0 / static_cast<int>(og.span);
+              if constexpr (PAIR) tma_load_3d_pair(dst, map, bar, 0, y, z);
+              else tma_load_3d(dst, map, &full_bar[stage], 0, y, z);
+            } else {
+              for (uint32_t sl = 0; sl < p.ks; ++sl) {
+                const int ks0 = k0 + static_cast<int>(sl * og.span);
+                for (uint32_t bx = 0; bx < og.boxes; ++bx) {
+                  uint8_t* d = dst + sl * slab_bytes + bx * og.box_bytes;
+                  const int x = og.mn_major ? mn0 + static_cast<int>(bx * og.box_mn_step) : ks0;
+                  const int y = og.mn_major ? ks0 : mn0;
+                  if constexpr (PAIR) tma_load_2d_pair(d, map, bar, x, y);
+                  else tma_load_2d(d, map, &full_bar[stage], x, y);
+                }
+              }
+            }
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (p.prof) prof_issue += clock64() - c1;
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
+      }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[load_a ? 0 : 9] = prof_wait;
+        p.prof[load_a ? 1 : 10] = prof_issue;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The tensor pipe queues next to nothing: issuing an MMA blocks until the pipe takes it, and
+    // whatever the issuing thread does between two issues that lasts longer than one MMA leaves the
+    // pipe idle.  So this loop is software-pipelined: the bookkeeping of a stage (releasing the
+    // stage, probing the next stage's barrier, building its descriptors) is slotted
+    // *between* the MMAs of the current stage, and the last MMA of one stage is followed
+    // directly by the first MMA of the next.
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       int g = 0;
       bool ok = true;
-      const int mma_per_stage = kSwizzleBytes / 32;  // 32 bytes of K per MMA for every dtype
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      constexpr int kMaxMma = 8;  // 4 per k-slab, at most 2 slabs per stage
+      const int n_mma = 4 * static_cast<int>(p.ks);
+      uint32_t off_a[kMaxMma], off_b[kMaxMma];  // descriptor start-address offsets (16-byte units) of each MMA of a stage
+#pragma unroll
+      for (int j = 0; j < kMaxMma; ++j) {
+        off_a[j] = ((j >> 2) * p.a.slab_adv_bytes + (j & 3) * p.a.k_adv_bytes) >> 4;
+        off_b[j] = ((j >> 2) * p.b.slab_adv_bytes + (j & 3) * p.b.k_adv_bytes) >> 4;
+      }
+      const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a), p.a.lbo, p.a.sbo, p.a.layout);
+      const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b), p.b.lbo, p.b.sbo, p.b.layout);
+      const uint32_t a_stage_units = (p.ks * Cfg::kABytes) >> 4, b_stage_units = (p.ks * Cfg::kBBytes) >> 4;
+      long long prof_wfull = 0, prof_wtmem = 0;
+      const long long cstart = p.prof ? clock64() : 0;
+      unsigned long long gstart = 0;
+      if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gstart));
+      bool data_ready = false;   // the current stage's barrier was already seen complete
+      for (int t = worker; t < num_tiles && ok; t += num_workers) {
         int kk_total = p.k;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           kk_total = p.groups[g].k;
         }
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, wctl, DEV_TIMEOUT_MMA_TMEM_EMPTY)) { ok = false; break; }
+        // PAIR: the peer's epilogue warps arrive remotely -> cluster-scope acquire
+        if (!mbar_test_wait(&tmem_empty_bar[acc], acc_phase ^ 1u) || PAIR) {
+          const long long ct0 = p.prof ? clock64() : 0;
+          if (!mbar_wait<PAIR>(&tmem_empty_bar[acc], acc_phase ^ 1u, wctl, DEV_TIMEOUT_MMA_TMEM_EMPTY)) { ok = false; break; }
+          if (p.prof) prof_wtmem += clock64() - ct0;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, wctl, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kABytes);
-          const uint32_t b_addr = smem_u32(smem_b + stage * Cfg::kBBytes);
-          const uint64_t a_desc = make_smem_desc(a_addr, p.a.lbo, p.a.sbo, p.a.layout);
-          const uint64_t b_desc = make_smem_desc(b_addr, p.b.lbo, p.b.sbo, p.b.layout);
-#pragma unroll
-          for (int kk = 0; kk < mma_per_stage; ++kk) {
-            umma<kTf32>(d_tmem, a_desc + ((kk * p.a.k_adv_bytes) >> 4), b_desc + ((kk * p.b.k_adv_bytes) >> 4),
-                        p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          if (!data_ready) {
+            const long long c0 = p.prof ? clock64() : 0;
+            if (!mbar_wait(&full_bar[stage], phase, wctl, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+            if (p.prof) prof_wfull += clock64() - c0;
           }
-          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          tc_fence_after();
+          const uint64_t a_desc = a_desc0 + static_cast<uint32_t>(stage) * a_stage_units;
+          const uint64_t b_desc = b_desc0 + static_cast<uint32_t>(stage) * b_stage_units;
+          int next_stage = stage + 1;
+          uint32_t next_phase = phase;
+          if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1u; }
+#pragma unroll
+          for (int j = 0; j < kMaxMma; ++j) {
+            if (j < n_mma) {
+              if (!(p.debug & 1)) {
+                const uint32_t accum = (kb | j) != 0 ? 1u : 0u;
+                if constexpr (PAIR) umma_pair<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
+                else umma<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
+              }
+              if (j == n_mma - 2) data_ready = mbar_test_wait(&full_bar[next_stage], next_phase);
+              if (j == n_mma - 1) {
+                // Release the stage (in both CTAs of a pair) as soon as its last MMA is queued: the
+                // commit is cheap to issue and the next stage's first MMA follows immediately.
+                if constexpr (PAIR) umma_commit_pair(&empty_bar[stage], 3);
+                else umma_commit(&empty_bar[stage]);
+              }
+            }
+          }
+          stage = next_stage;
+          phase = next_phase;
         }
         if (!ok) break;
-        umma_commit(&tmem_full_bar[acc]);  // accumulator complete -> epilogue
+        // Tile done: publish the accumulator to the epilogue (of both CTAs of a pair).
+        if constexpr (PAIR) umma_commit_pair(&tmem_full_bar[acc], 3);
+        else umma_commit(&tmem_full_bar[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[2] = prof_wfull; p.prof[5] = prof_wtmem;
+        p.prof[6] = clock64() - cstart;
+        unsigned long long gend;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gend));
+        p.prof[11] = static_cast<long long>(gend - gstart);  // the same interval in nanoseconds
       }
     }
     __syncwarp();
@@ -329,7 +451,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t acc_phase = 0;
     int g = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    long long prof_ewait = 0, prof_ebody = 0;
+    for (int t = worker; t < num_tiles && ok; t += num_workers) {
       int tm, tn;
       Problem pr;
       bool k_is_zero = false;  // a group with k == 0 contributes beta * C only
@@ -346,13 +469,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         pr = p.prob;
       }
+      const long long e0 = p.prof ? clock64() : 0;
       // warp-uniform outcome: tcgen05.ld below needs the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, wctl, DEV_TIMEOUT_EPI_TMEM_FULL))) {
+      if (!mbar_wait_warp<64>(&tmem_full_bar[acc], acc_phase, wctl, DEV_TIMEOUT_EPI_TMEM_FULL)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row = tm * kBlockM + lane_group * 32 + lane;
+      const long long e1 = p.prof ? clock64() : 0;
+      prof_ewait += e1 - e0;
+      const int row = tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
@@ -365,16 +491,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
         if (c == BLOCK_N / 32 - 1) {
-          // every column of this accumulator is in registers: hand TMEM back
+          // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+            else mbar_arrive(&tmem_empty_bar[acc]);
+          }
         }
-        epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
+        if (!(p.debug & 4)) epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
       }
+      if (p.prof) prof_ebody += clock64() - e1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) { p.prof[7] = prof_ewait; p.prof[8] = prof_ebody; }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -386,9 +517,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (PAIR) {
+    // Neither CTA may retire while its partner can still signal its barriers or read its operands.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 

@@ -83,6 +83,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster_acq(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -102,8 +114,11 @@ struct WaitCtl {
 };
 
 // Bounded wait.  Returns true when the phase completed, false when the CTA is
-// aborting (this wait or another one ran out of time).
-template <bool kClusterAcquire = false>
+// aborting (this wait or another one ran out of time).  kBackoffNs > 0 sleeps
+// between polls: for waiters that are not on the critical path (they would
+// otherwise compete with the producer and MMA threads for issue slots and
+// shared-memory bandwidth while they spin).
+template <bool kClusterAcquire = false, int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
   auto probe = [&]() {
     if constexpr (kClusterAcquire) return mbar_try_wait_cluster_acq(bar, parity);
@@ -113,6 +128,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   uint32_t it = 0;
   while (true) {
+    if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     if (probe()) return true;
     if (((++it) & 0xffu) == 0) {
       if (*ctl.abort_flag) return false;
@@ -123,6 +139,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       }
     }
   }
+}
+
+// Whole-warp wait in which only lane 0 polls; the outcome is broadcast.
+template <int kBackoffNs>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait<false, kBackoffNs>(bar, parity, ctl, code) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 
 // ----------------------------------------------------------------------- TMA
@@ -148,6 +173,23 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tma
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 3-D variants (one instruction fetches several 128-byte-wide slabs of a tile).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 

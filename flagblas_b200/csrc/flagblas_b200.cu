@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fb {
@@ -19,6 +20,8 @@ __device__ int g_fb_status = 0;
 namespace fb {
 
 static thread_local int t_last_cuda_error = 0;
+// Device buffer of 16 cycle counters, set by fb_debug_set_profile_buffer (profiling only).
+static long long* g_prof_buffer = nullptr;
 
 #define FB_CUDA_OK(expr)                                   \
   do {                                                     \
@@ -98,20 +101,43 @@ static int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inn
   return FB_OK;
 }
 
+// 3-D view used to fetch several 128-byte-wide slabs with one copy: extents {d0, d1, d2} with d0
+// contiguous, byte strides {s1, s2} for d1 and d2.
+static int encode_3d(CUtensorMap* map, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                     uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool atom32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FB_ERR_DRIVER;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, map_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    t_last_cuda_error = static_cast<int>(r);
+    return FB_ERR_DRIVER;
+  }
+  return FB_OK;
+}
+
 // Geometry of one operand's pipeline stage.  `tile_mn` rows/cols of the tile,
 // `mn_contig`: the operand's contiguous dimension is M (resp. N), not K.
-static OperandGeom make_geom(int esz, int tile_mn, bool mn_contig) {
+static OperandGeom make_geom(int esz, int tile_mn, bool mn_contig, int ks, bool use3d) {
   OperandGeom g{};
   const uint32_t span = kSwizzleBytes / esz;  // elements per 128-byte row
-  const uint32_t block_k = span;
+  g.span = span;
+  g.use3d = use3d ? 1 : 0;
   if (mn_contig) {
+    const uint32_t k_rows = span * ks;  // k rows per 128-byte chunk of MN in one stage
     g.mn_major = 1;
     g.boxes = tile_mn / span;
-    g.box_bytes = block_k * kSwizzleBytes;
+    g.box_bytes = k_rows * kSwizzleBytes;
     g.box_mn_step = span;
-    g.lbo = block_k * kSwizzleBytes;  // next 128-byte chunk of MN = next box
+    g.lbo = k_rows * kSwizzleBytes;              // next 128-byte chunk of MN
     g.sbo = (esz == 4 ? 4 : 8) * kSwizzleBytes;  // next group of k-rows (4 with 32-byte atoms, else 8)
     g.k_adv_bytes = (32 / esz) * kSwizzleBytes;  // one MMA consumes 32 bytes' worth of K = that many rows
+    g.slab_adv_bytes = span * kSwizzleBytes;     // k rows simply continue
     g.layout = esz == 4 ? kLayoutSw128Base32 : kLayoutSw128;
   } else {
     g.mn_major = 0;
@@ -121,6 +147,7 @@ static OperandGeom make_geom(int esz, int tile_mn, bool mn_contig) {
     g.lbo = 16;
     g.sbo = 8 * kSwizzleBytes;  // next group of 8 rows
     g.k_adv_bytes = 32;
+    g.slab_adv_bytes = tile_mn * kSwizzleBytes;  // slabs are stacked tile after tile
     g.layout = kLayoutSw128;
   }
   return g;
@@ -175,45 +202,100 @@ __global__ void bounded_wait_selftest_kernel(long long limit) {
 }
 
 // ------------------------------------------------------------- tile choice
-static int choose_block_n(long long m, long long n, int sms) {
-  const long long tm = (m + kBlockM - 1) / kBlockM;
+// Pick the tile width that minimises (waves x per-tile time); `workers` = CTAs (or CTA pairs)
+// that run concurrently, `tile_m` = rows per tile.
+static int choose_block_n(long long m, long long n, int tile_m, int workers, bool allow64) {
+  const long long tm = (m + tile_m - 1) / tile_m;
   double best = 1e300;
   int best_bn = 256;
   const int cand[3] = {256, 128, 64};
   const double eff[3] = {1.0, 0.88, 0.62};  // relative main-loop efficiency of the narrower tiles
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < (allow64 ? 3 : 2); ++i) {
     const long long tiles = tm * ((n + cand[i] - 1) / cand[i]);
-    const long long waves = (tiles + sms - 1) / sms;
+    const long long waves = (tiles + workers - 1) / workers;
     const double cost = static_cast<double>(waves) * cand[i] / eff[i];
     if (cost < best) { best = cost; best_bn = cand[i]; }
   }
   return best_bn;
 }
 
-template <int KIND, int BLOCK_N>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, int grid,
-                     cudaStream_t stream) {
-  using Cfg = TcCfg<KIND, BLOCK_N>;
-  auto kern = gemm_tc_kernel<KIND, BLOCK_N>;
-  static bool attr_set[64] = {};
+static int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+// Launch state kept per kernel instantiation and device.
+struct KernelState {
+  bool attr_set = false;
+  int max_clusters = 0;  // PAIR only: CTA pairs that can be co-resident
+};
+
+template <int KIND, int BLOCK_N, bool PAIR>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, long long tiles,
+                     int sm_count, cudaStream_t stream) {
+  using Cfg = TcCfg<KIND, BLOCK_N, PAIR>;
+  auto kern = gemm_tc_kernel<KIND, BLOCK_N, PAIR>;
+  static KernelState state[64];
+  static std::mutex mu;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev]) {
-    FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set[dev] = true;
+  KernelState& st = state[dev];
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!st.attr_set) {
+      FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      if (PAIR) {
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2));
+        q.blockDim = dim3(kNumThreads);
+        q.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+        q.attrs = qa; q.numAttrs = 1;
+        int n = 0;
+        FB_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, kern, &q));
+        st.max_clusters = n > 0 ? n : 1;
+      }
+      st.attr_set = true;
+    }
   }
-  kern<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
-  FB_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attrs[1];
+  const long long workers = PAIR ? st.max_clusters : sm_count;
+  const long long use = tiles < workers ? tiles : workers;
+  cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * use : use));
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  if (PAIR) {
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 1;
+  }
+  TcGemmParams pp = p;
+  pp.debug = env_int("FLAGBLAS_B200_DEBUG_SKIP", 0);
+  const int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
+  pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
+  if (pp.stages < 1 || pp.stages > max_stages) pp.stages = max_stages;
+  pp.prof = g_prof_buffer;
+  FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, pp));
   return FB_OK;
 }
 
-static int dispatch_tc(int dtype, int block_n, const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p,
-                       int grid, cudaStream_t stream) {
-#define FB_CASE(KIND)                                                           \
-  switch (block_n) {                                                            \
-    case 256: return launch_tc<KIND, 256>(ma, mb, p, grid, stream);             \
-    case 128: return launch_tc<KIND, 128>(ma, mb, p, grid, stream);             \
-    default: return launch_tc<KIND, 64>(ma, mb, p, grid, stream);               \
+// tiles < 0: grouped mode, the tile count lives on the device -> one worker per SM.
+static int dispatch_tc(int dtype, int block_n, bool pair, const CUtensorMap& ma, const CUtensorMap& mb,
+                       const TcGemmParams& p, long long tiles, int sm_count, cudaStream_t stream) {
+  if (tiles < 0) tiles = 1LL << 40;
+#define FB_CASE(KIND)                                                                              \
+  if (pair) {                                                                                      \
+    if (block_n == 256) return launch_tc<KIND, 256, true>(ma, mb, p, tiles, sm_count, stream);     \
+    return launch_tc<KIND, 128, true>(ma, mb, p, tiles, sm_count, stream);                         \
+  }                                                                                                \
+  switch (block_n) {                                                                               \
+    case 256: return launch_tc<KIND, 256, false>(ma, mb, p, tiles, sm_count, stream);              \
+    case 128: return launch_tc<KIND, 128, false>(ma, mb, p, tiles, sm_count, stream);              \
+    default: return launch_tc<KIND, 64, false>(ma, mb, p, tiles, sm_count, stream);                \
   }
   if (dtype == FB_F16) { FB_CASE(0) }
   if (dtype == FB_BF16) { FB_CASE(1) }
@@ -362,19 +444,57 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     }
   }
 
-  const int block_n = choose_block_n(m, n, di->sm_count);
+  // CTA pairs (256-row tiles) whenever there is more than one 128-row block of C;
+  // FLAGBLAS_B200_PAIR=0/1 and FLAGBLAS_B200_BLOCK_N override the choice (profiling sweeps).
+  bool pair = m > kBlockM;
+  const int force_pair = env_int("FLAGBLAS_B200_PAIR", -1);
+  if (force_pair == 0) pair = false;
+  if (force_pair == 1) pair = true;
+  const int tile_m = pair ? 2 * kBlockM : kBlockM;
+  int block_n = choose_block_n(m, n, tile_m, pair ? di->sm_count / 2 : di->sm_count, !pair);
+  const int force_bn = env_int("FLAGBLAS_B200_BLOCK_N", 0);
+  if (force_bn == 256 || force_bn == 128 || (force_bn == 64 && !pair)) block_n = force_bn;
+  const int b_rows = pair ? block_n / 2 : block_n;  // rows of the B tile each CTA fetches
   const uint32_t span = kSwizzleBytes / esz;
   const bool a_mn = transa == FB_OP_T;  // stored [k, m]: M contiguous
   const bool b_mn = transb == FB_OP_N;  // stored [k, n]: N contiguous
 
+  // One 3-D copy per operand and stage where the operand's extents allow it (the 3-D view's
+  // innermost extent is a full 128-byte row, so the dimension it tiles must be a multiple of
+  // `span`); then a stage can also hold two k-slabs, which halves barrier traffic and lets each
+  // copy instruction move twice the bytes.
+  const bool a3d = (a_mn ? (m % span == 0) : (k % span == 0)) && env_int("FLAGBLAS_B200_TMA3D", 1) != 0;
+  const bool b3d = (b_mn ? (n % span == 0) : (k % span == 0)) && env_int("FLAGBLAS_B200_TMA3D", 1) != 0;
+  int ks = (a3d && b3d && k > static_cast<long long>(span)) ? 2 : 1;
+  const int force_ks = env_int("FLAGBLAS_B200_KS", 0);
+  if (force_ks == 1 || (force_ks == 2 && a3d && b3d)) ks = force_ks;
+
   CUtensorMap ma, mb;
-  int rc;
   const bool atom32 = esz == 4;  // MN-major fp32 operands use the 32-byte-atom swizzle
-  if (a_mn) rc = encode_2d(&ma, dtype, A, m, k, lda * esz, span, span, atom32);
-  else rc = encode_2d(&ma, dtype, A, k, m, lda * esz, span, kBlockM);
-  if (rc) return rc;
-  if (b_mn) rc = encode_2d(&mb, dtype, B, n, k, ldb * esz, span, span, atom32);
-  else rc = encode_2d(&mb, dtype, B, k, n, ldb * esz, span, block_n);
+  const uint64_t kslabs = (static_cast<uint64_t>(k) + span - 1) / span;
+  auto encode_maps = [&](bool a3, bool b3, int nks) -> int {
+    int rc;
+    if (a3) {
+      if (a_mn) rc = encode_3d(&ma, dtype, A, span, k, m / span, lda * esz, kSwizzleBytes, span, span * nks, kBlockM / span, atom32);
+      else rc = encode_3d(&ma, dtype, A, span, m, kslabs, lda * esz, kSwizzleBytes, span, kBlockM, nks, false);
+    } else if (a_mn) rc = encode_2d(&ma, dtype, A, m, k, lda * esz, span, span, atom32);
+    else rc = encode_2d(&ma, dtype, A, k, m, lda * esz, span, kBlockM);
+    if (rc) return rc;
+    if (b3) {
+      if (b_mn) rc = encode_3d(&mb, dtype, B, span, k, n / span, ldb * esz, kSwizzleBytes, span, span * nks, b_rows / span, atom32);
+      else rc = encode_3d(&mb, dtype, B, span, n, kslabs, ldb * esz, kSwizzleBytes, span, b_rows, nks, false);
+    } else if (b_mn) rc = encode_2d(&mb, dtype, B, n, k, ldb * esz, span, span, atom32);
+    else rc = encode_2d(&mb, dtype, B, k, n, ldb * esz, span, b_rows);
+    return rc;
+  };
+  bool use_a3d = a3d, use_b3d = b3d;
+  int rc = encode_maps(use_a3d, use_b3d, ks);
+  if (rc && (use_a3d || use_b3d)) {
+    // the driver refused a 3-D view: fall back to plain 2-D boxes, one k-slab per stage
+    use_a3d = use_b3d = false;
+    ks = 1;
+    rc = encode_maps(false, false, 1);
+  }
   if (rc) return rc;
 
   TcGemmParams p{};
@@ -382,18 +502,19 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.prob.out = C; p.prob.ldo = ldc; p.prob.cin = C; p.prob.ldcin = ldc;
   p.prob.vec_ok = aligned16(C, ldc, esz) ? 1 : 0;
   p.k = static_cast<int>(k);
-  p.tiles_m = static_cast<int>((m + kBlockM - 1) / kBlockM);
+  p.tiles_m = static_cast<int>((m + tile_m - 1) / tile_m);
   p.tiles_n = static_cast<int>((n + block_n - 1) / block_n);
-  p.group_m = 16;
+  p.group_m = env_int("FLAGBLAS_B200_GROUP_M", pair ? 8 : 16);
+  if (p.group_m < 1) p.group_m = 1;
   p.alpha = alpha; p.beta = beta;
-  p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, kBlockM, block_n);
-  p.block_k = span;
-  p.a = make_geom(esz, kBlockM, a_mn);
-  p.b = make_geom(esz, block_n, b_mn);
+  p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n);
+  p.block_k = span * ks;
+  p.ks = ks;
+  p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
+  p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  const int grid = static_cast<int>(tiles < di->sm_count ? tiles : di->sm_count);
-  return dispatch_tc(dtype, block_n, ma, mb, p, grid, stream);
+  return dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
 }
 
 size_t fb_group_workspace_bytes(int group_count) {
@@ -438,13 +559,14 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   p.alpha = alpha; p.beta = beta;
   p.idesc = make_idesc(idesc_fmt(dtype), 0, b_k_contig ? 0 : 1, kBlockM, block_n);
   p.block_k = span;
-  p.a = make_geom(esz, kBlockM, false);
-  p.b = make_geom(esz, block_n, !b_k_contig);
+  p.ks = 1;
+  p.a = make_geom(esz, kBlockM, false, 1, false);
+  p.b = make_geom(esz, block_n, !b_k_contig, 1, false);
   p.num_groups = G;
   p.groups = ga.recs;
   p.total_tiles = ga.total_tiles;
   p.group_maps = ga.maps;
-  return dispatch_tc(dtype, block_n, ta, tb, p, di->sm_count, stream);
+  return dispatch_tc(dtype, block_n, /*pair=*/false, ta, tb, p, /*tiles=*/-1, di->sm_count, stream);
 }
 
 int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
@@ -524,6 +646,10 @@ int fb_device_status(int reset) {
 }
 
 int fb_last_cuda_error(void) { return t_last_cuda_error; }
+
+void fb_debug_set_profile_buffer(void* device_buffer_16_int64) {
+  g_prof_buffer = static_cast<long long*>(device_buffer_16_int64);
+}
 
 int fb_sm_count(void) {
   const DeviceInfo* di = device_info();

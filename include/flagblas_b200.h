@@ -136,6 +136,15 @@ int fb_device_status(int reset);
 /* cudaError_t (as int) of the last failed CUDA call made by this library on this thread. */
 int fb_last_cuda_error(void);
 
+/*
+ * Profiling aid: when set to a device buffer of 16 int64, CTA 0 of every tensor-core GEMM launched
+ * afterwards adds up SM cycles spent per role and phase (producer: [0] waiting for a free stage,
+ * [1] issuing copies; MMA issuer: [2] waiting for data, [3] issuing MMAs, [4] committing,
+ * [5] waiting for a free accumulator, [6] total; epilogue: [7] waiting, [8] draining) and stores
+ * them there.  NULL (the default) switches the accounting off.  Not thread safe.
+ */
+void fb_debug_set_profile_buffer(void* device_buffer_16_int64);
+
 /* Number of SMs the persistent kernels size their grids with on the current device. */
 int fb_sm_count(void);
 

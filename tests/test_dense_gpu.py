@@ -32,10 +32,14 @@ def _run(kind, ta, tb, m, n, k, alpha, beta, pad=0, seed=0, scale=1.0, c_nan=Fal
     what = "%s ta=%d tb=%d %dx%dx%d a=%g b=%g pad=%d" % (kind, ta, tb, m, n, k, alpha, beta, pad)
     assert_parity(got, ref, KINDS[kind][2], sc, what)
     if kind == "tf32":
-        # The tensor core truncates fp32 operands to TF32; the reference's Triton lowering rounds
-        # them to nearest (cvt.rna).  The two stay within the same 1e-3 bound of each other.
+        # The tensor core TRUNCATES fp32 operands to TF32 (measured: results match a truncating
+        # oracle to ~3e-5); a register-operand lowering that rounds to nearest (cvt.rna) differs by a
+        # systematic ~7e-4 relative shrink of every product plus zero-mean noise.  Against such an
+        # oracle the relative term stays 1e-3 but the absolute term needs 1e-2 of the typical
+        # magnitude (tail of the noise over tens of thousands of elements, short k).
         ref_rna = oracle_dense(kind, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, tf32_mode="rna")
-        assert_parity(got, ref_rna, KINDS[kind][2], sc, what + " (vs round-to-nearest inputs)")
+        d = torch.nan_to_num((got.double() - ref_rna.double()).abs(), nan=0.0)  # NaNs: untouched padding of C
+        assert bool((d <= 1e-2 * sc + 1e-3 * torch.nan_to_num(ref_rna.double().abs(), nan=0.0)).all()), what + " (vs round-to-nearest inputs)"
     return got, ref
 
 
@@ -212,8 +216,8 @@ def test_full_size_properties(cfg):
     assert fb.device_status() == 0
     assert not torch.isnan(C).any()
     # (1) sampled rows and columns against fp64 on the host
-    rows = torch.tensor(sorted({0, 1, 127, 128, m // 2 + 3, m - 1}), device=DEV)
-    cols = torch.tensor(sorted({0, 255, 256, n // 2 + 5, n - 1}), device=DEV)
+    rows = torch.tensor(sorted(r for r in {0, 1, 127, 128, m // 2 + 3, m - 1} if r < m), device=DEV)
+    cols = torch.tensor(sorted(c for c in {0, 255, 256, n // 2 + 5, n - 1} if c < n), device=DEV)
     opA = (A.t() if ta else A)
     opB = (B.t() if tb else B)
     if kind == "tf32":
@@ -227,12 +231,13 @@ def test_full_size_properties(cfg):
         ref_cols += beta * C0[:, cols].double().cpu()
     assert_parity(C[rows].float().cpu(), ref_rows.float(), rtol, sc, cfg + " rows")
     assert_parity(C[:, cols].float().cpu(), ref_cols.float(), rtol, sc, cfg + " cols")
-    # (2) linearity: doubling alpha (beta = 0) doubles the result exactly (power-of-two scaling)
+    # (2) linearity: doubling alpha (beta = 0) doubles the result -- exactly for normal numbers
+    # (power-of-two scaling commutes with rounding); fp16 subnormals may differ by one step (2^-24)
     C1 = torch.empty_like(C)
     C2 = torch.empty_like(C)
     op(ta, tb, m, n, k, 1.0, A, A.shape[1], B, B.shape[1], 0.0, C1, n)
     op(ta, tb, m, n, k, 2.0, A, A.shape[1], B, B.shape[1], 0.0, C2, n)
-    assert torch.equal(C1.float() * 2.0, C2.float())
+    assert float((C1.float() * 2.0 - C2.float()).abs().max()) <= (2.0 ** -23 if kind == "fp16" else 0.0)
     # (3) independent cross-check of the whole result: cuBLAS through torch on the same data
     if m * n <= 8192 * 8192:
         refc = _cublas(kind, ta, tb, A, B)
