@@ -39,6 +39,10 @@ def _load():
     handle.fb_gemm_workspace_bytes.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64]
     handle.fb_group_gemm.restype = i32
     handle.fb_group_gemm.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp, sz, vp]
+    handle.fb_group_gemm_no_alloc.restype = i32
+    handle.fb_group_gemm_no_alloc.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp]
+    handle.fb_no_alloc_max_groups.restype = i32
+    handle.fb_no_alloc_max_groups.argtypes = []
     handle.fb_group_mm.restype = i32
     handle.fb_group_mm.argtypes = [i32, i32, vp, i64, vp, i64, i64, vp, i64, vp, i32, i64, i64, vp, sz, vp]
     handle.fb_group_workspace_bytes.restype = sz
@@ -67,6 +71,8 @@ EXPORTED_SYMBOLS = (
     "fb_gemm_workspace_bytes",
     "fb_group_gemm",
     "fb_group_mm",
+    "fb_group_gemm_no_alloc",
+    "fb_no_alloc_max_groups",
     "fb_group_workspace_bytes",
     "fb_status_string",
     "fb_device_status",

@@ -18,7 +18,6 @@ _DEPS = [
     os.path.join(_HERE, "csrc", "fb_gemm_tc.cuh"),
     os.path.join(_HERE, "csrc", "fb_group_setup.cuh"),
     os.path.join(_HERE, "csrc", "fb_sgemm_simt.cuh"),
-    os.path.join(_HERE, "csrc", "fb_no_alloc.cuh"),
     os.path.join(os.path.dirname(_HERE), "include", "flagblas_b200.h"),
 ]
 

@@ -614,6 +614,57 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
                      static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------------------
+// Grouped GEMM for callers that must not allocate.
+//
+// fb_group_gemm needs a little device scratch per call (the tile table and the per-group tensor
+// maps that its set-up kernel writes).  Normally the caller passes that in.  Some callers cannot:
+// code running inside another runtime's "enqueue" hook whose contract forbids allocation, and
+// processes that have already handed every byte of HBM to their own memory pool, where a
+// cudaMalloc would fail or stall the device.  For them the scratch lives here, in a fixed
+// array that is part of the library image: every GPU that loads the library carries these
+// bytes until the process exits, which is why the capacity is kept small.
+constexpr int kNoAllocMaxGroups = 256;
+constexpr size_t kNoAllocScratchBytes =
+    ((sizeof(GroupRec) * kNoAllocMaxGroups + 255) / 256) * 256 + 256 + sizeof(CUtensorMap) * 2 * kNoAllocMaxGroups;
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[kNoAllocScratchBytes];
+
+// In host code `g_no_alloc_scratch` is only a handle for the runtime, not an address a kernel can
+// use; the device address is looked up once per device and cached here.
+static void* g_no_alloc_ptr[64] = {};
+static std::mutex g_no_alloc_mu;
+
+static int no_alloc_scratch(void** out) {
+  int dev = 0;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_no_alloc_mu);
+  if (!g_no_alloc_ptr[dev]) {
+    void* p = nullptr;
+    FB_CUDA_OK(cudaGetSymbolAddress(&p, g_no_alloc_scratch));  // address on the current device
+    g_no_alloc_ptr[dev] = p;
+  }
+  *out = g_no_alloc_ptr[dev];
+  return FB_OK;
+}
+
+int fb_group_gemm_no_alloc(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                           const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                           const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count,
+                           int64_t m_hint, int64_t n_hint, int64_t k_hint, float alpha, float beta, void* stream) {
+  if (group_count > kNoAllocMaxGroups) return FB_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = no_alloc_scratch(&scratch);
+  if (rc) return rc;
+  // Same set-up kernel, same GEMM kernel, same arithmetic as fb_group_gemm; only the scratch differs.
+  // The set-up kernel rewrites every record, map and the tile count it later reads, so nothing in the
+  // array has to be cleared between calls.
+  return fb_group_gemm(dtype, b_k_contiguous, d_a, d_b, d_c, d_out, d_m, d_n, d_k, d_lda, d_ldb, d_ldc, group_count,
+                       m_hint, n_hint, k_hint, alpha, beta, scratch, kNoAllocScratchBytes, stream);
+}
+
+int fb_no_alloc_max_groups(void) { return kNoAllocMaxGroups; }
+
 const char* fb_status_string(int status) {
   switch (status) {
     case FB_OK: return "ok";
@@ -622,7 +673,7 @@ const char* fb_status_string(int status) {
     case FB_ERR_LAUNCH: return "CUDA error at launch";
     case FB_ERR_UNSUPPORTED: return "unsupported device or size";
     case FB_ERR_DRIVER: return "tensor-map encoding failed";
-    case FB_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+    case FB_ERR_TOO_LARGE: return "request exceeds a fixed capacity (more groups than the built-in scratch holds)";
     case DEV_TIMEOUT_PRODUCER_EMPTY: return "device: TMA producer timed out waiting for a free stage";
     case DEV_TIMEOUT_MMA_FULL: return "device: MMA issuer timed out waiting for operand data";
     case DEV_TIMEOUT_MMA_TMEM_EMPTY: return "device: MMA issuer timed out waiting for a free accumulator";

@@ -121,6 +121,35 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
 
 size_t fb_group_workspace_bytes(int group_count);
 
+/*
+ * fb_group_gemm without a workspace argument, for callers that are not allowed to allocate
+ * device memory at all.  (This entry point has no counterpart in the reference.)
+ *
+ * Who needs it: code that runs inside another runtime's enqueue/execute hook, where the host
+ * forbids cudaMalloc on the hot path, and services that reserved all of HBM for their own pool
+ * up front, so that a later cudaMalloc would fail or stall.  Such callers still own and pass every
+ * input and output; only the call's internal scratch (tile table + per-group tensor maps) is
+ * taken from a fixed array inside the library instead of from `workspace`.
+ *
+ * Limits and rules:
+ *   - at most fb_no_alloc_max_groups() (= 256) groups per call; more returns FB_ERR_TOO_LARGE;
+ *   - the array costs about 80 KB of device memory on every GPU that loads the library, for
+ *     the life of the process;
+ *   - the first call on each device looks the array's address up (cudaGetSymbolAddress); make
+ *     that first call before starting any stream capture on that device;
+ *   - all calls share the one array per device: two calls whose GPU work can overlap (different
+ *     streams, different threads) race on it -- order them on one stream or with events;
+ *   - no cudaMalloc / cudaFree / allocating library routine is called, on any call.
+ * Results are those of fb_group_gemm for the same arguments, bit for bit.
+ */
+int fb_group_gemm_no_alloc(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                           const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                           const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count,
+                           int64_t m_hint, int64_t n_hint, int64_t k_hint, float alpha, float beta, void* stream);
+
+/* Largest group_count fb_group_gemm_no_alloc accepts. */
+int fb_no_alloc_max_groups(void);
+
 /* ---- diagnostics -------------------------------------------------------- */
 
 /* Human-readable text for an FB_* code or a device status. */
