@@ -131,10 +131,10 @@ def run_reference(args, rank, world):
         if i >= args.warmup:
             vals.append((tf, secs))
     tf = sum(v[0] for v in vals) / len(vals)
-    sample = "torch.matmul fp32, %d of %d output rows of %s per step (inputs upcast)" % (rows, m, args.workload)
+    sample = "torch.matmul fp32 on %d of %d output rows of %s, repeated for ~%.0f s per step (inputs upcast)" % (rows, m, args.workload, per_step)
     line = {
         "impl": "reference", "metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(v[1] for v in vals) / len(vals),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * 2.0 * rows * n * k / (tf * 1e12),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
@@ -279,7 +279,7 @@ def main():
 
             tf, rows, secs, threads = cpu_baseline.time_dense_rows(m, n, k, ta, tb, target_seconds=12.0, seed=seed, scale=sa)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                                    "sample": "torch.matmul fp32 on %d of %d output rows of %s (inputs upcast), %.1f s" % (rows, m, args.workload, secs)}
+                                    "sample": "torch.matmul fp32 on %d of %d output rows of %s (inputs upcast), repeated for %.1f s" % (rows, m, args.workload, secs)}
         print(json.dumps(line), flush=True)
     if use_dist:
         tdist.destroy_process_group()

@@ -84,8 +84,9 @@ def all_gather_columns(C_local: torch.Tensor, m: int, n: int, ldc: int, rank: in
     packed = torch.zeros(m, width, dtype=C_local.dtype, device=C_local.device)
     if n1 > n0:
         packed[:, : n1 - n0].copy_(c2d[:, n0:n1])
-    gathered = torch.empty(world, m, width, dtype=C_local.dtype, device=C_local.device)
-    dist.all_gather_into_tensor(gathered, packed, group=group)
+    flat = torch.empty(world * m, width, dtype=C_local.dtype, device=C_local.device)  # rank-major concatenation
+    dist.all_gather_into_tensor(flat, packed, group=group)
+    gathered = flat.view(world, m, width)
     for r, (s, e) in enumerate(ranges):
         if r != rank and e > s:
             c2d[:, s:e].copy_(gathered[r, :, : e - s])
