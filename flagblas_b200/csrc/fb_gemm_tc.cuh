@@ -68,6 +68,8 @@ struct GroupRec {
   int tile_start;  // first linear tile index of this group
   int tiles_n;
   int vec_ok;
+  int a3d, b3d;  // this group's A / B tensor map is a 3-D view (one copy per stage)
+  int row_base;  // first row of the group this pass covers (rows before it belong to the other pass)
   void* out;
   long long ldo;
   const void* cin;
@@ -288,6 +290,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int t = worker; t < num_tiles && ok; t += num_workers) {
         int tm, tn, kk_total;
         const CUtensorMap* map = load_a ? &tmA : &tmB;
+        uint32_t use3d = og.use3d;
+        int row_base = 0;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           const GroupRec& gr = p.groups[g];
@@ -296,13 +300,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tn = lt - tm * gr.tiles_n;
           kk_total = gr.k;
           map = &p.group_maps[2 * g + (load_a ? 0 : 1)];
+          use3d = load_a ? gr.a3d : gr.b3d;
+          row_base = gr.row_base;
           fence_tensormap_acquire(map);
         } else {
           swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
           kk_total = p.k;
         }
         // first row (A) / first column (B) of the operand slab this CTA fetches
-        const int mn0 = load_a ? tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
+        const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -321,22 +327,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             else mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (a_stage_bytes + b_stage_bytes));
           }
           if (!(p.debug & 2)) {
-            if (og.use3d) {
+            if (use3d) {
               // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row
               const int y = og.mn_major ? k0 : mn0;
               const int z = og.mn_major ? mn0 / static_cast<int>(og.span) : k0 / static_cast<int>(og.span);
               if constexpr (PAIR) tma_load_3d_pair(dst, map, bar, 0, y, z);
               else tma_load_3d(dst, map, &full_bar[stage], 0, y, z);
+            } else if (og.mn_major) {
+              // one box per 128-byte chunk of MN, each holding every k row of the stage
+              for (uint32_t bx = 0; bx < og.boxes; ++bx) {
+                uint8_t* d = dst + bx * og.box_bytes;
+                const int x = mn0 + static_cast<int>(bx * og.box_mn_step);
+                if constexpr (PAIR) tma_load_2d_pair(d, map, bar, x, k0);
+                else tma_load_2d(d, map, &full_bar[stage], x, k0);
+              }
             } else {
+              // one box per k-slab
               for (uint32_t sl = 0; sl < p.ks; ++sl) {
-                const int ks0 = k0 + static_cast<int>(sl * og.span);
-                for (uint32_t bx = 0; bx < og.boxes; ++bx) {
-                  uint8_t* d = dst + sl * slab_bytes + bx * og.box_bytes;
-                  const int x = og.mn_major ? mn0 + static_cast<int>(bx * og.box_mn_step) : ks0;
-                  const int y = og.mn_major ? ks0 : mn0;
-                  if constexpr (PAIR) tma_load_2d_pair(d, map, bar, x, y);
-                  else tma_load_2d(d, map, &full_bar[stage], x, y);
-                }
+                uint8_t* d = dst + sl * slab_bytes;
+                const int x = k0 + static_cast<int>(sl * og.span);
+                if constexpr (PAIR) tma_load_2d_pair(d, map, bar, x, mn0);
+                else tma_load_2d(d, map, &full_bar[stage], x, mn0);
               }
             }
           }
@@ -380,7 +391,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long cstart = p.prof ? clock64() : 0;
       unsigned long long gstart = 0;
       if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gstart));
-      bool data_ready = false;   // the current stage's barrier was already seen complete
+      bool data_ready = false;   // the current stage's barrier was already seen complete (and fenced)
+      uint64_t a_desc = 0, b_desc = 0;  // descriptors of the current stage
       for (int t = worker; t < num_tiles && ok; t += num_workers) {
         int kk_total = p.k;
         if (grouped) {
@@ -401,13 +413,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long c0 = p.prof ? clock64() : 0;
             if (!mbar_wait(&full_bar[stage], phase, wctl, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
             if (p.prof) prof_wfull += clock64() - c0;
+            tc_fence_after();
+            a_desc = a_desc0 + static_cast<uint32_t>(stage) * a_stage_units;
+            b_desc = b_desc0 + static_cast<uint32_t>(stage) * b_stage_units;
           }
-          tc_fence_after();
-          const uint64_t a_desc = a_desc0 + static_cast<uint32_t>(stage) * a_stage_units;
-          const uint64_t b_desc = b_desc0 + static_cast<uint32_t>(stage) * b_stage_units;
           int next_stage = stage + 1;
           uint32_t next_phase = phase;
           if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1u; }
+          uint64_t a_next = 0, b_next = 0;
 #pragma unroll
           for (int j = 0; j < kMaxMma; ++j) {
             if (j < n_mma) {
@@ -416,10 +429,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if constexpr (PAIR) umma_pair<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
                 else umma<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
               }
-              if (j == n_mma - 2) data_ready = mbar_test_wait(&full_bar[next_stage], next_phase);
+              if (j == n_mma - 2) {
+                // Slot before the last MMA: everything the next stage needs, so that its first MMA
+                // can follow this stage's last one back to back.
+                data_ready = mbar_test_wait(&full_bar[next_stage], next_phase);
+                if (data_ready) tc_fence_after();
+                a_next = a_desc0 + static_cast<uint32_t>(next_stage) * a_stage_units;
+                b_next = b_desc0 + static_cast<uint32_t>(next_stage) * b_stage_units;
+              }
               if (j == n_mma - 1) {
-                // Release the stage (in both CTAs of a pair) as soon as its last MMA is queued: the
-                // commit is cheap to issue and the next stage's first MMA follows immediately.
+                // Release the stage (in both CTAs of a pair) as soon as its last MMA is queued.  With
+                // only three stages in the ring the refill latency is on the critical path: releasing
+                // even one MMA later measurably starves the next stages.
                 if constexpr (PAIR) umma_commit_pair(&empty_bar[stage], 3);
                 else umma_commit(&empty_bar[stage]);
               }
@@ -427,6 +448,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           stage = next_stage;
           phase = next_phase;
+          a_desc = a_next;
+          b_desc = b_next;
         }
         if (!ok) break;
         // Tile done: publish the accumulator to the epilogue (of both CTAs of a pair).
@@ -454,6 +477,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     long long prof_ewait = 0, prof_ebody = 0;
     for (int t = worker; t < num_tiles && ok; t += num_workers) {
       int tm, tn;
+      int row_base = 0;
       Problem pr;
       bool k_is_zero = false;  // a group with k == 0 contributes beta * C only
       if (grouped) {
@@ -465,6 +489,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pr.m = gr.m; pr.n = gr.n; pr.out = gr.out; pr.ldo = gr.ldo; pr.cin = gr.cin; pr.ldcin = gr.ldcin;
         pr.vec_ok = gr.vec_ok;
         k_is_zero = gr.k == 0;
+        row_base = gr.row_base;
       } else {
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         pr = p.prob;
@@ -478,7 +503,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const long long e1 = p.prof ? clock64() : 0;
       prof_ewait += e1 - e0;
-      const int row = tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
+      const int row = row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1

@@ -517,10 +517,15 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   return dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
 }
 
+// Workspace of one pass: records, the tile count, tensor maps.
+static constexpr size_t group_pass_bytes(size_t groups) {
+  return (sizeof(GroupRec) * groups + 255) / 256 * 256 + 256 + sizeof(CUtensorMap) * 2 * groups;
+}
+static constexpr size_t group_ws_bytes(size_t groups) { return 2 * group_pass_bytes(groups); }
+
 size_t fb_group_workspace_bytes(int group_count) {
   if (group_count <= 0) return 0;
-  return round_up(sizeof(GroupRec) * static_cast<size_t>(group_count), 256) + 256 +
-         sizeof(CUtensorMap) * 2 * static_cast<size_t>(group_count);
+  return group_ws_bytes(static_cast<size_t>(group_count));
 }
 
 static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long n_hint,
@@ -533,40 +538,93 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     return FB_ERR_WORKSPACE;
   const int esz = elem_size(dtype);
   const uint32_t span = kSwizzleBytes / esz;
-  const int block_n = (n_hint > 0 && n_hint <= 64) ? 64 : ((n_hint > 0 && n_hint <= 128) ? 128 : 256);
-
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
-  ga.recs = reinterpret_cast<GroupRec*>(ws);
-  ga.total_tiles = reinterpret_cast<int*>(ws + round_up(sizeof(GroupRec) * static_cast<size_t>(G), 256));
-  ga.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ga.total_tiles) + 256);
+  const bool atom32 = esz == 4;
+  // Tile plan: one pass of CTA-pair tiles (256 x block_n, two k-slabs per stage).  With
+  // FLAGBLAS_B200_GROUP_SPLIT=1 the pair pass takes only the whole 256-row blocks of each group and a
+  // second pass of single-CTA tiles (128 x block_n) takes the remaining rows; on the MoE benchmark
+  // shape that saves padded rows but loses as much to the slower single-CTA kernel, so it is off by
+  // default.  FLAGBLAS_B200_PAIR=0 runs everything in a single-CTA pass; _KS / _TMA3D as in the dense path.
+  int block_n = (n_hint > 0 && n_hint <= 64) ? 64 : ((n_hint > 0 && n_hint <= 128) ? 128 : 256);
+  const bool pair = env_int("FLAGBLAS_B200_PAIR", 1) != 0 && block_n >= 128;
+  const bool split = pair && env_int("FLAGBLAS_B200_GROUP_SPLIT", 0) != 0;
+  ga.span = static_cast<int>(span);
+  ga.allow3d = env_int("FLAGBLAS_B200_TMA3D", 1) != 0 ? 1 : 0;
   ga.b_k_contig = b_k_contig;
   ga.esz = esz;
-  ga.block_n = block_n;
 
-  // Templates carry everything the device does not patch: dtype, box, swizzle.
-  // Their address/extents are placeholders (the workspace itself, a valid 256-byte aligned range).
-  CUtensorMap ta, tb;
-  int rc = encode_2d(&ta, dtype, ws, span, kBlockM, kSwizzleBytes, span, kBlockM);
-  if (rc) return rc;
-  if (b_k_contig) rc = encode_2d(&tb, dtype, ws, span, block_n, kSwizzleBytes, span, block_n);
-  else rc = encode_2d(&tb, dtype, ws, span, span, kSwizzleBytes, span, span, esz == 4);
-  if (rc) return rc;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  GroupPass pass[2] = {};
+  int pass_ks[2] = {1, 1};
+  bool pass_pair[2] = {false, false};
+  for (int i = 0; i < 2; ++i) {
+    GroupPass& ps = pass[i];
+    uint8_t* base = ws + i * group_pass_bytes(G);
+    ps.recs = reinterpret_cast<GroupRec*>(base);
+    ps.total_tiles = reinterpret_cast<int*>(base + round_up(sizeof(GroupRec) * static_cast<size_t>(G), 256));
+    ps.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ps.total_tiles) + 256);
+    ps.block_n = block_n;
+  }
+  if (pair) {
+    pass[0].enabled = 1; pass[0].tile_m = 2 * kBlockM; pass_pair[0] = true;
+    pass_ks[0] = env_int("FLAGBLAS_B200_KS", 2) == 1 ? 1 : 2;
+    if (split) {
+      pass[0].rows_mod = 2 * kBlockM; pass[0].leading = 1;
+      pass[1].enabled = 1; pass[1].tile_m = kBlockM; pass[1].rows_mod = 2 * kBlockM; pass[1].leading = 0;
+    }
+  } else {
+    pass[0].enabled = 1; pass[0].tile_m = kBlockM;
+  }
+  // Templates carry everything the device does not patch: dtype, box, swizzle (and, for the 3-D
+  // views, the 128-byte innermost extent and the 128-byte pitch of the slab dimension).
+  // Their address / extents are placeholders (the workspace itself, a valid 256-byte aligned range).
+  for (int i = 0; i < 2; ++i) {
+    GroupPass& ps = pass[i];
+    if (!ps.enabled) continue;
+    const int ks = pass_ks[i];
+    const int b_rows = pass_pair[i] ? block_n / 2 : block_n;
+    int rc = encode_2d(&ps.tmpl_a, dtype, ws, span, kBlockM, kSwizzleBytes, span, kBlockM);
+    if (rc) return rc;
+    if (b_k_contig) rc = encode_2d(&ps.tmpl_b, dtype, ws, span, b_rows, kSwizzleBytes, span, b_rows);
+    else rc = encode_2d(&ps.tmpl_b, dtype, ws, span, span * ks, kSwizzleBytes, span, span * ks, atom32);
+    if (rc) return rc;
+    rc = encode_3d(&ps.tmpl_a3, dtype, ws, span, kBlockM, ks, kSwizzleBytes, kSwizzleBytes, span, kBlockM, ks, false);
+    if (!rc) {
+      if (b_k_contig)
+        rc = encode_3d(&ps.tmpl_b3, dtype, ws, span, b_rows, ks, kSwizzleBytes, kSwizzleBytes, span, b_rows, ks, false);
+      else
+        rc = encode_3d(&ps.tmpl_b3, dtype, ws, span, span * ks, b_rows / span, kSwizzleBytes, kSwizzleBytes, span,
+                       span * ks, b_rows / span, atom32);
+    }
+    if (rc) {  // no 3-D views on this driver: every group uses 2-D boxes
+      ga.allow3d = 0;
+      ps.tmpl_a3 = ps.tmpl_a;
+      ps.tmpl_b3 = ps.tmpl_b;
+    }
+  }
 
-  group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(ta, tb, ga);
+  group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
   FB_CUDA_OK(cudaGetLastError());
 
-  TcGemmParams p{};
-  p.alpha = alpha; p.beta = beta;
-  p.idesc = make_idesc(idesc_fmt(dtype), 0, b_k_contig ? 0 : 1, kBlockM, block_n);
-  p.block_k = span;
-  p.ks = 1;
-  p.a = make_geom(esz, kBlockM, false, 1, false);
-  p.b = make_geom(esz, block_n, !b_k_contig, 1, false);
-  p.num_groups = G;
-  p.groups = ga.recs;
-  p.total_tiles = ga.total_tiles;
-  p.group_maps = ga.maps;
-  return dispatch_tc(dtype, block_n, /*pair=*/false, ta, tb, p, /*tiles=*/-1, di->sm_count, stream);
+  for (int i = 0; i < 2; ++i) {
+    const GroupPass& ps = pass[i];
+    if (!ps.enabled) continue;
+    const int ks = pass_ks[i];
+    const int b_rows = pass_pair[i] ? block_n / 2 : block_n;
+    TcGemmParams p{};
+    p.alpha = alpha; p.beta = beta;
+    p.idesc = make_idesc(idesc_fmt(dtype), 0, b_k_contig ? 0 : 1, ps.tile_m, block_n);
+    p.block_k = span * ks;
+    p.ks = ks;
+    p.a = make_geom(esz, kBlockM, false, ks, false);
+    p.b = make_geom(esz, b_rows, !b_k_contig, ks, false);
+    p.num_groups = G;
+    p.groups = ps.recs;
+    p.total_tiles = ps.total_tiles;
+    p.group_maps = ps.maps;
+    const int rc = dispatch_tc(dtype, block_n, pass_pair[i], ps.tmpl_a, ps.tmpl_b, p, /*tiles=*/-1, di->sm_count, stream);
+    if (rc) return rc;
+  }
+  return FB_OK;
 }
 
 int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
@@ -625,8 +683,7 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
 // array that is part of the library image: every GPU that loads the library carries these
 // bytes until the process exits, which is why the capacity is kept small.
 constexpr int kNoAllocMaxGroups = 256;
-constexpr size_t kNoAllocScratchBytes =
-    ((sizeof(GroupRec) * kNoAllocMaxGroups + 255) / 256) * 256 + 256 + sizeof(CUtensorMap) * 2 * kNoAllocMaxGroups;
+constexpr size_t kNoAllocScratchBytes = group_ws_bytes(kNoAllocMaxGroups);
 static __device__ __align__(256) unsigned char g_no_alloc_scratch[kNoAllocScratchBytes];
 
 // In host code `g_no_alloc_scratch` is only a handle for the runtime, not an address a kernel can

@@ -96,6 +96,17 @@ def test_grouped_alpha_zero_and_beta_zero(kind):
     assert not torch.isnan(got).any()
 
 
+@pytest.mark.parametrize("env", [{"FLAGBLAS_B200_GROUP_SPLIT": "1"}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_TMA3D": "0"},
+                                 {"FLAGBLAS_B200_KS": "1"}])
+def test_grouped_tile_plan_variants(env, monkeypatch):
+    """The alternative tile plans (two-pass split, single-CTA tiles, 2-D copies, one k-slab per stage)
+    compute the same thing."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    _run_group("bf16", [5, 0, 70, 33, 300, 128, 129, 1, 700, 256], 512, 384, 1.5, 0.5, seed=11)
+    _run_group("tf32", [40, 200, 64, 513], 200, 136, 1.5, 0.5, seed=12, var_nk=True)
+
+
 def test_grouped_many_groups():
     _run_group("bf16", [((7 * i) % 90) for i in range(600)], 128, 256, 1.0, 0.0, seed=7)
 
