@@ -117,6 +117,73 @@ class ClockSampler:
                 "samples": len(s)}
 
 
+def _time(fn, torch, steps=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def other_configs(fb, torch, dev):
+    """Short device-resident timings of the remaining BASELINE configs (not the headline)."""
+    peak, _ = measured_peak()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        hbm = 6650.0
+    out = {}
+    dts = {"fp16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32, "fp32": torch.float32}
+    for name, (op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed) in WORKLOADS.items():
+        if name == HEADLINE:
+            continue
+        g = torch.Generator(device=dev).manual_seed(seed)
+        A = (torch.randn((k, m) if ta else (m, k), generator=g, device=dev) * sa).to(dts[kind])
+        B = (torch.randn((n, k) if tb else (k, n), generator=g, device=dev) * sb).to(dts[kind])
+        C = (torch.randn(m, n, generator=g, device=dev) * 0.02).to(dts[kind])
+        fn = getattr(fb, op)
+        ms = _time(lambda: fn(ta, tb, m, n, k, alpha, A, A.shape[1], B, B.shape[1], beta, C, n), torch)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        nbytes = A.element_size() * (m * k + k * n + m * n * (2 if beta != 0 else 1))
+        rec = {"tflops": tf, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9}
+        if name == "tf32gemm_skinny_tn":
+            rec.update(bound="hbm", frac=rec["gbs"] / hbm, peak=hbm)
+        elif kind == "tf32":
+            rec.update(bound="tensor", frac=tf / (peak / 2), peak=peak / 2)   # TF32 runs at half the 16-bit rate
+        elif kind == "fp32":
+            rec.update(bound="fp32 FFMA (latency bound at this size)", frac=None)
+        else:
+            rec.update(bound="tensor", frac=tf / peak, peak=peak)
+        out[name] = rec
+        del A, B, C
+    # grouped MoE config: 64 experts, K=4096, N=1536, Zipf(1.2) token counts, bf16
+    E, K, N, T = 64, 4096, 1536, 32768
+    gc = torch.Generator().manual_seed(3)
+    w = torch.arange(1, E + 1, dtype=torch.float64) ** -1.2
+    ms_ = torch.multinomial(w / w.sum(), T, replacement=True, generator=gc).bincount(minlength=E).tolist()
+    g = torch.Generator(device=dev).manual_seed(3)
+    A = torch.randn(T, K, generator=g, device=dev).bfloat16()
+    B = (torch.randn(E * K, N, generator=g, device=dev) * 0.02).bfloat16()
+    O = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+    ap, bp, op_, s = [], [], [], 0
+    for e, mg in enumerate(ms_):
+        ap.append(A.data_ptr() + s * K * 2); bp.append(B.data_ptr() + e * K * N * 2); op_.append(O.data_ptr() + s * N * 2); s += mg
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    args = (O, i64(ap), i64(bp), i64(op_), i64(op_), i32(ms_), i32([N] * E), i32([K] * E), i32([K] * E), i32([N] * E),
+            i32([N] * E), E, T, N, K, 1.0, 0.0)
+    ms = _time(lambda: fb.group_bfgemm(*args), torch)
+    tf = 2.0 * T * N * K / (ms * 1e-3) / 1e12
+    out["group_bfgemm_moe64"] = {"tflops": tf, "ms": ms, "bound": "tensor", "frac": tf / peak, "peak": peak}
+    return out
+
+
 def run_reference(args, rank, world):
     """Reference arm: the path on the host cores (torch.matmul fp32 over a bounded row sample)."""
     if rank != 0:
@@ -154,6 +221,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the brief runs of the other BASELINE configs")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -180,17 +248,27 @@ def main():
 
     op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
     dt = {"fp16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32, "fp32": torch.float32}[kind]
-    g = torch.Generator(device=dev).manual_seed(seed)  # same seed on every rank: A and B are replicated
+    g = torch.Generator(device=dev).manual_seed(seed)  # same seed on every rank: the same global A, B, C
     A = (torch.randn((k, m) if ta else (m, k), generator=g, device=dev) * sa).to(dt)
     B = (torch.randn((n, k) if tb else (k, n), generator=g, device=dev) * sb).to(dt)
     C = (torch.randn(m, n, generator=g, device=dev) * 0.02).to(dt) if beta != 0 else torch.full((m, n), float("nan"), device=dev, dtype=dt)
-    lda, ldb, ldc = A.shape[1], B.shape[1], n
+    lda = A.shape[1]
     n0, n1 = fbdist.column_ranges(n, world)[rank]
+    nl = n1 - n0
+    if world > 1:
+        # Column-sharded layout: A replicated, every rank owns its columns of B and of C as local,
+        # densely pitched shards (what a tensor-parallel caller holds); nothing is exchanged.
+        B = (B[n0:n1] if tb else B[:, n0:n1]).contiguous()
+        C = C[:, n0:n1].contiguous()
+    ldb, ldc = B.shape[1], C.shape[1]
+    opfn = getattr(fb, op)
+    gathered = torch.empty(world, m, max(nl, 1), dtype=dt, device=dev) if (use_dist and args.gather) else None
 
     def step():
-        fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
-        if use_dist and args.gather:
-            fbdist.all_gather_columns(C, m, n, ldc, rank, world)
+        if nl > 0:
+            opfn(ta, tb, m, nl, k, alpha, A, lda, B, ldb, beta, C, ldc)
+        if gathered is not None:
+            tdist.all_gather_into_tensor(gathered.view(world * m, -1), C)
 
     def barrier():
         if use_dist:
@@ -222,24 +300,18 @@ def main():
     # ---- end to end: host buffers in, host buffer out, through the operator API
     esz = A.element_size()
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
-    hC = torch.empty((m, max(n1 - n0, 1)), dtype=dt).pin_memory()
-    B2 = B.view(-1)[: (n if tb else k) * ldb].view(-1, ldb)
-    hB2 = hB.view(-1, ldb)
-    C2 = C.view(m, ldc)
+    hC = torch.empty(C.shape, dtype=dt).pin_memory()
 
     def e2e_step():
         A.copy_(hA, non_blocking=True)
-        if tb:
-            B2[n0:n1].copy_(hB2[n0:n1], non_blocking=True)
-        else:
-            B2[:, n0:n1].copy_(hB2[:, n0:n1], non_blocking=True)
-        fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
-        hC[:, : n1 - n0].copy_(C2[:, n0:n1], non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        if nl > 0:
+            opfn(ta, tb, m, nl, k, alpha, A, lda, B, ldb, beta, C, ldc)
+        hC.copy_(C, non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_step()
     barrier()
-    t0 = time.perf_counter()
     e0.record()
     for _ in range(args.e2e_steps):
         e2e_step()
@@ -250,8 +322,13 @@ def main():
         t = torch.tensor([e2e_ms], device=dev)
         tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    h2d = (A.numel() + (n1 - n0) * k) * esz
-    d2h = m * (n1 - n0) * esz
+    h2d = (A.numel() + B.numel()) * esz
+    d2h = C.numel() * esz
+
+    # ---- the other BASELINE configs, briefly (single GPU only; informational)
+    others = {}
+    if world == 1 and not args.no_other_configs:
+        others = other_configs(fb, torch, dev)
 
     if rank == 0:
         peak, peak_src = measured_peak()
@@ -264,13 +341,14 @@ def main():
             "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb,
                        "alpha": alpha, "beta": beta, "accumulate": "f32",
                        "parallelism": "single GPU" if world == 1 else "N-split of C columns over %d GPUs, no collective%s" % (world, " + all-gather" if args.gather else ""),
-                       "l2": "inputs (%.0f MiB) larger than L2; no flush between steps" % ((A.numel() + B.numel() + C.numel()) * esz / 2**20)},
+                       "l2": "per-GPU inputs (%.0f MiB) %s L2; no flush between steps" % ((A.numel() + B.numel() + C.numel()) * esz / 2**20, "larger than" if (A.numel() + B.numel() + C.numel()) * esz > 126e6 else "NOT larger than")},
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                          "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
                          "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": args.steps,
+            "other_configs": others,
             "clocks": clk.summary(),
             "device_status": status,
         }
