@@ -22,8 +22,13 @@ the storage type being modelled ("fp32", "tf32", "fp16", "bf16"); outputs are
 rounded once to that type.  The accumulator is formed in float64 and narrowed
 to float32 before the epilogue, which differs from the reference's fp32
 chunk-wise accumulation by a few fp32 ulps of the partial sums -- far inside
-every tolerance used and pinned by the golden vectors in ``tests/golden``
-(generated from the reference's own kernels by ``tests/golden/make_golden.py``).
+every tolerance used and pinned by the golden vectors in ``tests/golden``: fp32 / fp16 vectors made
+by the reference's own kernels under Triton's CPU interpreter (``make_golden.py``), and bf16 / fp16 /
+fp32 / TF32 vectors made by the same kernels running natively on a B200 (``make_golden_gpu.py``).
+The latter show that on B200 the reference's TF32 dots TRUNCATE their fp32 operands (the operands go
+from shared memory straight into the tensor core), hence ``tf32_mode="trunc"`` is the default here;
+``"rna"`` (round to nearest, what a register-operand lowering does) and ``"none"`` are kept for
+comparison.
 """
 import numpy as np
 
@@ -83,7 +88,7 @@ def _inputs(a, kind, tf32_mode):
 
 
 # --------------------------------------------------------------------- dense
-def gemm(kind, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, tf32_mode="rna"):
+def gemm(kind, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, tf32_mode="trunc"):
     """In-place dense GEMM on flat row-major buffers; returns None like the reference.
 
     ``A``, ``B``, ``C`` are 1-D (or any-shape, C-contiguous) numpy arrays that are
@@ -129,7 +134,7 @@ def gemm_fp64(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):
 
 
 # ------------------------------------------------------------------- grouped
-def group_gemm(kind, a_list, b_list, c_list, alpha, beta, b_stored_nk=False, tf32_mode="rna"):
+def group_gemm(kind, a_list, b_list, c_list, alpha, beta, b_stored_nk=False, tf32_mode="trunc"):
     """Per-group ``out_g = alpha * A_g @ B_g + beta * C_g`` (group_gemm.py:131-218, 488-504).
 
     ``a_list[g]`` is ``[m_g, k_g]``; ``b_list[g]`` is ``[k_g, n_g]``, or ``[n_g, k_g]`` when

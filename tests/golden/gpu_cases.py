@@ -1,0 +1,68 @@
+"""Seeded inputs of the GPU golden vectors, shared by the generator (``make_golden_gpu.py``) and the
+tests that consume ``gpu_reference.npz``.  Only the reference's outputs are stored in the fixture; the
+inputs are regenerated from these seeds (torch's CPU generator), and a few input elements are stored
+alongside to detect a generator mismatch."""
+import torch
+
+DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32, "tf32": torch.float32}
+DENSE_AB = {"bf16": (1.5, 0.5), "fp16": (1.5, 0.5), "fp32": (2.5, 0.5)}
+DENSE_SHAPES = {"bf16": ((96, 80, 72, 0), (70, 130, 45, 8)), "fp16": ((70, 130, 45, 8),), "fp32": ((70, 130, 45, 4),)}
+GROUP_MS, GROUP_K, GROUP_N = [5, 0, 70, 33, 100], 256, 192
+GROUP_AB = {"ab": (1.5, 0.5), "b0": (1.0, 0.0)}
+
+
+def dense_cases(kind):
+    """Yields (key, (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C) as CPU tensors."""
+    dt = DTYPES[kind]
+    gen = torch.Generator(device="cpu").manual_seed(31)
+    alpha, beta = DENSE_AB[kind]
+    for ta in (0, 1):
+        for tb in (0, 1):
+            for ci, (m, n, k, pad) in enumerate(DENSE_SHAPES[kind]):
+                lda, ldb, ldc = (m if ta else k) + pad, (k if tb else n) + pad, n + pad
+                A = torch.randn((k if ta else m), lda, generator=gen).to(dt)
+                B = torch.randn((n if tb else k), ldb, generator=gen).to(dt)
+                C = torch.randn(m, ldc, generator=gen).to(dt)
+                yield "dense_%s_t%d%d_c%d" % (kind, ta, tb, ci), (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C
+
+
+def group_case(kind, tag):
+    """(ms, K, N, alpha, beta, A [sum m, K], B [E*K, N], C [sum m, N]) as CPU tensors."""
+    dt = DTYPES[kind]
+    gen = torch.Generator(device="cpu").manual_seed(33)
+    E = len(GROUP_MS)
+    A = torch.randn(sum(GROUP_MS), GROUP_K, generator=gen).to(dt)
+    B = (torch.randn(E * GROUP_K, GROUP_N, generator=gen) * GROUP_K ** -0.5).to(dt)
+    C = torch.randn(sum(GROUP_MS), GROUP_N, generator=gen).to(dt)
+    alpha, beta = GROUP_AB[tag]
+    return GROUP_MS, GROUP_K, GROUP_N, alpha, beta, A, B, C
+
+
+def tf32_probe():
+    """All-positive fp32 inputs: truncating the operands to TF32 shows up as a ~7e-4 shrink of every
+    output, rounding them to nearest does not."""
+    gen = torch.Generator(device="cpu").manual_seed(34)
+    m, n, k = 128, 128, 2048
+    return m, n, k, torch.rand(m, k, generator=gen) + 0.5, torch.rand(n, k, generator=gen) + 0.5
+
+
+def group_mm_case():
+    gen = torch.Generator(device="cpu").manual_seed(35)
+    A = torch.randn(216, 128, generator=gen).bfloat16()
+    B = (torch.randn(4, 128, 96, generator=gen) / 11).bfloat16()
+    offs = torch.tensor([20, 20, 150, 216], dtype=torch.int32)
+    return A, B, offs
+
+
+def pack(t):
+    """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.contiguous().view(torch.int16).numpy()
+    return t.contiguous().numpy()
+
+
+def unpack(a, kind):
+    t = torch.from_numpy(a)
+    if kind in ("bf16", "fp16"):
+        return t.view(DTYPES[kind])
+    return t

@@ -1,0 +1,177 @@
+"""Generate ``gpu_reference.npz``: outputs of the REFERENCE's own Triton kernels run natively on a GPU.
+
+Complements ``make_golden.py`` (CPU interpreter: fp32 / fp16 only): on a GPU the reference's generic
+level-3 kernels also run in bf16 and with real TF32 dots, which pins the two things the CPU vectors
+cannot -- bfloat16 results and the TF32 rounding the reference's lowering applies.
+
+Needs an installed copy of the reference (it is not shipped with this repo), e.g.
+
+    python -m pip install --no-deps --no-build-isolation --target baseline/_ref /path/to/FlagBLAS
+    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py
+
+and a CUDA device.  The same import shims as ``make_golden.py`` apply (stub ``sqlalchemy``,
+``BLAS_VENDOR`` / ``ARCH`` / ``FLAGGEMS_DB_URL``, pass-through ``libentry`` that launches every kernel
+with the first configuration of its tuning list); only the *generic* kernels of
+``flag_blas.ops.level3`` are called (plain pointer kernels, one CTA per tile, no clusters).
+"""
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+SITE = os.path.abspath(os.environ.get("FLAGBLAS_REFERENCE_SITE", os.path.join(ROOT, "baseline", "_ref")))
+
+
+def _import_reference():
+    os.environ.pop("TRITON_INTERPRET", None)
+    os.environ["BLAS_VENDOR"] = "nvidia"
+    os.environ["ARCH"] = "sm_90"
+    os.environ["FLAGGEMS_DB_URL"] = "sqlite:////tmp/flagblas_golden_gpu.db"
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]  # the repo's own flag_blas alias must not win
+    sys.path.insert(0, SITE)
+
+    class _Any:
+        def __init__(self, *a, **k):
+            pass
+
+        def __getattr__(self, n):
+            return _Any()
+
+        def __call__(self, *a, **k):
+            return _Any()
+
+        def __class_getitem__(cls, i):
+            return cls
+
+    sa = types.ModuleType("sqlalchemy")
+    for sub in ("ext", "ext.automap", "orm", "exc", "engine", "schema"):
+        sys.modules["sqlalchemy." + sub] = types.ModuleType("sqlalchemy." + sub)
+    sys.modules["sqlalchemy"] = sa
+    sa.ext = sys.modules["sqlalchemy.ext"]
+    sa.ext.automap = sys.modules["sqlalchemy.ext.automap"]
+    sa.orm, sa.exc = sys.modules["sqlalchemy.orm"], sys.modules["sqlalchemy.exc"]
+    sa.engine, sa.schema = sys.modules["sqlalchemy.engine"], sys.modules["sqlalchemy.schema"]
+
+    class DeclarativeBase:
+        pass
+
+    class Session:
+        def __init__(self, *a, **k):
+            pass
+
+    sa.orm.DeclarativeBase, sa.orm.Session = DeclarativeBase, Session
+    sa.orm.Mapped = sa.orm.MappedColumn = _Any
+    sa.orm.mapped_column = lambda **k: None
+    sa.exc.IntegrityError = Exception
+    sa.engine.Engine = _Any
+    sa.create_engine = lambda url: _Any()
+    sa.ext.automap.AutomapBase = _Any
+
+    class _AB:
+        classes = {}
+
+        def prepare(self, e):
+            pass
+
+    sa.ext.automap.automap_base = lambda: _AB()
+    sa.inspect = lambda o: _Any()
+
+    shim = types.ModuleType("flag_blas.utils.libentry")
+
+    class _Tuned:
+        def __init__(self, fn, configs):
+            self.fn, self.configs = fn, configs
+
+        def __getitem__(self, grid):
+            cfg = self.configs[0]
+            extra = dict(cfg.kwargs)
+            extra.update(num_warps=cfg.num_warps, num_stages=cfg.num_stages)
+            return lambda *a, **k: self.fn[grid](*a, **k, **extra)
+
+    class _LC:
+        model = None
+
+    shim.libentry = lambda: (lambda fn: fn)
+    shim.libtuner = lambda configs, key, **kw: (lambda fn: _Tuned(fn, configs))
+    shim.libcache = _LC()
+    sys.modules["flag_blas.utils.libentry"] = shim
+
+    import torch
+    import flag_blas  # noqa: F401  (the reference)
+
+    assert os.path.abspath(flag_blas.__file__).startswith(SITE), flag_blas.__file__
+    mods = {}
+    for name in ("sgemm", "hgemm", "bfgemm"):
+        mods[name] = getattr(sys.modules["flag_blas.ops.level3." + name], name)
+    gg = sys.modules["flag_blas.ops.level3.group_gemm"]
+    for name in ("group_bfgemm", "group_hgemm", "group_tf32gemm", "group_mm"):
+        mods[name] = getattr(gg, name)
+    return torch, mods
+
+
+def main():
+    torch, ref = _import_reference()
+    sys.path.insert(0, HERE)
+    import gpu_cases as gc
+
+    dev = "cuda"
+    out = {"device": np.array(torch.cuda.get_device_name(0)), "triton": np.array(__import__("triton").__version__)}
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
+
+    # ---------------------------------------------------------------- dense bf16 / fp16 / fp32
+    for kind, fn in (("bf16", ref["bfgemm"]), ("fp16", ref["hgemm"]), ("fp32", ref["sgemm"])):
+        for key, (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C in gc.dense_cases(kind):
+            Cd = C.to(dev)
+            fn(ta, tb, m, n, k, alpha, A.to(dev), lda, B.to(dev), ldb, beta, Cd, ldc)
+            torch.cuda.synchronize()
+            out[key + "_C"] = gc.pack(Cd.cpu())
+            out[key + "_probe"] = np.concatenate([A.float().numpy().ravel()[:8], B.float().numpy().ravel()[:8]])
+        print("dense", kind, "done", flush=True)
+
+    # ---------------------------------------------------------------- grouped bf16 / fp16 / tf32
+    for kind, fn, transB in (("bf16", ref["group_bfgemm"], False), ("fp16", ref["group_hgemm"], False),
+                             ("tf32", ref["group_tf32gemm"], True)):
+        for tag in ("ab", "b0"):
+            ms, K, N, al, be, A, B, C = gc.group_case(kind, tag)
+            E = len(ms)
+            Ad, Cd = A.to(dev), C.to(dev)
+            o = torch.full_like(Cd, float("nan")) if be == 0.0 else torch.zeros_like(Cd)
+            Bs = (torch.cat([B[g * K:(g + 1) * K].t().contiguous() for g in range(E)], 0) if transB else B).to(dev)
+            es = A.element_size()
+            ap, bp, cp, op, s = [], [], [], [], 0
+            for g, mg in enumerate(ms):
+                ap.append(Ad.data_ptr() + s * K * es); cp.append(Cd.data_ptr() + s * N * es)
+                op.append(o.data_ptr() + s * N * es); bp.append(Bs.data_ptr() + g * K * N * es)
+                s += mg
+            fn(o, i64(ap), i64(bp), i64(cp), i64(op), i32(ms), i32([N] * E), i32([K] * E), i32([K] * E),
+               i32([K if transB else N] * E), i32([N] * E), E, sum(ms), N, K, alpha=al, beta=be)
+            torch.cuda.synchronize()
+            out["group_%s_%s_out" % (kind, tag)] = gc.pack(o.cpu())
+            out["group_%s_%s_probe" % (kind, tag)] = np.concatenate([A.float().numpy().ravel()[:8], B.float().numpy().ravel()[:8]])
+        print("grouped", kind, "done", flush=True)
+
+    # TF32 rounding probe through the reference's group_tf32gemm (one group)
+    m, n, k, A, Bt = gc.tf32_probe()
+    Ad, Bd = A.to(dev), Bt.to(dev)
+    o = torch.zeros(m, n, device=dev)
+    ref["group_tf32gemm"](o, i64([Ad.data_ptr()]), i64([Bd.data_ptr()]), i64([o.data_ptr()]), i64([o.data_ptr()]), i32([m]), i32([n]),
+                          i32([k]), i32([k]), i32([k]), i32([n]), 1, m, n, k, alpha=1.0, beta=0.0)
+    torch.cuda.synchronize()
+    out["tf32probe_out"] = o.cpu().numpy()
+
+    A, B, offs = gc.group_mm_case()
+    Cm = ref["group_mm"](A.to(dev), B.to(dev), offs.to(dev))
+    torch.cuda.synchronize()
+    out["mm_C"] = gc.pack(Cm.cpu())
+
+    path = os.path.join(HERE, "gpu_reference.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
