@@ -12,9 +12,9 @@ from .ops import *  # noqa: F401,F403
 from .ops import __all__ as _ops_all
 from ._lib import FlagBlasError, device_status  # noqa: F401
 
-# ``flag_blas.c_operators`` is the name the reference reserves for a compiled
-# extension (src/flag_blas/config.py:35-41); here it is the loaded C-ABI library.
-c_operators = _lib.lib
+# ``flag_blas.c_operators`` is the name the reference reserves for a compiled extension
+# (src/flag_blas/config.py:35-41); here it is the pybind11 module over the C ABI.
+from . import c_operators  # noqa: E402,F401
 
 device = runtime.device.name
 vendor_name = runtime.device.vendor_name

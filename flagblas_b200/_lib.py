@@ -1,8 +1,11 @@
-"""ctypes binding of ``libflagblas_b200.so`` -- the C ABI declared in ``include/flagblas_b200.h``.
+"""Loader of the native code: ``libflagblas_b200.so`` (the C ABI declared in
+``include/flagblas_b200.h``) and the pybind11 module ``c_operators`` bound over it.
 
-There is no fallback: if the shared library is missing (and cannot be built
-because ``nvcc`` is absent) importing this module raises, and every operator
-raises :class:`FlagBlasError` when the library reports a non-zero status.
+The operators call through ``c_operators`` (``cop`` below); the ctypes handle ``lib`` exposes
+the same C symbols directly (used by tests that exercise the ABI itself).  There is no fallback:
+if the native code is missing (and cannot be built because ``nvcc`` / ``g++`` are absent)
+importing this module raises, and every operator raises :class:`FlagBlasError` when the library
+reports a non-zero status.
 """
 import ctypes
 import os
@@ -27,8 +30,8 @@ class FlagBlasError(RuntimeError):
 
 def _load():
     path = _build.LIB_PATH
-    if not os.path.exists(path):
-        # Source checkout without a built library: build it once (needs nvcc, not a GPU).
+    if not os.path.exists(path) or not os.path.exists(_build.EXT_PATH):
+        # Source checkout without built native code: build it once (needs nvcc and g++, not a GPU).
         _build.build()
     handle = ctypes.CDLL(path)
     c = ctypes
@@ -64,6 +67,7 @@ def _load():
 
 lib = None
 lib = _load()
+from . import c_operators as cop  # noqa: E402  (pybind11 module; links against the library loaded above)
 
 # Every symbol include/flagblas_b200.h declares; tests check the library exports them all.
 EXPORTED_SYMBOLS = (
@@ -90,4 +94,4 @@ def check(status, where=""):
 
 def device_status(reset=True):
     """Synchronise and return the device status word (0 = healthy)."""
-    return lib.fb_device_status(1 if reset else 0)
+    return cop.device_status(1 if reset else 0)

@@ -12,8 +12,8 @@ row-major matrices, ``ld*`` = row stride in elements, in place on ``C``.
 (``group_tf32gemm``, ``ops/level3/group_gemm.py:427-581``): fp32 storage, TF32
 tensor-core products, fp32 accumulation.
 
-The arithmetic runs in the native library through its C ABI (``fb_gemm``); this
-module only validates arguments the way the reference does and hands over raw
+The arithmetic runs in the native library through its C ABI (``fb_gemm``, reached via the
+pybind11 module ``c_operators``); this module only validates arguments the way the reference does and hands over raw
 addresses and the current CUDA stream.
 """
 import torch
@@ -21,7 +21,7 @@ import torch
 from ... import _lib
 from .._constants import CUBLAS_OP_N, CUBLAS_OP_T
 
-_lib_handle = _lib.lib
+_cop = _lib.cop
 
 
 def _scalar(x):
@@ -38,8 +38,7 @@ def _scale_whole(C, beta, code):
         stream = torch.cuda.current_stream().cuda_stream
         # k == 0 makes fb_gemm scale the (1 x numel) block by beta (zero-fill when beta == 0).
         _lib.check(
-            _lib_handle.fb_gemm(code, 0, 0, 1, numel, 0, 0.0, None, 1, None, numel, beta, C.data_ptr(), numel,
-                                None, 0, stream),
+            _cop.gemm(code, 0, 0, 1, numel, 0, 0.0, 0, 1, 0, numel, beta, C.data_ptr(), numel, 0, 0, stream),
             "scale",
         )
 
@@ -82,16 +81,16 @@ def _launch(code, name, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, 
     """Enqueue one fb_gemm on the current stream of ``device`` from raw addresses."""
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream().cuda_stream
-        ws_bytes = _lib_handle.fb_gemm_workspace_bytes(code, transa, transb, m, n, k, a_ptr, lda, b_ptr, ldb)
+        ws_bytes = _cop.gemm_workspace_bytes(code, transa, transb, m, n, k, a_ptr, lda, b_ptr, ldb)
         ws = None
-        ws_ptr = None
+        ws_ptr = 0
         if ws_bytes:
             # scratch comes from torch's caching allocator, ordered on the current stream
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
             ws_ptr = ws.data_ptr()
         _lib.check(
-            _lib_handle.fb_gemm(code, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, beta, c_ptr, ldc,
-                                ws_ptr, ws_bytes, stream),
+            _cop.gemm(code, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, beta, c_ptr, ldc, ws_ptr, ws_bytes,
+                      stream),
             name,
         )
 

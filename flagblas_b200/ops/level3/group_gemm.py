@@ -16,11 +16,11 @@ import torch
 
 from ... import _lib
 
-_lib_handle = _lib.lib
+_cop = _lib.cop
 
 
 def _workspace(device, groups):
-    nbytes = _lib_handle.fb_group_workspace_bytes(groups)
+    nbytes = _cop.group_workspace_bytes(groups)
     # tile table + per-group tensor maps, from torch's caching allocator (stream ordered)
     return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
 
@@ -40,7 +40,7 @@ def _group(code, b_k_contig, name, group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_ou
         stream = torch.cuda.current_stream().cuda_stream
         ws, nbytes = _workspace(dev, group_size)
         _lib.check(
-            _lib_handle.fb_group_gemm(code, b_k_contig, d_a_ptrs.data_ptr(), d_b_ptrs.data_ptr(), d_c_ptrs.data_ptr(),
+            _cop.group_gemm(code, b_k_contig, d_a_ptrs.data_ptr(), d_b_ptrs.data_ptr(), d_c_ptrs.data_ptr(),
                                       d_output_ptrs.data_ptr(), d_m_sizes.data_ptr(), d_n_sizes.data_ptr(),
                                       d_k_sizes.data_ptr(), d_ldas.data_ptr(), d_ldbs.data_ptr(), d_ldcs.data_ptr(),
                                       group_size, int(M), int(N), int(K), alpha, beta, ws.data_ptr(), nbytes, stream),
@@ -109,7 +109,7 @@ def group_mm(A: torch.Tensor, B: torch.Tensor, offs: torch.Tensor) -> torch.Tens
         stream = torch.cuda.current_stream().cuda_stream
         ws, nbytes = _workspace(A.device, num_groups)
         _lib.check(
-            _lib_handle.fb_group_mm(_CODES[A.dtype], b_k_contig, A.data_ptr(), A.stride(0), B.data_ptr(), ldb,
+            _cop.group_mm(_CODES[A.dtype], b_k_contig, A.data_ptr(), A.stride(0), B.data_ptr(), ldb,
                                     B.stride(0), C.data_ptr(), C.stride(0), offs.data_ptr(), num_groups, N, K,
                                     ws.data_ptr(), nbytes, stream),
             "group_mm",

@@ -202,7 +202,7 @@ def test_moe_config4_properties():
 def test_bounded_wait_reports_timeout():
     """A wait on a barrier nothing completes gives up after its limit and reports it; the
     context stays usable afterwards."""
-    assert fb.c_operators.fb_selftest_bounded_wait(20_000_000, None) == 105
+    assert fb.c_operators.selftest_bounded_wait(20_000_000, 0) == 105
     assert fb.device_status() == 0
     x = torch.ones(8, device=DEV)
     assert float(x.sum()) == 8.0
