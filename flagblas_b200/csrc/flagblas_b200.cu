@@ -209,7 +209,9 @@ static int choose_block_n(long long m, long long n, int tile_m, int workers, boo
   double best = 1e300;
   int best_bn = 256;
   const int cand[3] = {256, 128, 64};
-  const double eff[3] = {1.0, 0.88, 0.62};  // relative main-loop efficiency of the narrower tiles
+  // Relative main-loop efficiency of the narrower tiles (measured: per-stage copy and barrier costs do
+  // not shrink with the tile, so a 128-wide tile runs at little more than half the rate of a 256-wide one).
+  const double eff[3] = {1.0, 0.6, 0.35};
   for (int i = 0; i < (allow64 ? 3 : 2); ++i) {
     const long long tiles = tm * ((n + cand[i] - 1) / cand[i]);
     const long long waves = (tiles + workers - 1) / workers;
