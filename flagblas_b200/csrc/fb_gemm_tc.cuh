@@ -92,6 +92,15 @@ struct TcGemmParams {
   const GroupRec* groups;
   const int* total_tiles;        // device scalar written by the table builder
   const CUtensorMap* group_maps;  // [2 * num_groups]: A_g, B_g
+  // Stream-K tail (dense mode only).  When `sk_enabled`, every worker first takes `sk_dp` whole tiles
+  // (tile = worker + i * workers); the `sk_rem` tiles left over (fewer than there are workers) are
+  // cut into k-stage units and dealt out evenly, so that the last partial wave costs its share of a
+  // tile time instead of a whole one.  A tile split over several workers is finished by the worker
+  // that holds its first stages ("owner"); the others park their fp32 partial accumulators in
+  // `sk_partials` (one slot per worker) and raise `sk_flags[worker]`.
+  int sk_enabled, sk_dp, sk_rem;
+  float* sk_partials;  // [workers][tile rows][BLOCK_N]
+  int* sk_flags;       // [workers], zeroed before the launch
   // Profiling switches (results are meaningless when set): bit 0 = issue no MMA, bit 1 = issue no TMA copy.
   int debug;
   int stages;  // pipeline stages actually used (<= the compiled maximum)
@@ -180,6 +189,47 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       }
     }
   }
+}
+
+// One unit of work of a persistent worker: stages [sb, se) of the k loop of one output tile.
+enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2 };
+struct WorkItem {
+  int tile;
+  int sb, se;
+  int kind;
+};
+
+// The idx-th work item of `worker` in dense mode (see the stream-K fields of TcGemmParams).
+// `stages` = k-stages per tile.  Returns false when the worker has no idx-th item.
+__device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worker, int workers, int stages, int idx,
+                                                WorkItem& it) {
+  const int tiles = p.tiles_m * p.tiles_n;
+  if (!p.sk_enabled) {
+    it.tile = worker + idx * workers;
+    it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
+    return it.tile < tiles;
+  }
+  if (idx < p.sk_dp) {
+    it.tile = worker + idx * workers;
+    it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
+    return true;
+  }
+  const long long units = static_cast<long long>(p.sk_rem) * stages;
+  long long u = worker * units / workers;
+  const long long u1 = (worker + 1) * units / workers;
+  for (int q = 0; u < u1; ++q) {
+    const int tl = static_cast<int>(u / stages);
+    const int sb = static_cast<int>(u - static_cast<long long>(tl) * stages);
+    const long long len = min(static_cast<long long>(stages - sb), u1 - u);
+    if (q == idx - p.sk_dp) {
+      it.tile = p.sk_dp * workers + tl;
+      it.sb = sb; it.se = sb + static_cast<int>(len);
+      it.kind = sb > 0 ? ITEM_PARTIAL : (it.se < stages ? ITEM_OWNER : ITEM_FULL);
+      return true;
+    }
+    u += len;
+  }
+  return false;
 }
 
 // PAIR = true: two CTAs of a cluster work on one 256 x BLOCK_N tile with
@@ -274,6 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_holder;
 
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
+  const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
 
   if (warp == 0 || warp == 3) {
     // ----------------------------------------------------------- TMA producers
@@ -287,7 +338,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int g = 0;
       bool ok = true;
       long long prof_wait = 0, prof_issue = 0;
-      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+      for (int idx = 0; ok; ++idx) {
+        WorkItem item;
+        int t;
+        if (grouped) {
+          t = worker + idx * num_workers;
+          if (t >= num_tiles) break;
+        } else {
+          if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
+          t = item.tile;
+        }
         int tm, tn, kk_total;
         const CUtensorMap* map = load_a ? &tmA : &tmB;
         uint32_t use3d = og.use3d;
@@ -311,7 +371,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBRows;
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_begin = grouped ? 0 : item.sb, kb_end = grouped ? k_blocks : item.se;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
           const long long c1 = p.prof ? clock64() : 0;
@@ -393,13 +454,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gstart));
       bool data_ready = false;   // the current stage's barrier was already seen complete (and fenced)
       uint64_t a_desc = 0, b_desc = 0;  // descriptors of the current stage
-      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+      for (int idx = 0; ok; ++idx) {
+        WorkItem item;
+        int t;
+        if (grouped) {
+          t = worker + idx * num_workers;
+          if (t >= num_tiles) break;
+        } else {
+          if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
+          t = item.tile;
+        }
         int kk_total = p.k;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           kk_total = p.groups[g].k;
         }
-        const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+        const int k_blocks = grouped ? (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k)
+                                     : item.se - item.sb;  // stages of this work item
         // PAIR: the peer's epilogue warps arrive remotely -> cluster-scope acquire
         if (!mbar_test_wait(&tmem_empty_bar[acc], acc_phase ^ 1u) || PAIR) {
           const long long ct0 = p.prof ? clock64() : 0;
@@ -475,7 +546,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int g = 0;
     bool ok = true;
     long long prof_ewait = 0, prof_ebody = 0;
-    for (int t = worker; t < num_tiles && ok; t += num_workers) {
+    constexpr int kSkWarps = PAIR ? 8 : 4;  // epilogue warps that park one work item's partials
+    for (int idx = 0; ok; ++idx) {
+      WorkItem item;
+      item.kind = ITEM_FULL;
+      int t;
+      if (grouped) {
+        t = worker + idx * num_workers;
+        if (t >= num_tiles) break;
+      } else {
+        if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
+        t = item.tile;
+      }
       int tm, tn;
       int row_base = 0;
       Problem pr;
@@ -506,6 +588,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row = row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
+      // Stream-K: this thread's row inside a worker's partial slot, and for an owner the workers
+      // (worker + 1 .. sk_last) that hold the rest of the tile's k range.
+      const size_t sk_row_off = static_cast<size_t>(static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane) * BLOCK_N;
+      constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
+      int sk_last = worker;
+      if (item.kind == ITEM_OWNER) {
+        const long long units = static_cast<long long>(p.sk_rem) * dense_stages;
+        const long long tile_end = static_cast<long long>(t - p.sk_dp * num_workers + 1) * dense_stages;
+        while (sk_last + 1 < num_workers && (sk_last + 1) * units / num_workers < tile_end) ++sk_last;
+        // wait (bounded) until every contributor has parked its partial sums
+        uint32_t good = 1;
+        if (lane == 0) {
+          const long long w0 = clock64();
+          for (int v = worker + 1; v <= sk_last && good; ++v) {
+            while (true) {
+              int f;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.sk_flags + v) : "memory");
+              if (f >= kSkWarps) break;
+              if (*abort_flag) { good = 0; break; }
+              if (clock64() - w0 > FB_WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(&g_fb_status, 0, DEV_TIMEOUT_STREAMK_PARTIAL);
+                good = 0;
+                break;
+              }
+              __nanosleep(64);
+            }
+          }
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) ok = false;  // still drain TMEM below so that the MMA issuer is not left waiting
+      }
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N / 32; ++c) {
         uint32_t r[32];
@@ -514,6 +628,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (k_is_zero) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (item.kind == ITEM_OWNER && ok) {
+          for (int v = worker + 1; v <= sk_last; ++v) {
+            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot + sk_row_off + c * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 x = __ldcg(src + q);
+              r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
+              r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
+              r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
+              r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
+            }
+          }
         }
         if (c == BLOCK_N / 32 - 1) {
           // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
@@ -524,7 +651,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             else mbar_arrive(&tmem_empty_bar[acc]);
           }
         }
-        if (!(p.debug & 4)) epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
+        if (item.kind == ITEM_PARTIAL) {
+          // park the raw fp32 partial sums in this worker's slot
+          float4* dst = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot + sk_row_off + c * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            __stcg(dst + q, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
+                                        __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
+        } else if (!(p.debug & 4) && ok) {
+          epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
+        }
+      }
+      if (item.kind == ITEM_PARTIAL) {
+        __threadfence();  // the partial sums are visible GPU-wide before the flag says so
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.sk_flags + worker, 1);
       }
       if (p.prof) prof_ebody += clock64() - e1;
       acc ^= 1;

@@ -30,6 +30,7 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_EPI_TMEM_FULL = 104,   // epilogue waiting for the MMA to finish a tile
   DEV_TIMEOUT_TEST_FLAG = 105,       // self-test: a wait on a flag nothing sets
   DEV_TIMEOUT_PEER = 106,            // 2-CTA pair handshake
+  DEV_TIMEOUT_STREAMK_PARTIAL = 107, // stream-K owner waiting for another worker's partial sums
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

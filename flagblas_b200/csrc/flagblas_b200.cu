@@ -226,6 +226,13 @@ static int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+constexpr size_t kStreamKFlagBytes = 1024;  // one int per worker (at most 148), padded
+
+// Bytes of stream-K scratch for a dense call: one fp32 partial tile per worker plus the flags.
+static size_t streamk_bytes(int sm_count, int block_n) {
+  return static_cast<size_t>(sm_count) * kBlockM * block_n * sizeof(float) + kStreamKFlagBytes;
+}
+
 // Launch state kept per kernel instantiation and device.
 struct KernelState {
   bool attr_set = false;
@@ -276,6 +283,21 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     cfg.attrs = attrs; cfg.numAttrs = 1;
   }
   TcGemmParams pp = p;
+  pp.sk_enabled = 0;
+  if (p.num_groups == 0 && p.sk_partials && env_int("FLAGBLAS_B200_STREAMK", 0) != 0) {
+    // Stream-K tail (opt-in, FLAGBLAS_B200_STREAMK=1): for a partial last wave with few waves.  Measured
+    // slower than whole tiles on every shape tried so far (the owner's reduction of the parked partial
+    // sums is a chain of L2 round trips at the very end of the kernel), hence off by default.
+    const long long stages = (p.k + static_cast<long long>(p.block_k) - 1) / p.block_k;
+    const long long dp = tiles / workers, rem = tiles - dp * workers;
+    if (rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4 * workers) {
+      pp.sk_enabled = 1;
+      pp.sk_dp = static_cast<int>(dp);
+      pp.sk_rem = static_cast<int>(rem);
+      FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
+    }
+  }
+  if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
   pp.debug = env_int("FLAGBLAS_B200_DEBUG_SKIP", 0);
   const int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
   pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
@@ -383,6 +405,36 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   return FB_OK;
 }
 
+// Tile plan of a dense tensor-core call (shared by fb_gemm and fb_gemm_workspace_bytes).
+struct DensePlan {
+  bool pair;
+  int tile_m, block_n;
+  long long tiles;
+  bool want_streamk;  // the call can use stream-K scratch if the caller provides it
+};
+
+static DensePlan plan_dense(long long m, long long n, long long k, int esz, int sm_count) {
+  DensePlan pl{};
+  // CTA pairs (256-row tiles) whenever there is more than one 128-row block of C;
+  // FLAGBLAS_B200_PAIR=0/1 and FLAGBLAS_B200_BLOCK_N override the choice (profiling sweeps).
+  pl.pair = m > kBlockM;
+  const int force_pair = env_int("FLAGBLAS_B200_PAIR", -1);
+  if (force_pair == 0) pl.pair = false;
+  if (force_pair == 1) pl.pair = true;
+  pl.tile_m = pl.pair ? 2 * kBlockM : kBlockM;
+  const int workers = pl.pair ? sm_count / 2 : sm_count;
+  pl.block_n = choose_block_n(m, n, pl.tile_m, workers, !pl.pair);
+  const int force_bn = env_int("FLAGBLAS_B200_BLOCK_N", 0);
+  if (force_bn == 256 || force_bn == 128 || (force_bn == 64 && !pl.pair)) pl.block_n = force_bn;
+  pl.tiles = ((m + pl.tile_m - 1) / pl.tile_m) * ((n + pl.block_n - 1) / pl.block_n);
+  const long long span = kSwizzleBytes / esz;
+  const long long stages = (k + 2 * span - 1) / (2 * span);  // with two k-slabs per stage
+  const long long dp = pl.tiles / workers, rem = pl.tiles - dp * workers;
+  pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * workers &&
+                    env_int("FLAGBLAS_B200_STREAMK", 0) != 0;
+  return pl;
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -393,7 +445,15 @@ size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int
                                int64_t lda, const void* B, int64_t ldb) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
-  return pl.a_bytes + pl.b_bytes;
+  size_t bytes = pl.a_bytes + pl.b_bytes;
+  if (dtype != FB_F32) {
+    const DeviceInfo* di = device_info();
+    if (di) {
+      const DensePlan dp = plan_dense(m, n, k, elem_size(dtype), di->sm_count);
+      if (dp.want_streamk) bytes += streamk_bytes(di->sm_count, dp.block_n);
+    }
+  }
+  return bytes;
 }
 
 int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, float alpha, const void* A,
@@ -426,12 +486,14 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
                           static_cast<const float*>(B), ldb, beta, static_cast<float*>(C), ldc, di->sm_count, stream);
 
   const int esz = elem_size(dtype);
+  size_t ws_used = 0;  // bytes of the workspace taken by packed operands
   // Operands that TMA cannot address in place are packed to a 16-byte pitched copy first.
   const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
   if (pl.pack_a || pl.pack_b) {
     if (!workspace || workspace_bytes < pl.a_bytes + pl.b_bytes || (reinterpret_cast<uintptr_t>(workspace) & 255))
       return FB_ERR_WORKSPACE;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    ws_used = pl.a_bytes + pl.b_bytes;
     if (pl.pack_a) {
       int rc = esz == 2 ? run_pack<uint16_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream)
                         : run_pack<uint32_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream);
@@ -446,16 +508,10 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     }
   }
 
-  // CTA pairs (256-row tiles) whenever there is more than one 128-row block of C;
-  // FLAGBLAS_B200_PAIR=0/1 and FLAGBLAS_B200_BLOCK_N override the choice (profiling sweeps).
-  bool pair = m > kBlockM;
-  const int force_pair = env_int("FLAGBLAS_B200_PAIR", -1);
-  if (force_pair == 0) pair = false;
-  if (force_pair == 1) pair = true;
-  const int tile_m = pair ? 2 * kBlockM : kBlockM;
-  int block_n = choose_block_n(m, n, tile_m, pair ? di->sm_count / 2 : di->sm_count, !pair);
-  const int force_bn = env_int("FLAGBLAS_B200_BLOCK_N", 0);
-  if (force_bn == 256 || force_bn == 128 || (force_bn == 64 && !pair)) block_n = force_bn;
+  const DensePlan dplan = plan_dense(m, n, k, esz, di->sm_count);
+  const bool pair = dplan.pair;
+  const int tile_m = dplan.tile_m;
+  const int block_n = dplan.block_n;
   const int b_rows = pair ? block_n / 2 : block_n;  // rows of the B tile each CTA fetches
   const uint32_t span = kSwizzleBytes / esz;
   const bool a_mn = transa == FB_OP_T;  // stored [k, m]: M contiguous
@@ -515,6 +571,13 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
+  // Optional stream-K scratch behind the packed operands: used only when the caller provided it.
+  if (dplan.want_streamk && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
+      workspace_bytes >= ws_used + streamk_bytes(di->sm_count, block_n)) {
+    uint8_t* sk = static_cast<uint8_t*>(workspace) + ws_used;
+    p.sk_flags = reinterpret_cast<int*>(sk);
+    p.sk_partials = reinterpret_cast<float*>(sk + kStreamKFlagBytes);
+  }
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   return dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
 }

@@ -26,3 +26,40 @@ def test_dense_plan_variants(env, kind, monkeypatch):
         torch.cuda.synchronize()
         assert fb.device_status() == 0
         assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], result_scale(k, A, B, 1.5) + 0.5, "%s %s ta=%d tb=%d" % (kind, env, ta, tb))
+
+
+@pytest.mark.parametrize("kind,ta,tb,m,n,k", [
+    ("bf16", 0, 1, 1024, 1024, 4096),    # 16 pair tiles over all workers: every tile split ~5 ways
+    ("fp16", 0, 0, 4096, 4096, 1024),    # 3 whole waves + a 34-tile tail
+    ("bf16", 1, 0, 2304, 2048, 2048),    # ragged tail
+    ("tf32", 1, 0, 64, 8192, 8192),      # skinny: 64 single-CTA tiles spread over all SMs
+    ("tf32", 0, 1, 1000, 1536, 2000),    # edge tiles inside a split tile
+    ("bf16", 0, 0, 130, 4100, 6144),     # single-CTA tiles (m <= 128 ... two row blocks), ragged n
+])
+def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
+    """The opt-in stream-K schedule (FLAGBLAS_B200_STREAMK=1): shapes whose last wave is partial are
+    finished with k-split tiles (partial sums parked in the workspace, reduced by the tile's owner).
+    Same tolerance as every other dense test, and close agreement with the default whole-tile schedule."""
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=31, scale=0.25)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    outs = {}
+    for sk in ("1", "0"):
+        monkeypatch.setenv("FLAGBLAS_B200_STREAMK", sk)
+        Cd = C.to(DEV)
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        outs[sk] = Cd.float().cpu()
+    sc = result_scale(k, A, B, 1.5) + 0.5
+    # both schedules against fp64 on the GPU-resident data (the numpy oracle is too slow at these sizes)
+    opA = (Ad.t() if ta else Ad).double()
+    opB = (Bd.t() if tb else Bd).double()
+    if kind == "tf32":
+        trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+        opA, opB = trunc(opA), trunc(opB)
+    ref = (1.5 * (opA @ opB) + 0.5 * C.to(DEV).double()).float().cpu()
+    for sk in ("1", "0"):
+        assert_parity(outs[sk], ref, KINDS[kind][2], sc, "stream-k=%s %s %dx%dx%d" % (sk, kind, m, n, k))
+    # different summation order: the two schedules may differ by a rounding step of the output type
+    assert_parity(outs["1"], outs["0"], KINDS[kind][2], sc, "stream-k vs whole tiles")
