@@ -181,6 +181,20 @@ def other_configs(fb, torch, dev):
     ms = _time(lambda: fb.group_bfgemm(*args), torch)
     tf = 2.0 * T * N * K / (ms * 1e-3) / 1e12
     out["group_bfgemm_moe64"] = {"tflops": tf, "ms": ms, "bound": "tensor", "frac": tf / peak, "peak": peak}
+    del A, B, O
+    # matrix-vector products (the callers' decode-time shape): A read once, HBM bound
+    for op, dt in (("bfgemv", torch.bfloat16), ("sgemv", torch.float32)):
+        for trans in (0, 1):
+            m = n = 16384
+            g = torch.Generator(device=dev).manual_seed(5)
+            A = torch.randn(m, n, generator=g, device=dev).to(dt)
+            x = torch.randn(n, generator=g, device=dev).to(dt)
+            y = torch.zeros(m, device=dev, dtype=dt)
+            fn = getattr(fb, op)
+            ms = _time(lambda: fn(trans, m, n, 1.0, A, n, x, 1, 0.0, y, 1), torch)
+            gbs = A.element_size() * (m * n + m + n) / (ms * 1e-3) / 1e9
+            out["%s_16384_%s" % (op, "nt"[trans])] = {"ms": ms, "gbs": gbs, "bound": "hbm", "frac": gbs / hbm, "peak": hbm}
+            del A, x, y
     return out
 
 

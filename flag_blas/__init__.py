@@ -11,5 +11,6 @@ from flagblas_b200 import c_operators, device, ops, runtime, testing, vendor_nam
 
 sys.modules[__name__ + ".ops"] = ops
 sys.modules[__name__ + ".ops.level3"] = ops.level3
+sys.modules[__name__ + ".ops.level2"] = ops.level2
 sys.modules[__name__ + ".testing"] = testing
 sys.modules[__name__ + ".runtime"] = runtime

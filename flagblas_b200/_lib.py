@@ -40,6 +40,10 @@ def _load():
     handle.fb_gemm.argtypes = [i32, i32, i32, i64, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
     handle.fb_gemm_workspace_bytes.restype = sz
     handle.fb_gemm_workspace_bytes.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64]
+    handle.fb_gemv.restype = i32
+    handle.fb_gemv.argtypes = [i32, i32, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
+    handle.fb_gemv_workspace_bytes.restype = sz
+    handle.fb_gemv_workspace_bytes.argtypes = [i32, i32, i64, i64]
     handle.fb_group_gemm.restype = i32
     handle.fb_group_gemm.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp, sz, vp]
     handle.fb_group_gemm_no_alloc.restype = i32
@@ -73,6 +77,8 @@ from . import c_operators as cop  # noqa: E402  (pybind11 module; links against 
 EXPORTED_SYMBOLS = (
     "fb_gemm",
     "fb_gemm_workspace_bytes",
+    "fb_gemv",
+    "fb_gemv_workspace_bytes",
     "fb_group_gemm",
     "fb_group_mm",
     "fb_group_gemm_no_alloc",
@@ -85,6 +91,53 @@ EXPORTED_SYMBOLS = (
     "fb_selftest_bounded_wait",
     "fb_debug_set_profile_buffer",
 )
+
+
+# ---------------------------------------------------------------- per-call host plumbing
+# Kept as short as possible: for small problems the host side of a call costs more than the kernel.
+_scratch_cache = {}
+
+
+def enter(device):
+    """Make ``device`` current if it is not; returns (raw current stream of it, device to restore or -1)."""
+    import torch
+
+    idx = device.index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    cur = torch._C._cuda_getDevice()
+    prev = -1
+    if cur != idx:
+        torch.cuda.set_device(idx)
+        prev = cur
+    return torch._C._cuda_getCurrentRawStream(idx), prev
+
+
+def leave(prev):
+    if prev >= 0:
+        import torch
+
+        torch.cuda.set_device(prev)
+
+
+def scratch(device, stream, nbytes):
+    """Address of at least ``nbytes`` of device scratch tied to (device, stream).
+
+    One buffer per (device, stream) is kept and grown on demand: calls on one stream run in order, so
+    the next call may overwrite what the previous one left -- exactly the reuse rule of the C ABI's
+    workspace arguments.  Costs at most the largest request per stream for the life of the process.
+    """
+    if nbytes == 0:
+        return 0
+    key = (device.index, stream)
+    buf = _scratch_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        import torch
+
+        size = 1 << max(16, (nbytes - 1).bit_length())
+        buf = torch.empty(size, dtype=torch.uint8, device=device)
+        _scratch_cache[key] = buf
+    return buf.data_ptr()
 
 
 def check(status, where=""):

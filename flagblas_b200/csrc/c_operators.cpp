@@ -22,6 +22,12 @@ PYBIND11_MODULE(c_operators, m) {
   });
   m.def("gemm_workspace_bytes", [](int dtype, int ta, int tb, int64_t mm, int64_t nn, int64_t kk, addr a, int64_t lda, addr b,
                                    int64_t ldb) { return fb_gemm_workspace_bytes(dtype, ta, tb, mm, nn, kk, p(a), lda, p(b), ldb); });
+  m.def("gemv", [](int dtype, int trans, int64_t mm, int64_t nn, float alpha, addr a, int64_t lda, addr x, int64_t incx,
+                   float beta, addr y, int64_t incy, addr ws, size_t ws_bytes, addr stream) {
+    return fb_gemv(dtype, trans, mm, nn, alpha, p(a), lda, p(x), incx, beta, p(y), incy, p(ws), ws_bytes, p(stream));
+  });
+  m.def("gemv_workspace_bytes",
+        [](int dtype, int trans, int64_t mm, int64_t nn) { return fb_gemv_workspace_bytes(dtype, trans, mm, nn); });
   m.def("group_gemm", [](int dtype, int b_k_contig, addr da, addr db, addr dc, addr dout, addr dm, addr dn, addr dk, addr dlda,
                          addr dldb, addr dldc, int groups, int64_t mh, int64_t nh, int64_t kh, float alpha, float beta, addr ws,
                          size_t ws_bytes, addr stream) {

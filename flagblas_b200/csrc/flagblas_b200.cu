@@ -16,6 +16,7 @@ __device__ int g_fb_status = 0;
 #include "fb_gemm_tc.cuh"
 #include "fb_group_setup.cuh"
 #include "fb_sgemm_simt.cuh"
+#include "fb_gemv.cuh"
 
 namespace fb {
 
@@ -435,6 +436,119 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   return pl;
 }
 
+// ------------------------------------------------------------------- gemv
+// How a matrix-vector call is spread over the GPU (shared by fb_gemv and fb_gemv_workspace_bytes).
+struct GemvPlan {
+  int lanes;        // threads along the columns (per row block for N)
+  int threads;
+  int grid_x;
+  int splits;       // ranges of the reduced dimension; > 1 needs the fp32 partial buffer
+  long long chunk;  // reduced-dimension elements per range
+};
+
+static GemvPlan plan_gemv(int trans, long long m, long long n, int esz, int sms) {
+  GemvPlan pl{};
+  const long long E = 16 / esz;
+  const long long vec_cols = (n + E - 1) / E;
+  pl.threads = 256;
+  pl.splits = 1;
+  // FLAGBLAS_B200_GEMV_TX / _GEMV_SPLITS override the choices below (profiling sweeps).
+  const int force_tx = env_int("FLAGBLAS_B200_GEMV_TX", 0);
+  const int force_splits = env_int("FLAGBLAS_B200_GEMV_SPLITS", 0);
+  if (trans == FB_OP_N) {
+    int tx = 4;
+    while (tx < 256 && tx < vec_cols) tx *= 2;
+    if (force_tx >= 4 && force_tx <= 256 && (force_tx & (force_tx - 1)) == 0) tx = force_tx;
+    pl.lanes = tx;
+    const long long rows_per_cta = (256 / tx) * kGemvRows;
+    const long long row_ctas = (m + rows_per_cta - 1) / rows_per_cta;
+    pl.grid_x = static_cast<int>(row_ctas < 32LL * sms ? row_ctas : 32LL * sms);
+    pl.chunk = n;
+    const long long step = tx * E;  // columns one pass of a group covers
+    long long s = 1;
+    // Few row blocks and long rows: split the columns so that every SM gets work, as long as a
+    // range keeps at least eight passes.
+    if (row_ctas < sms) {
+      const long long by_work = (n + 8 * step - 1) / (8 * step);
+      const long long by_fill = (4LL * sms + row_ctas - 1) / row_ctas;
+      s = by_work < by_fill ? by_work : by_fill;
+    }
+    if (force_splits > 0) s = force_splits;
+    if (s > 1) {
+      long long chunk = (n + s - 1) / s;
+      chunk = (chunk + step - 1) / step * step;
+      pl.chunk = chunk;
+      pl.splits = static_cast<int>((n + chunk - 1) / chunk);
+    }
+  } else {
+    int tx = 1;
+    while (tx < 256 && tx < vec_cols) tx *= 2;
+    if (force_tx >= 1 && force_tx <= 256 && (force_tx & (force_tx - 1)) == 0) tx = force_tx;
+    pl.lanes = tx;
+    const long long ny = 256 / tx;
+    const long long col_ctas = (vec_cols + tx - 1) / tx;
+    pl.grid_x = static_cast<int>(col_ctas);
+    // measured on B200: 4 CTAs per SM are best for 16-bit types, 16 per SM for fp32
+    const long long want_t = (esz == 4 ? 16LL : 4LL) * sms;
+    const long long by_fill = (want_t + col_ctas - 1) / col_ctas;
+    const long long by_work = (m + 32 * ny - 1) / (32 * ny);  // at least 32 rows per thread
+    long long s = by_work < by_fill ? by_work : by_fill;
+    if (force_splits > 0) s = force_splits;
+    if (s < 1) s = 1;
+    if (s > 65535) s = 65535;
+    long long chunk = (m + s - 1) / s;
+    chunk = (chunk + ny - 1) / ny * ny;
+    pl.chunk = chunk;
+    pl.splits = static_cast<int>((m + chunk - 1) / chunk);
+  }
+  if (pl.splits < 1) pl.splits = 1;
+  return pl;
+}
+
+template <class T>
+static int run_gemv(int trans, long long m, long long n, float alpha, const void* A, long long lda, const void* x,
+                    long long incx, float beta, void* y, long long incy, void* workspace, size_t workspace_bytes,
+                    int sms, cudaStream_t stream) {
+  const long long len_y = trans == FB_OP_N ? m : n;
+  if (alpha == 0.f) {
+    if (beta == 1.f) return FB_OK;
+    gemv_scale_kernel<T><<<static_cast<unsigned>((len_y + 255) / 256), 256, 0, stream>>>(static_cast<T*>(y), len_y,
+                                                                                         incy, beta);
+    FB_CUDA_OK(cudaGetLastError());
+    return FB_OK;
+  }
+  const GemvPlan pl = plan_gemv(trans, m, n, sizeof(T), sms);
+  GemvParams p{};
+  p.m = static_cast<int>(m); p.n = static_cast<int>(n); p.lda = lda;
+  p.A = A; p.x = x; p.y = y; p.incx = incx; p.incy = incy;
+  p.alpha = alpha; p.beta = beta;
+  p.splits = pl.splits; p.chunk = pl.chunk; p.tx = pl.lanes;
+  p.a_vec = aligned16(A, lda, sizeof(T)) ? 1 : 0;
+  p.x_vec = (incx == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) ? 1 : 0;
+  if (pl.splits > 1) {
+    const size_t need = static_cast<size_t>(pl.splits) * static_cast<size_t>(len_y) * sizeof(float);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return FB_ERR_WORKSPACE;
+    p.partial = static_cast<float*>(workspace);
+  }
+  const dim3 grid(static_cast<unsigned>(pl.grid_x), static_cast<unsigned>(pl.splits));
+  if (trans == FB_OP_N) {
+    gemv_n_kernel<T><<<grid, 256, 0, stream>>>(p);
+  } else {
+    // rows in flight per thread; FLAGBLAS_B200_GEMV_U overrides (profiling sweeps)
+    const int u = env_int("FLAGBLAS_B200_GEMV_U", sizeof(T) == 4 ? 4 : 8);
+    if (u == 2) gemv_t_kernel<T, 2><<<grid, pl.threads, 0, stream>>>(p);
+    else if (u == 4) gemv_t_kernel<T, 4><<<grid, pl.threads, 0, stream>>>(p);
+    else gemv_t_kernel<T, 8><<<grid, pl.threads, 0, stream>>>(p);
+  }
+  FB_CUDA_OK(cudaGetLastError());
+  if (pl.splits > 1) {
+    gemv_finish_kernel<T><<<static_cast<unsigned>((len_y + 255) / 256), 256, 0, stream>>>(
+        p.partial, pl.splits, len_y, static_cast<T*>(y), incy, alpha, beta);
+    FB_CUDA_OK(cudaGetLastError());
+  }
+  return FB_OK;
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -786,6 +900,41 @@ int fb_group_gemm_no_alloc(int dtype, int b_k_contiguous, const int64_t* d_a, co
 }
 
 int fb_no_alloc_max_groups(void) { return kNoAllocMaxGroups; }
+
+size_t fb_gemv_workspace_bytes(int dtype, int trans, int64_t m, int64_t n) {
+  if (m <= 0 || n <= 0 || (dtype != FB_F32 && dtype != FB_F16 && dtype != FB_BF16)) return 0;
+  const DeviceInfo* di = device_info();
+  if (!di) return 0;
+  const GemvPlan pl = plan_gemv(trans, m, n, elem_size(dtype), di->sm_count);
+  if (pl.splits <= 1) return 0;
+  return static_cast<size_t>(pl.splits) * static_cast<size_t>(trans == FB_OP_N ? m : n) * sizeof(float);
+}
+
+int fb_gemv(int dtype, int trans, int64_t m, int64_t n, float alpha, const void* A, int64_t lda, const void* x,
+            int64_t incx, float beta, void* y, int64_t incy, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (dtype != FB_F32 && dtype != FB_F16 && dtype != FB_BF16) return FB_ERR_INVALID_ARG;
+  if (trans != FB_OP_N && trans != FB_OP_T) return FB_ERR_INVALID_ARG;
+  if (m < 0 || n < 0 || incx <= 0 || incy <= 0) return FB_ERR_INVALID_ARG;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return FB_OK;
+  if (!y) return FB_ERR_INVALID_ARG;
+  if (alpha != 0.f && (!A || !x || lda < n)) return FB_ERR_INVALID_ARG;
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+  switch (dtype) {
+    case FB_F16:
+      return run_gemv<__half>(trans, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes,
+                              di->sm_count, stream);
+    case FB_BF16:
+      return run_gemv<__nv_bfloat16>(trans, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes,
+                                     di->sm_count, stream);
+    default:
+      return run_gemv<float>(trans, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes,
+                             di->sm_count, stream);
+  }
+}
 
 const char* fb_status_string(int status) {
   switch (status) {

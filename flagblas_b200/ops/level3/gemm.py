@@ -34,13 +34,8 @@ def _scale_whole(C, beta, code):
     if beta == 1.0 or C.numel() == 0:
         return
     numel = C.numel()
-    with torch.cuda.device(C.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        # k == 0 makes fb_gemm scale the (1 x numel) block by beta (zero-fill when beta == 0).
-        _lib.check(
-            _cop.gemm(code, 0, 0, 1, numel, 0, 0.0, 0, 1, 0, numel, beta, C.data_ptr(), numel, 0, 0, stream),
-            "scale",
-        )
+    # k == 0 makes fb_gemm scale the (1 x numel) block by beta (zero-fill when beta == 0).
+    _launch(code, "scale", 0, 0, 1, numel, 0, 0.0, 0, 1, 0, numel, beta, C.data_ptr(), numel, C.device)
 
 
 def _validate(dtype, name, transa, transb, m, n, k, A, lda, B, ldb, C, ldc):
@@ -79,20 +74,17 @@ def _validate_extents(transa, transb, m, n, k, A, lda, B, ldb, C, ldc):
 
 def _launch(code, name, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, beta, c_ptr, ldc, device):
     """Enqueue one fb_gemm on the current stream of ``device`` from raw addresses."""
-    with torch.cuda.device(device):
-        stream = torch.cuda.current_stream().cuda_stream
+    stream, prev = _lib.enter(device)
+    try:
+        # packed copies of operands TMA cannot address in place, if any, go to per-stream scratch
         ws_bytes = _cop.gemm_workspace_bytes(code, transa, transb, m, n, k, a_ptr, lda, b_ptr, ldb)
-        ws = None
-        ws_ptr = 0
-        if ws_bytes:
-            # scratch comes from torch's caching allocator, ordered on the current stream
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
-            ws_ptr = ws.data_ptr()
-        _lib.check(
-            _cop.gemm(code, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, beta, c_ptr, ldc, ws_ptr, ws_bytes,
-                      stream),
-            name,
-        )
+        ws_ptr = _lib.scratch(device, stream, ws_bytes)
+        status = _cop.gemm(code, transa, transb, m, n, k, alpha, a_ptr, lda, b_ptr, ldb, beta, c_ptr, ldc, ws_ptr,
+                           ws_bytes, stream)
+    finally:
+        _lib.leave(prev)
+    if status:
+        _lib.check(status, name)
 
 
 def _gemm(code, dtype, name, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):

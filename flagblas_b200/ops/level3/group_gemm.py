@@ -19,12 +19,6 @@ from ... import _lib
 _cop = _lib.cop
 
 
-def _workspace(device, groups):
-    nbytes = _cop.group_workspace_bytes(groups)
-    # tile table + per-group tensor maps, from torch's caching allocator (stream ordered)
-    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
-
-
 def _group(code, b_k_contig, name, group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes,
            d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta):
     alpha = alpha.item() if isinstance(alpha, torch.Tensor) else float(alpha)
@@ -36,16 +30,18 @@ def _group(code, b_k_contig, name, group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_ou
     for t in (d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs):
         assert t.dtype == torch.int32 and t.is_cuda and t.is_contiguous() and t.numel() >= group_size
     dev = d_a_ptrs.device
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream().cuda_stream
-        ws, nbytes = _workspace(dev, group_size)
-        _lib.check(
-            _cop.group_gemm(code, b_k_contig, d_a_ptrs.data_ptr(), d_b_ptrs.data_ptr(), d_c_ptrs.data_ptr(),
-                                      d_output_ptrs.data_ptr(), d_m_sizes.data_ptr(), d_n_sizes.data_ptr(),
-                                      d_k_sizes.data_ptr(), d_ldas.data_ptr(), d_ldbs.data_ptr(), d_ldcs.data_ptr(),
-                                      group_size, int(M), int(N), int(K), alpha, beta, ws.data_ptr(), nbytes, stream),
-            name,
-        )
+    stream, prev = _lib.enter(dev)
+    try:
+        # tile table + per-group tensor maps live in per-stream scratch
+        nbytes = _cop.group_workspace_bytes(group_size)
+        ws_ptr = _lib.scratch(dev, stream, nbytes)
+        status = _cop.group_gemm(code, b_k_contig, d_a_ptrs.data_ptr(), d_b_ptrs.data_ptr(), d_c_ptrs.data_ptr(),
+                                 d_output_ptrs.data_ptr(), d_m_sizes.data_ptr(), d_n_sizes.data_ptr(),
+                                 d_k_sizes.data_ptr(), d_ldas.data_ptr(), d_ldbs.data_ptr(), d_ldcs.data_ptr(),
+                                 group_size, int(M), int(N), int(K), alpha, beta, ws_ptr, nbytes, stream)
+    finally:
+        _lib.leave(prev)
+    _lib.check(status, name)
     return group_out
 
 
@@ -105,15 +101,16 @@ def group_mm(A: torch.Tensor, B: torch.Tensor, offs: torch.Tensor) -> torch.Tens
     C = A.new_empty(M, N)
     if M == 0 or N == 0 or num_groups == 0:
         return C
-    with torch.cuda.device(A.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        ws, nbytes = _workspace(A.device, num_groups)
-        _lib.check(
-            _cop.group_mm(_CODES[A.dtype], b_k_contig, A.data_ptr(), A.stride(0), B.data_ptr(), ldb,
-                                    B.stride(0), C.data_ptr(), C.stride(0), offs.data_ptr(), num_groups, N, K,
-                                    ws.data_ptr(), nbytes, stream),
-            "group_mm",
-        )
+    stream, prev = _lib.enter(A.device)
+    try:
+        nbytes = _cop.group_workspace_bytes(num_groups)
+        ws_ptr = _lib.scratch(A.device, stream, nbytes)
+        status = _cop.group_mm(_CODES[A.dtype], b_k_contig, A.data_ptr(), A.stride(0), B.data_ptr(), ldb,
+                               B.stride(0), C.data_ptr(), C.stride(0), offs.data_ptr(), num_groups, N, K,
+                               ws_ptr, nbytes, stream)
+    finally:
+        _lib.leave(prev)
+    _lib.check(status, "group_mm")
     return C
 
 

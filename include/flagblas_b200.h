@@ -78,6 +78,28 @@ size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int
                                int64_t lda, const void* B, int64_t ldb);
 
 /*
+ * Matrix-vector product (the one-column limit of the GEMM path):
+ *     trans = N:  y[m] <- alpha * A * x[n]   + beta * y
+ *     trans = T:  y[n] <- alpha * A^T * x[m] + beta * y
+ *   A stored [m, lda>=n] row-major; x and y strided by incx, incy > 0 (elements).
+ *   dtype FB_F32 / FB_F16 / FB_BF16: storage type of A, x and y; products and sums in fp32,
+ *   alpha * acc + beta * y formed in fp32 and rounded once.  y is not read when beta == 0.
+ *   m == 0 or n == 0: nothing is done.  alpha == 0: the len_y strided elements of y are
+ *   scaled by beta (zero-filled when beta == 0) and A, x are not touched.
+ * Replaces the bodies of
+ *   sgemv   src/flag_blas/ops/level2/gemv.py:2285-2375
+ *   hgemv   src/flag_blas/ops/level2/gemv.py:2814-2926
+ *   bfgemv  src/flag_blas/ops/level2/gemv.py:2929-3041
+ * Shapes with few output elements per SM split the reduced dimension; they need
+ * fb_gemv_workspace_bytes(...) bytes of 16-byte aligned device scratch (0 otherwise).  The
+ * additions happen in a fixed order: results are reproducible from run to run.
+ */
+int fb_gemv(int dtype, int trans, int64_t m, int64_t n, float alpha, const void* A, int64_t lda, const void* x,
+            int64_t incx, float beta, void* y, int64_t incy, void* workspace, size_t workspace_bytes, void* stream);
+
+size_t fb_gemv_workspace_bytes(int dtype, int trans, int64_t m, int64_t n);
+
+/*
  * Grouped GEMM:  for g in [0, group_count):
  *     out_g[m_g,n_g] <- alpha * A_g[m_g,k_g] * B_g + beta * C_g
  *

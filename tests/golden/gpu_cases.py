@@ -54,6 +54,27 @@ def group_mm_case():
     return A, B, offs
 
 
+GEMV_KINDS = {"sgemv": "fp32", "hgemv": "fp16", "bfgemv": "bf16"}
+# (m, n, lda - n, incx, incy, alpha, beta): general, strided, the reference's split-K shapes
+# (m <= 64 and n >= 4096; the mirrored one for trans = T), its small power-of-two-n kernel, beta == 0.
+GEMV_SHAPES = ((70, 130, 6, 1, 1, 1.5, 0.5), (33, 47, 0, 2, 3, -0.75, 1.0), (48, 5000, 8, 1, 1, 1.5, 0.5),
+               (4200, 40, 0, 1, 1, 1.5, 0.5), (100, 16, 0, 1, 1, 2.0, 0.0))
+
+
+def gemv_cases(name):
+    """Yields (key, (trans, m, n, lda, incx, incy, alpha, beta), A, x, y) as CPU tensors."""
+    dt = DTYPES[GEMV_KINDS[name]]
+    gen = torch.Generator(device="cpu").manual_seed(36)
+    for trans in (0, 1):
+        for ci, (m, n, pad, incx, incy, alpha, beta) in enumerate(GEMV_SHAPES):
+            lda = n + pad
+            len_x, len_y = (n, m) if trans == 0 else (m, n)
+            A = torch.randn(m, lda, generator=gen).to(dt)
+            x = torch.randn(1 + (len_x - 1) * incx, generator=gen).to(dt)
+            y = torch.randn(1 + (len_y - 1) * incy, generator=gen).to(dt)
+            yield "gemv_%s_t%d_c%d" % (name, trans, ci), (trans, m, n, lda, incx, incy, alpha, beta), A, x, y
+
+
 def pack(t):
     """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
     if t.dtype in (torch.bfloat16, torch.float16):

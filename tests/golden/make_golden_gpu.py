@@ -7,12 +7,14 @@ cannot -- bfloat16 results and the TF32 rounding the reference's lowering applie
 Needs an installed copy of the reference (it is not shipped with this repo), e.g.
 
     python -m pip install --no-deps --no-build-isolation --target baseline/_ref /path/to/FlagBLAS
-    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py
+    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py          # gpu_reference.npz
+    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py gemv     # gpu_reference_gemv.npz
 
 and a CUDA device.  The same import shims as ``make_golden.py`` apply (stub ``sqlalchemy``,
 ``BLAS_VENDOR`` / ``ARCH`` / ``FLAGGEMS_DB_URL``, pass-through ``libentry`` that launches every kernel
 with the first configuration of its tuning list); only the *generic* kernels of
-``flag_blas.ops.level3`` are called (plain pointer kernels, one CTA per tile, no clusters).
+``flag_blas.ops.level3`` and the kernels of ``flag_blas.ops.level2.gemv`` are called (plain pointer
+kernels, one CTA per tile, no clusters).
 """
 import os
 import sys
@@ -109,7 +111,31 @@ def _import_reference():
     gg = sys.modules["flag_blas.ops.level3.group_gemm"]
     for name in ("group_bfgemm", "group_hgemm", "group_tf32gemm", "group_mm"):
         mods[name] = getattr(gg, name)
+    gv = sys.modules["flag_blas.ops.level2.gemv"]
+    for name in ("sgemv", "hgemv", "bfgemv"):
+        mods[name] = getattr(gv, name)
     return torch, mods
+
+
+def main_gemv():
+    """``gpu_reference_gemv.npz``: the reference's sgemv / hgemv / bfgemv on the seeded cases of gpu_cases."""
+    torch, ref = _import_reference()
+    sys.path.insert(0, HERE)
+    import gpu_cases as gc
+
+    dev = "cuda"
+    out = {"device": np.array(torch.cuda.get_device_name(0)), "triton": np.array(__import__("triton").__version__)}
+    for name in ("sgemv", "hgemv", "bfgemv"):
+        for key, (trans, m, n, lda, incx, incy, alpha, beta), A, x, y in gc.gemv_cases(name):
+            yd = y.to(dev)
+            ref[name](trans, m, n, alpha, A.to(dev), lda, x.to(dev), incx, beta, yd, incy)
+            torch.cuda.synchronize()
+            out[key + "_y"] = gc.pack(yd.cpu())
+            out[key + "_probe"] = np.concatenate([A.float().numpy().ravel()[:8], x.float().numpy().ravel()[:1]])
+        print("gemv", name, "done", flush=True)
+    path = os.path.join(HERE, "gpu_reference_gemv.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
 
 
 def main():
@@ -174,4 +200,7 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["gemv"]:
+        main_gemv()
+    else:
+        main()
