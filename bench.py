@@ -32,8 +32,11 @@ WORKLOADS = {
     "bfgemm_mlp_nt": ("bfgemm", "bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 1.0, 0.02, 2),
     "tf32gemm_skinny_tn": ("tf32gemm", "tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
     "tf32gemm_8192_tn": ("tf32gemm", "tf32", 1, 0, 8192, 8192, 8192, 1.5, 0.5, 0.577, 0.577, 4),
+    "tf32gemm_16384_tn": ("tf32gemm", "tf32", 1, 0, 16384, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
     "sgemm_512_nn": ("sgemm", "fp32", 0, 0, 512, 512, 512, 1.0, 0.0, 0.577, 0.577, 0),
 }
+# BASELINE config 4: 64 experts sharing K and N, token counts ~ Multinomial(T, Zipf(1.2)), seed 3
+MOE = {"name": "group_bfgemm_moe64", "experts": 64, "k": 4096, "n": 1536, "tokens": 32768, "zipf": 1.2, "seed": 3}
 HEADLINE = "hgemm_8192_nn"
 FALLBACK_TENSOR_PEAK = 1590.0  # TFLOP/s, earlier measurement on this pool, used only without MEASURED_PEAKS.json
 
@@ -163,10 +166,8 @@ def other_configs(fb, torch, dev):
         out[name] = rec
         del A, B, C
     # grouped MoE config: 64 experts, K=4096, N=1536, Zipf(1.2) token counts, bf16
-    E, K, N, T = 64, 4096, 1536, 32768
-    gc = torch.Generator().manual_seed(3)
-    w = torch.arange(1, E + 1, dtype=torch.float64) ** -1.2
-    ms_ = torch.multinomial(w / w.sum(), T, replacement=True, generator=gc).bincount(minlength=E).tolist()
+    E, K, N, T = MOE["experts"], MOE["k"], MOE["n"], MOE["tokens"]
+    ms_ = moe_token_counts(torch)
     g = torch.Generator(device=dev).manual_seed(3)
     A = torch.randn(T, K, generator=g, device=dev).bfloat16()
     B = (torch.randn(E * K, N, generator=g, device=dev) * 0.02).bfloat16()
@@ -198,11 +199,134 @@ def other_configs(fb, torch, dev):
     return out
 
 
+def moe_token_counts(torch):
+    w = torch.arange(1, MOE["experts"] + 1, dtype=torch.float64) ** -MOE["zipf"]
+    gc = torch.Generator().manual_seed(MOE["seed"])
+    return torch.multinomial(w / w.sum(), MOE["tokens"], replacement=True, generator=gc).bincount(minlength=MOE["experts"]).tolist()
+
+
+def run_grouped(args, rank, world, local_rank):
+    """BASELINE config 4 as the benchmarked workload: ``group_bfgemm`` over 64 experts.  With N > 1 ranks
+    the groups are dealt out by FLOPs (largest first, oversize groups cut into row slices); every rank
+    holds the tokens and weights, runs its pieces, and nothing is exchanged."""
+    import torch
+
+    import flagblas_b200 as fb
+    from flagblas_b200 import dist as fbdist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as tdist
+
+        tdist.init_process_group("nccl", device_id=dev)
+    E, K, N, T = MOE["experts"], MOE["k"], MOE["n"], MOE["tokens"]
+    ms_ = moe_token_counts(torch)
+    g = torch.Generator(device=dev).manual_seed(MOE["seed"])
+    A = torch.randn(T, K, generator=g, device=dev).bfloat16()
+    B = (torch.randn(E * K, N, generator=g, device=dev) * 0.02).bfloat16()
+    O = torch.full((T, N), float("nan"), device=dev, dtype=torch.bfloat16)
+    starts = [sum(ms_[:e]) for e in range(E)]
+    a_ptrs = [A.data_ptr() + s * K * 2 for s in starts]
+    b_ptrs = [B.data_ptr() + e * K * N * 2 for e in range(E)]
+    o_ptrs = [O.data_ptr() + s * N * 2 for s in starts]
+    plan = fbdist.plan_group_shards(ms_, [N] * E, [K] * E, world, row_align=256)
+    imbalance = fbdist.plan_imbalance(plan, ms_, [N] * E, [K] * E)
+    arrays, pieces = fbdist.shard_group_arrays(plan[rank], a_ptrs, b_ptrs, o_ptrs, o_ptrs, ms_, [N] * E, [K] * E,
+                                               [K] * E, [N] * E, [N] * E, 2, dev)
+    rows_here = sum(r for _, _, r in plan[rank])
+
+    def step():
+        if pieces:
+            fb.group_bfgemm(O, *arrays, pieces, rows_here, N, K, 1.0, 0.0)
+
+    def barrier():
+        if use_dist:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    def maxed(ms):
+        if use_dist:
+            t = torch.tensor([ms], device=dev)
+            tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    assert fb.device_status() == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms_step = maxed(e0.elapsed_time(e1)) / args.steps
+    flops = 2.0 * T * N * K
+    value = flops / (ms_step * 1e-3) / 1e12
+    status = fb.device_status()
+
+    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
+    hO = torch.empty(O.shape, dtype=O.dtype).pin_memory()
+
+    def e2e_step():
+        A.copy_(hA, non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        step()
+        hO.copy_(O, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = maxed(e0.elapsed_time(e1) / args.e2e_steps)
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        line = {
+            "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": MOE["name"], "op": "group_bfgemm", "experts": E, "k": K, "n": N, "tokens": T,
+                       "token_counts": "Multinomial(32768, Zipf(1.2)) seed 3", "alpha": 1.0, "beta": 0.0,
+                       "accumulate": "f32",
+                       "parallelism": "single GPU" if world == 1 else "groups dealt by FLOPs over %d GPUs (row slices of oversize groups), no collective; planned imbalance %.3f" % (world, imbalance),
+                       "l2": "per-GPU inputs (%.0f MiB) larger than L2; no flush between steps" % ((A.numel() + B.numel() + O.numel()) * 2 / 2**20)},
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                         "frac": value / world / peak, "traffic": ncu_traffic(MOE["name"]) if world == 1 else None,
+                         "peak_source": peak_src, "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (A.numel() + B.numel()) * 2, "d2h_bytes_per_step": O.numel() * 2,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": 2 * args.steps,  # table builder + GEMM kernel per step
+            "clocks": clk.summary(), "device_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import cpu_baseline
+
+            tf, rows, secs, threads = cpu_baseline.time_dense_rows(T, N, K, 0, 0, target_seconds=12.0, seed=MOE["seed"], scale=1.0)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": "torch.matmul fp32 on %d token rows against one expert's [4096, 1536] weights (inputs upcast), repeated for %.1f s" % (rows, secs)}
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        tdist.destroy_process_group()
+
+
 def run_reference(args, rank, world):
     """Reference arm: the path on the host cores (torch.matmul fp32 over a bounded row sample)."""
     if rank != 0:
         return
     from oracle import cpu_baseline
+
+    if args.workload == MOE["name"]:
+        WORKLOADS[MOE["name"]] = ("group_bfgemm", "bf16", 0, 0, MOE["tokens"], MOE["n"], MOE["k"], 1.0, 0.0, 1.0, 0.02, MOE["seed"])
 
     op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
     per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
@@ -231,7 +355,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS) + [MOE["name"]])
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
@@ -245,6 +369,9 @@ def main():
         run_reference(args, rank, world)
         return
     args.warmup = max(args.warmup, 3)
+    if args.workload == MOE["name"]:
+        run_grouped(args, rank, world, local_rank)
+        return
 
     import torch
 

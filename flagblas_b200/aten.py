@@ -1,0 +1,264 @@
+"""``torch``-level entry: serve ``aten::mm / addmm / bmm / mv / addmv`` on CUDA tensors with this library.
+
+Mirrors the registration scaffolding of the reference (``src/flag_blas/__init__.py:49-189``: ``enable``,
+``only_enable``, ``use_blas``, ``all_registered_ops``, ``all_registered_keys``; ``runtime/register.py:21-145``:
+the ``Register`` class walking a ``(aten key, function[, condition])`` table).  In the reference the table
+(``_FULL_CONFIG``) is empty, so nothing is ever registered; here it lists the five operators below.
+
+The functions take whatever strides ``torch`` hands them: a matrix that is row-major, or the transpose
+of a row-major matrix, is passed in place with ``trans = N / T`` and its pitch as the leading dimension;
+anything else is made contiguous first.  fp16 and bf16 run on the tensor cores with fp32 accumulation;
+fp32 runs the IEEE kernel unless ``torch.backends.cuda.matmul.allow_tf32`` is set, then the TF32 kernel.
+Other dtypes are not provided: leave them out with ``use_blas(exclude=...)`` / ``only_enable(include=...)``
+or keep such calls outside the ``with`` block.
+"""
+import warnings
+
+import torch
+
+from . import _lib
+from .ops._constants import CUBLAS_OP_N, CUBLAS_OP_T
+from .ops.level2 import gemv as _gemv
+from .ops.level3 import gemm as _gemm
+
+_cop = _lib.cop
+
+
+def _code(dtype):
+    if dtype == torch.float16:
+        return _lib.FB_F16
+    if dtype == torch.bfloat16:
+        return _lib.FB_BF16
+    if dtype == torch.float32:
+        return _lib.FB_TF32 if torch.backends.cuda.matmul.allow_tf32 else _lib.FB_F32
+    raise NotImplementedError("flag_blas aten overrides cover float16, bfloat16 and float32, not %s" % dtype)
+
+
+def as_operand(t):
+    """``(tensor, trans, ld)`` with ``op(row-major [rows, ld] storage at tensor.data_ptr()) == t``."""
+    r, c = t.shape
+    if r > 1 and c > 1:
+        if t.stride(1) == 1 and t.stride(0) >= c:
+            return t, CUBLAS_OP_N, t.stride(0)
+        if t.stride(0) == 1 and t.stride(1) >= r:
+            return t, CUBLAS_OP_T, t.stride(1)
+    t = t.contiguous()
+    return t, CUBLAS_OP_N, max(c, 1)
+
+
+def _mm_into(out, a, b, alpha, beta):
+    """out[m, n] (contiguous) <- alpha * a @ b + beta * out."""
+    m, k = a.shape
+    n = b.shape[1]
+    if m == 0 or n == 0:
+        return out
+    if k == 0:
+        return out.zero_() if beta == 0 else out.mul_(beta)
+    a, ta, lda = as_operand(a)
+    b, tb, ldb = as_operand(b)
+    _gemm._launch(_code(a.dtype), "aten::mm", ta, tb, m, n, k, float(alpha), a.data_ptr(), lda, b.data_ptr(), ldb,
+                  float(beta), out.data_ptr(), n, a.device)
+    return out
+
+
+def mm(self, mat2):
+    """aten::mm(Tensor self, Tensor mat2) -> Tensor"""
+    assert self.dim() == 2 and mat2.dim() == 2 and self.shape[1] == mat2.shape[0] and self.dtype == mat2.dtype
+    out = torch.empty((self.shape[0], mat2.shape[1]), dtype=self.dtype, device=self.device)
+    return _mm_into(out, self, mat2, 1.0, 0.0)
+
+
+def addmm(self, mat1, mat2, *, beta=1, alpha=1):
+    """aten::addmm(Tensor self, Tensor mat1, Tensor mat2, *, Scalar beta=1, Scalar alpha=1) -> Tensor"""
+    assert mat1.dim() == 2 and mat2.dim() == 2 and mat1.shape[1] == mat2.shape[0] and mat1.dtype == mat2.dtype
+    m, n = mat1.shape[0], mat2.shape[1]
+    if beta == 0:
+        out = torch.empty((m, n), dtype=mat1.dtype, device=mat1.device)  # self is not read, NaNs included
+    else:
+        out = self.to(mat1.dtype).expand(m, n).clone(memory_format=torch.contiguous_format)
+    return _mm_into(out, mat1, mat2, alpha, beta)
+
+
+def bmm(self, mat2):
+    """aten::bmm(Tensor self, Tensor mat2) -> Tensor: one GEMM per batch entry on the current stream."""
+    assert self.dim() == 3 and mat2.dim() == 3 and self.shape[0] == mat2.shape[0] and self.shape[2] == mat2.shape[1]
+    out = torch.empty((self.shape[0], self.shape[1], mat2.shape[2]), dtype=self.dtype, device=self.device)
+    for i in range(self.shape[0]):
+        _mm_into(out[i], self[i], mat2[i], 1.0, 0.0)
+    return out
+
+
+def _mv_into(out, a, x, alpha, beta):
+    m, n = a.shape
+    if m == 0:
+        return out
+    if n == 0:
+        return out.zero_() if beta == 0 else out.mul_(beta)
+    a, trans, lda = as_operand(a)
+    if x.stride(0) < 1:
+        x = x.contiguous()
+    code = _lib.FB_F32 if a.dtype == torch.float32 else _code(a.dtype)
+    # the stored matrix is [m, lda] (trans = N) or [n, lda] (trans = T, product with its transpose)
+    sm, sn = (m, n) if trans == CUBLAS_OP_N else (n, m)
+    _gemv._call(code, "aten::mv", trans, sm, sn, float(alpha), a.data_ptr(), lda, x.data_ptr(), x.stride(0),
+                float(beta), out.data_ptr(), 1, a.device)
+    return out
+
+
+def mv(self, vec):
+    """aten::mv(Tensor self, Tensor vec) -> Tensor"""
+    assert self.dim() == 2 and vec.dim() == 1 and self.shape[1] == vec.shape[0] and self.dtype == vec.dtype
+    out = torch.empty((self.shape[0],), dtype=self.dtype, device=self.device)
+    return _mv_into(out, self, vec, 1.0, 0.0)
+
+
+def addmv(self, mat, vec, *, beta=1, alpha=1):
+    """aten::addmv(Tensor self, Tensor mat, Tensor vec, *, Scalar beta=1, Scalar alpha=1) -> Tensor"""
+    assert mat.dim() == 2 and vec.dim() == 1 and mat.shape[1] == vec.shape[0] and mat.dtype == vec.dtype
+    if beta == 0:
+        out = torch.empty((mat.shape[0],), dtype=mat.dtype, device=mat.device)
+    else:
+        out = self.to(mat.dtype).expand(mat.shape[0]).clone(memory_format=torch.contiguous_format)
+    return _mv_into(out, mat, vec, alpha, beta)
+
+
+# (aten key, function[, condition]) -- the reference's `_FULL_CONFIG` format.
+_FULL_CONFIG = (
+    ("mm", mm),
+    ("addmm", addmm),
+    ("bmm", bmm),
+    ("mv", mv),
+    ("addmv", addmv),
+)
+FULL_CONFIG_BY_FUNC = {}
+for _item in _FULL_CONFIG:
+    FULL_CONFIG_BY_FUNC.setdefault(_item[1].__name__, []).append(_item)
+
+
+class Register:
+    """Registers the selected table entries into a ``torch.library.Library`` under the CUDA key."""
+
+    reg_key = "CUDA"
+
+    def __init__(self, config, user_include_ops=None, user_exclude_ops=None, cpp_patched_ops=None, lib=None,
+                 full_config_by_func=None):
+        self.lib = lib
+        self.all_ops = []
+        self.all_keys = []
+        include = list(user_include_ops or [])
+        self.exclude_ops = [] if include else list(user_exclude_ops or [])
+        patched = set(cpp_patched_ops or [])
+        self.config = []
+        for item in config:
+            key, fn = item[0], item[1]
+            if len(item) > 2 and not item[2]():
+                continue
+            if include:
+                if fn.__name__ not in include and key not in include:
+                    continue
+            elif fn.__name__ in self.exclude_ops or key in self.exclude_ops or key in patched:
+                continue
+            self.config.append((key, fn))
+        if include and not self.config:
+            warnings.warn("only_enable failed: No op to register. Check if include is correct.")
+        for key, fn in self.config:
+            self.register_impl(key, fn)
+
+    def register_impl(self, key, fn):
+        if self.lib is None:
+            raise ValueError("Library instance is not provided.")
+        self.lib.impl(key, fn, self.reg_key)
+        self.all_ops.append(fn.__name__)
+        self.all_keys.append(key)
+
+    def get_all_ops(self):
+        return self.all_ops
+
+    def get_all_keys(self):
+        return self.all_keys
+
+    def get_unused_ops(self):
+        return self.exclude_ops
+
+
+registrar = Register
+current_work_registrar = None
+_aten_lib = None
+
+
+def _default_lib():
+    global _aten_lib
+    if _aten_lib is None:
+        _aten_lib = torch.library.Library("aten", "IMPL")
+    return _aten_lib
+
+
+def _names(setting):
+    if setting is None or setting == "default":
+        return []
+    if isinstance(setting, str):
+        import yaml
+
+        with open(setting) as f:
+            data = yaml.safe_load(f) or {}
+        if isinstance(data, dict):
+            data = data.get("exclude") or data.get("include") or []
+        return list(data)
+    return list(setting)
+
+
+def enable(lib=None, unused=None, registrar=Register, record=False, once=False, path=None):
+    """Register every operator of the table except the names in ``unused`` (list, or a YAML path with an
+    ``exclude:`` list).  Registration lasts for the life of ``lib`` (default: a process-wide library)."""
+    global current_work_registrar
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)  # torch warns that an existing CUDA kernel is overridden
+        current_work_registrar = registrar(_FULL_CONFIG, user_include_ops=[], user_exclude_ops=_names(unused),
+                                           cpp_patched_ops=[], lib=lib if lib is not None else _default_lib())
+
+
+def only_enable(lib=None, include=None, registrar=Register, record=False, once=False, path=None):
+    """Register only the named operators (function names or aten keys)."""
+    names = _names(include)
+    if not names:
+        warnings.warn("only_enable failed: No include entries resolved from list or yaml.")
+        return
+    global current_work_registrar
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)
+        current_work_registrar = registrar(_FULL_CONFIG, user_include_ops=names, user_exclude_ops=[],
+                                           cpp_patched_ops=[], full_config_by_func=FULL_CONFIG_BY_FUNC,
+                                           lib=lib if lib is not None else _default_lib())
+
+
+class use_blas:
+    """``with flag_blas.use_blas(): ...`` -- the overrides are active inside the block only.
+    ``include`` has priority over ``exclude``, as in the reference."""
+
+    def __init__(self, exclude=None, include=None, record=False, once=False, path=None):
+        self.exclude = exclude if isinstance(exclude, (list, tuple, set, str)) else []
+        self.include = include if isinstance(include, (list, tuple, set, str)) else []
+        self.lib = None
+
+    def __enter__(self):
+        self.lib = torch.library.Library("aten", "IMPL")
+        if self.include:
+            only_enable(lib=self.lib, include=self.include)
+        else:
+            enable(lib=self.lib, unused=self.exclude)
+        return self
+
+    def __exit__(self, exc_type, exc_val, exc_tb):
+        global current_work_registrar
+        self.lib._destroy()
+        self.lib = None
+        current_work_registrar = None
+        return False
+
+
+def all_registered_ops():
+    return current_work_registrar.get_all_ops() if current_work_registrar else []
+
+
+def all_registered_keys():
+    return current_work_registrar.get_all_keys() if current_work_registrar else []

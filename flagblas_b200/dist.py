@@ -138,3 +138,27 @@ def plan_imbalance(plan, m_sizes, n_sizes, k_sizes) -> float:
     loads = [sum(2.0 * rows * n_sizes[g] * k_sizes[g] for g, _, rows in p) for p in plan]
     total = sum(loads)
     return max(loads) / (total / len(plan)) if total else 1.0
+
+
+def shard_group_arrays(pieces, a_ptrs, b_ptrs, c_ptrs, out_ptrs, m_sizes, n_sizes, k_sizes, ldas, ldbs, ldcs,
+                       elem_size: int, device):
+    """Device argument arrays of one rank's share of a grouped GEMM.
+
+    ``pieces`` is one entry of :func:`plan_group_shards` -- ``(group, row_start, rows)`` triples; the
+    other arguments are the *host* lists that describe the whole problem (addresses as ints).  A piece
+    is the row slice ``[row_start, row_start + rows)`` of its group: A, C and out advance by
+    ``row_start`` rows, B is shared.  Returns the eleven tensors ``group_bfgemm`` / ``group_hgemm`` /
+    ``group_tf32gemm`` take after ``group_out`` (int64 addresses, int32 sizes and strides) and the
+    piece count.
+    """
+    ap, bp, cp, op, ms, ns, ks, la, lb, lc = ([] for _ in range(10))
+    for g, start, rows in pieces:
+        ap.append(a_ptrs[g] + start * ldas[g] * elem_size)
+        bp.append(b_ptrs[g])
+        cp.append(c_ptrs[g] + start * ldcs[g] * elem_size)
+        op.append(out_ptrs[g] + start * ldcs[g] * elem_size)
+        ms.append(rows); ns.append(n_sizes[g]); ks.append(k_sizes[g])
+        la.append(ldas[g]); lb.append(ldbs[g]); lc.append(ldcs[g])
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=device)  # noqa: E731
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)  # noqa: E731
+    return (i64(ap), i64(bp), i64(cp), i64(op), i32(ms), i32(ns), i32(ks), i32(la), i32(lb), i32(lc)), len(pieces)

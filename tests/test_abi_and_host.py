@@ -137,3 +137,23 @@ def test_group_plan_balances_zipf():
             assert pos == m
         assert dist.plan_imbalance(plan, ms, n, k) < 1.03
     assert dist.plan_group_shards([0, 0], [8, 8], [8, 8], 2) == [[], []]
+
+
+def test_shard_group_arrays_addresses():
+    ms, n, k = [300, 0, 700], [64, 64, 64], [128, 128, 128]
+    plan = dist.plan_group_shards(ms, n, k, 2, row_align=256)
+    a = [1000, 2000, 3000]
+    b = [10, 20, 30]
+    o = [5000, 6000, 7000]
+    rows_seen = {0: 0, 2: 0}
+    for pieces in plan:
+        (ap, bp, cp, op, m_, n_, k_, la, lb, lc), cnt = dist.shard_group_arrays(
+            pieces, a, b, o, o, ms, n, k, k, n, n, 2, "cpu")
+        assert cnt == len(pieces) and ap.dtype == torch.int64 and m_.dtype == torch.int32
+        for i, (g, start, rows) in enumerate(pieces):
+            assert int(ap[i]) == a[g] + start * k[g] * 2          # A advances by whole rows of lda elements
+            assert int(bp[i]) == b[g]                              # B is shared by the slices of a group
+            assert int(op[i]) == o[g] + start * n[g] * 2 and int(cp[i]) == int(op[i])
+            assert int(m_[i]) == rows and int(n_[i]) == 64 and int(k_[i]) == 128
+            rows_seen[g] += rows
+    assert rows_seen == {0: 300, 2: 700}

@@ -1,0 +1,99 @@
+"""``flag_blas.use_blas()``: aten::mm / addmm / bmm / mv / addmv served by this library (reference
+scaffolding: src/flag_blas/__init__.py:49-189).  CPU part: table and stride logic.  GPU part: results
+inside the context against torch's own kernels outside it, and proof that the override really ran."""
+import pytest
+import torch
+
+import flagblas_b200 as fb
+from flagblas_b200 import aten
+
+
+def test_table_and_registrar_selection():
+    assert [k for k, _ in aten._FULL_CONFIG] == ["mm", "addmm", "bmm", "mv", "addmv"]
+
+    class FakeLib:
+        def __init__(self):
+            self.calls = []
+
+        def impl(self, key, fn, dispatch_key):
+            self.calls.append((key, fn.__name__, dispatch_key))
+
+    lib = FakeLib()
+    r = aten.Register(aten._FULL_CONFIG, user_exclude_ops=["bmm", "addmv"], lib=lib)
+    assert r.get_all_keys() == ["mm", "addmm", "mv"] and all(c[2] == "CUDA" for c in lib.calls)
+    lib = FakeLib()
+    r = aten.Register(aten._FULL_CONFIG, user_include_ops=["mv"], lib=lib)
+    assert r.get_all_ops() == ["mv"]
+    with pytest.raises(ValueError):
+        aten.Register(aten._FULL_CONFIG, lib=None)
+
+
+def test_as_operand_strides():
+    a = torch.zeros(6, 8)
+    t, trans, ld = aten.as_operand(a)
+    assert (trans, ld) == (0, 8) and t.data_ptr() == a.data_ptr()
+    t, trans, ld = aten.as_operand(a.t())                 # stored [6, 8], seen as [8, 6]
+    assert (trans, ld) == (1, 8) and t.data_ptr() == a.data_ptr()
+    t, trans, ld = aten.as_operand(a[:, :5])              # row-major with pitch 8
+    assert (trans, ld) == (0, 8)
+    t, trans, ld = aten.as_operand(a[::2, ::2])           # neither: copied
+    assert (trans, ld) == (0, 4) and t.is_contiguous()
+    t, trans, ld = aten.as_operand(torch.zeros(1, 8).expand(4, 8))
+    assert (trans, ld) == (0, 8) and t.is_contiguous()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_use_blas_serves_torch_matmul(dtype, monkeypatch):
+    dev = "cuda"
+    g = torch.Generator(device="cpu").manual_seed(0)
+    a = torch.randn(300, 200, generator=g).to(dtype).to(dev)
+    b = torch.randn(200, 136, generator=g).to(dtype).to(dev)
+    bt = torch.randn(136, 200, generator=g).to(dtype).to(dev)
+    bias = torch.randn(136, generator=g).to(dtype).to(dev)
+    x = torch.randn(200, generator=g).to(dtype).to(dev)
+    ba = torch.randn(3, 64, 200, generator=g).to(dtype).to(dev)
+    bb = torch.randn(3, 200, 72, generator=g).to(dtype).to(dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    want = [torch.mm(a, b), a @ bt.t(), torch.addmm(bias, a, b, beta=0.5, alpha=2.0), torch.bmm(ba, bb),
+            torch.mv(a, x), torch.mv(a.t(), torch.mv(a, x)), torch.addmv(torch.mv(a, x), a, x, beta=0.5, alpha=-1.0),
+            torch.nn.functional.linear(a, bt, bias)]
+    calls = {"gemm": 0, "gemv": 0}
+    real_gemm, real_gemv = aten._gemm._launch, aten._gemv._call
+    monkeypatch.setattr(aten._gemm, "_launch", lambda *p: (calls.__setitem__("gemm", calls["gemm"] + 1), real_gemm(*p))[1])
+    monkeypatch.setattr(aten._gemv, "_call", lambda *p: (calls.__setitem__("gemv", calls["gemv"] + 1), real_gemv(*p))[1])
+    with fb.use_blas():
+        assert fb.all_registered_keys() == ["mm", "addmm", "bmm", "mv", "addmv"]
+        got = [torch.mm(a, b), a @ bt.t(), torch.addmm(bias, a, b, beta=0.5, alpha=2.0), torch.bmm(ba, bb),
+               torch.mv(a, x), torch.mv(a.t(), torch.mv(a, x)), torch.addmv(torch.mv(a, x), a, x, beta=0.5, alpha=-1.0),
+               torch.nn.functional.linear(a, bt, bias)]
+        torch.cuda.synchronize()
+        inside = dict(calls)
+    assert inside["gemm"] >= 6 and inside["gemv"] >= 5
+    assert fb.all_registered_keys() == []
+    torch.mm(a, b)                                       # the library is gone: torch's own kernel again
+    assert calls == inside
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for w, gv in zip(want, got):
+        assert w.shape == gv.shape and w.dtype == gv.dtype
+        scale = float(w.float().abs().max())
+        assert float((w.float() - gv.float()).abs().max()) <= tol * scale * (4 if len(w.shape) == 1 else 1)
+    assert fb.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_use_blas_autograd_and_include():
+    dev = "cuda"
+    a = torch.randn(64, 96, device=dev, requires_grad=True)
+    b = torch.randn(96, 32, device=dev, requires_grad=True)
+    (a @ b).sum().backward()
+    ga, gb = a.grad.clone(), b.grad.clone()
+    a.grad = b.grad = None
+    with fb.use_blas(include=["mm"]):
+        assert fb.all_registered_ops() == ["mm"]
+        (a @ b).sum().backward()
+    torch.testing.assert_close(a.grad, ga, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(b.grad, gb, rtol=1e-5, atol=1e-4)
+    with fb.use_blas():
+        with pytest.raises(NotImplementedError):
+            torch.mm(a.double().detach(), b.double().detach())
