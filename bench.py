@@ -319,12 +319,91 @@ def run_grouped(args, rank, world, local_rank):
         tdist.destroy_process_group()
 
 
+GEMV = {  # name: (operator, torch dtype name, trans, m, n)
+    "bfgemv_16384_n": ("bfgemv", "bfloat16", 0, 16384, 16384), "bfgemv_16384_t": ("bfgemv", "bfloat16", 1, 16384, 16384),
+    "sgemv_16384_n": ("sgemv", "float32", 0, 16384, 16384), "sgemv_16384_t": ("sgemv", "float32", 1, 16384, 16384),
+}
+
+
+def run_gemv(args, local_rank):
+    """Matrix-vector workloads (single GPU): y = A x or A^T x, A 16384 x 16384 read once -- HBM bound."""
+    import torch
+
+    import flagblas_b200 as fb
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    op, dtn, trans, m, n = GEMV[args.workload]
+    dt = getattr(torch, dtn)
+    g = torch.Generator(device=dev).manual_seed(5)
+    A = torch.randn(m, n, generator=g, device=dev).to(dt)
+    x = torch.randn(m if trans else n, generator=g, device=dev).to(dt)
+    y = torch.full((n if trans else m,), float("nan"), device=dev, dtype=dt)
+    fn = getattr(fb, op)
+
+    def step():
+        fn(trans, m, n, 1.0, A, n, x, 1, 0.0, y, 1)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    nbytes = A.element_size() * (m * n + m + n)
+    hA = A.cpu().pin_memory()
+    hy = torch.empty(y.shape, dtype=dt).pin_memory()
+
+    def e2e_step():
+        A.copy_(hA, non_blocking=True)
+        step()
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm, src = float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except (OSError, KeyError, ValueError):
+        hbm, src = 6650.0, "fallback"
+    gbs = nbytes / (ms_step * 1e-3) / 1e9
+    ws = fb.c_operators.gemv_workspace_bytes({"bfloat16": 3, "float32": 0}[dtn], trans, m, n)
+    line = {
+        "metric": "gemm_tflops", "value": 2.0 * m * n / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": {"bfloat16": "bf16", "float32": "f32"}[dtn], "data": "synthetic",
+        "config": {"workload": args.workload, "op": op, "trans": trans, "m": m, "n": n, "alpha": 1.0, "beta": 0.0,
+                   "l2": "A (%.0f MiB) larger than L2; no flush between steps" % (A.numel() * A.element_size() / 2**20)},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                     "traffic": ncu_traffic(args.workload), "peak_source": src},
+        "e2e": {"value": 2.0 * m * n / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": A.numel() * A.element_size(), "d2h_bytes_per_step": y.numel() * y.element_size(),
+                "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps * (2 if ws else 1), "clocks": clk.summary(), "device_status": fb.device_status(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args, rank, world):
     """Reference arm: the path on the host cores (torch.matmul fp32 over a bounded row sample)."""
     if rank != 0:
         return
     from oracle import cpu_baseline
 
+    if args.workload in GEMV:
+        op_, _, tr_, m_, n_ = GEMV[args.workload]
+        WORKLOADS[args.workload] = (op_, "fp32", 0, 0, m_, 1, n_, 1.0, 0.0, 1.0, 1.0, 5)   # A x as an [m, n] x [n, 1] product
     if args.workload == MOE["name"]:
         WORKLOADS[MOE["name"]] = ("group_bfgemm", "bf16", 0, 0, MOE["tokens"], MOE["n"], MOE["k"], 1.0, 0.0, 1.0, 0.02, MOE["seed"])
 
@@ -355,7 +434,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS) + [MOE["name"]])
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS) + [MOE["name"]] + sorted(GEMV))
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
@@ -371,6 +450,10 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.workload == MOE["name"]:
         run_grouped(args, rank, world, local_rank)
+        return
+    if args.workload in GEMV:
+        if rank == 0:
+            run_gemv(args, local_rank)
         return
 
     import torch

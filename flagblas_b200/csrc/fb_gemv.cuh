@@ -71,8 +71,8 @@ __device__ __forceinline__ float dot16(const uint4& a, const uint4& b, float acc
 // warps, by a fixed-order pass over shared memory.
 constexpr int kGemvRows = 4;
 
-template <class T>
-__global__ void __launch_bounds__(256) gemv_n_kernel(const GemvParams p) {
+template <class T, int UNR, int MINB>
+__global__ void __launch_bounds__(256, MINB) gemv_n_kernel(const GemvParams p) {
   constexpr int E = 16 / sizeof(T);
   constexpr int R = kGemvRows;
   __shared__ float red[8][R];
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(256) gemv_n_kernel(const GemvParams p) {
     for (int r = 0; r < R; ++r) acc[r] = 0.f;
     long long c = c0 + static_cast<long long>(tx) * E;
     if (fast) {
-#pragma unroll 2
+#pragma unroll UNR
       for (; c + E <= c1; c += step) {
         uint4 a[R];
 #pragma unroll
@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(256) gemv_n_kernel(const GemvParams p) {
 // rows at a time -- a warp reads 512 contiguous bytes when the matrix is wide, and several whole rows
 // when it is narrow.  grid: (column panels of p.tx * E columns, splits over rows).  The ty partial sums
 // are combined through shared memory by a fixed-shape tree.
-template <class T, int U>
-__global__ void __launch_bounds__(256) gemv_t_kernel(const GemvParams p) {
+template <class T, int U, int MINB>
+__global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
   constexpr int E = 16 / sizeof(T);
   __shared__ float red[256 * E];
   const int tx = threadIdx.x & (p.tx - 1);

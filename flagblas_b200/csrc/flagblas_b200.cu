@@ -532,13 +532,23 @@ static int run_gemv(int trans, long long m, long long n, float alpha, const void
   }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), static_cast<unsigned>(pl.splits));
   if (trans == FB_OP_N) {
-    gemv_n_kernel<T><<<grid, 256, 0, stream>>>(p);
+    // variant = unroll * 10 + min CTAs per SM; FLAGBLAS_B200_GEMV_NV overrides (profiling sweeps)
+    switch (env_int("FLAGBLAS_B200_GEMV_NV", 24)) {
+      case 16: gemv_n_kernel<T, 1, 6><<<grid, 256, 0, stream>>>(p); break;
+      case 18: gemv_n_kernel<T, 1, 8><<<grid, 256, 0, stream>>>(p); break;
+      case 25: gemv_n_kernel<T, 2, 5><<<grid, 256, 0, stream>>>(p); break;
+      case 26: gemv_n_kernel<T, 2, 6><<<grid, 256, 0, stream>>>(p); break;
+      default: gemv_n_kernel<T, 2, 4><<<grid, 256, 0, stream>>>(p); break;
+    }
   } else {
-    // rows in flight per thread; FLAGBLAS_B200_GEMV_U overrides (profiling sweeps)
-    const int u = env_int("FLAGBLAS_B200_GEMV_U", sizeof(T) == 4 ? 4 : 8);
-    if (u == 2) gemv_t_kernel<T, 2><<<grid, pl.threads, 0, stream>>>(p);
-    else if (u == 4) gemv_t_kernel<T, 4><<<grid, pl.threads, 0, stream>>>(p);
-    else gemv_t_kernel<T, 8><<<grid, pl.threads, 0, stream>>>(p);
+    // variant = rows in flight per thread * 10 + min CTAs per SM; FLAGBLAS_B200_GEMV_TV overrides
+    switch (env_int("FLAGBLAS_B200_GEMV_TV", sizeof(T) == 4 ? 46 : 85)) {
+      case 46: gemv_t_kernel<T, 4, 6><<<grid, pl.threads, 0, stream>>>(p); break;
+      case 48: gemv_t_kernel<T, 4, 8><<<grid, pl.threads, 0, stream>>>(p); break;
+      case 28: gemv_t_kernel<T, 2, 8><<<grid, pl.threads, 0, stream>>>(p); break;
+      case 86: gemv_t_kernel<T, 8, 6><<<grid, pl.threads, 0, stream>>>(p); break;
+      default: gemv_t_kernel<T, 8, 5><<<grid, pl.threads, 0, stream>>>(p); break;
+    }
   }
   FB_CUDA_OK(cudaGetLastError());
   if (pl.splits > 1) {
