@@ -14,6 +14,7 @@ from . import build as _build
 
 FB_F32, FB_TF32, FB_F16, FB_BF16 = 0, 1, 2, 3
 FB_OK = 0
+FB_FP8_E4M3, FB_FP8_E5M2 = 0, 1
 
 
 class FlagBlasError(RuntimeError):
@@ -44,6 +45,10 @@ def _load():
     handle.fb_gemv.argtypes = [i32, i32, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
     handle.fb_gemv_workspace_bytes.restype = sz
     handle.fb_gemv_workspace_bytes.argtypes = [i32, i32, i64, i64]
+    handle.fb_gemv_fp8.restype = i32
+    handle.fb_gemv_fp8.argtypes = [i32, i32, i32, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
+    handle.fb_gemv_fp8_workspace_bytes.restype = sz
+    handle.fb_gemv_fp8_workspace_bytes.argtypes = [i64, i64]
     handle.fb_group_gemm.restype = i32
     handle.fb_group_gemm.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp, sz, vp]
     handle.fb_group_gemm_no_alloc.restype = i32
@@ -79,6 +84,8 @@ EXPORTED_SYMBOLS = (
     "fb_gemm_workspace_bytes",
     "fb_gemv",
     "fb_gemv_workspace_bytes",
+    "fb_gemv_fp8",
+    "fb_gemv_fp8_workspace_bytes",
     "fb_group_gemm",
     "fb_group_mm",
     "fb_group_gemm_no_alloc",

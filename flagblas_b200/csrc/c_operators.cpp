@@ -28,6 +28,11 @@ PYBIND11_MODULE(c_operators, m) {
   });
   m.def("gemv_workspace_bytes",
         [](int dtype, int trans, int64_t mm, int64_t nn) { return fb_gemv_workspace_bytes(dtype, trans, mm, nn); });
+  m.def("gemv_fp8", [](int a_fmt, int x_fmt, int y_dtype, int64_t mm, int64_t nn, float alpha, addr a, int64_t lda, addr x,
+                       int64_t incx, float beta, addr y, int64_t incy, addr ws, size_t ws_bytes, addr stream) {
+    return fb_gemv_fp8(a_fmt, x_fmt, y_dtype, mm, nn, alpha, p(a), lda, p(x), incx, beta, p(y), incy, p(ws), ws_bytes, p(stream));
+  });
+  m.def("gemv_fp8_workspace_bytes", [](int64_t mm, int64_t nn) { return fb_gemv_fp8_workspace_bytes(mm, nn); });
   m.def("group_gemm", [](int dtype, int b_k_contig, addr da, addr db, addr dc, addr dout, addr dm, addr dn, addr dk, addr dlda,
                          addr dldb, addr dldc, int groups, int64_t mh, int64_t nh, int64_t kh, float alpha, float beta, addr ws,
                          size_t ws_bytes, addr stream) {

@@ -250,8 +250,15 @@ struct TcCfg {
                                      ? 8
                                      : (kSmemLimit - 1024 - kCtlBytes) / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kCtlBytes + 1024;
-  static constexpr int kTmemCols = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+  // One MMA instruction covers at most 256 columns; a 512-wide tile is two halves side by side in
+  // TMEM and fills all 512 columns, so its accumulator cannot be double buffered.
+  static constexpr int kMmaN = BLOCK_N > 256 ? 256 : BLOCK_N;
+  static constexpr int kHalves = BLOCK_N / kMmaN;
+  static constexpr int kAccBufs = BLOCK_N > 256 ? 1 : 2;
+  static constexpr int kTmemCols = kAccBufs * BLOCK_N < 32 ? 32 : kAccBufs * BLOCK_N;
+  static constexpr int kHalfBBytes = kBBytes / kHalves;  // bytes of one half of this CTA's B slab
   static constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;  // rows of C per scheduled tile
+  static_assert(BLOCK_N <= 256 || PAIR, "512-wide tiles exist only as CTA-pair tiles");
 };
 
 // g_fb_status (the device status word) is defined by the including translation unit.
@@ -369,7 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // first row (A) / first column (B) of the operand slab this CTA fetches
         const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
-                               : tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::kBRows;
+                               : tn * BLOCK_N + static_cast<int>(cta_rank) * (Cfg::kBRows / Cfg::kHalves);
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
         const int kb_begin = grouped ? 0 : item.sb, kb_end = grouped ? k_blocks : item.se;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -389,11 +396,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if (!(p.debug & 2)) {
             if (use3d) {
-              // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row
-              const int y = og.mn_major ? k0 : mn0;
-              const int z = og.mn_major ? mn0 / static_cast<int>(og.span) : k0 / static_cast<int>(og.span);
-              if constexpr (PAIR) tma_load_3d_pair(dst, map, bar, 0, y, z);
-              else tma_load_3d(dst, map, &full_bar[stage], 0, y, z);
+              // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row.
+              // A 512-wide tile's B stage is two halves, each laid out like a 256-wide tile's B stage
+              // (this CTA's 128 columns of tile columns [256 h, 256 h + 256)), fetched by one copy each.
+              const int halves = load_a ? 1 : Cfg::kHalves;
+              for (int h = 0; h < halves; ++h) {
+                const int mn = mn0 + h * Cfg::kMmaN;
+                const int y = og.mn_major ? k0 : mn;
+                const int z = og.mn_major ? mn / static_cast<int>(og.span) : k0 / static_cast<int>(og.span);
+                uint8_t* d = dst + h * p.ks * Cfg::kHalfBBytes;
+                if constexpr (PAIR) tma_load_3d_pair(d, map, bar, 0, y, z);
+                else tma_load_3d(d, map, &full_bar[stage], 0, y, z);
+              }
             } else if (og.mn_major) {
               // one box per 128-byte chunk of MN, each holding every k row of the stage
               for (uint32_t bx = 0; bx < og.boxes; ++bx) {
@@ -437,13 +451,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t acc_phase = 0;
       int g = 0;
       bool ok = true;
-      constexpr int kMaxMma = 8;  // 4 per k-slab, at most 2 slabs per stage
-      const int n_mma = 4 * static_cast<int>(p.ks);
+      constexpr int kH = Cfg::kHalves;
+      constexpr int kMaxMma = 8 * kH;  // 4 k-steps per k-slab, at most 2 slabs per stage, kH column halves
+      const int n_mma = 4 * static_cast<int>(p.ks) * kH;
       uint32_t off_a[kMaxMma], off_b[kMaxMma];  // descriptor start-address offsets (16-byte units) of each MMA of a stage
 #pragma unroll
       for (int j = 0; j < kMaxMma; ++j) {
-        off_a[j] = ((j >> 2) * p.a.slab_adv_bytes + (j & 3) * p.a.k_adv_bytes) >> 4;
-        off_b[j] = ((j >> 2) * p.b.slab_adv_bytes + (j & 3) * p.b.k_adv_bytes) >> 4;
+        // j = (slab, k-step, half): both halves of a k-step follow each other and share the A operand
+        const int half = j % kH, step = (j / kH) & 3, slab = j / (4 * kH);
+        off_a[j] = (slab * p.a.slab_adv_bytes + step * p.a.k_adv_bytes) >> 4;
+        off_b[j] = (half * p.ks * Cfg::kHalfBBytes + slab * p.b.slab_adv_bytes + step * p.b.k_adv_bytes) >> 4;
       }
       const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a), p.a.lbo, p.a.sbo, p.a.layout);
       const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b), p.b.lbo, p.b.sbo, p.b.layout);
@@ -496,9 +513,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < kMaxMma; ++j) {
             if (j < n_mma) {
               if (!(p.debug & 1)) {
-                const uint32_t accum = (kb | j) != 0 ? 1u : 0u;
-                if constexpr (PAIR) umma_pair<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
-                else umma<kTf32>(d_tmem, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
+                const uint32_t accum = (kb | (j / kH)) != 0 ? 1u : 0u;  // first k-step of the tile overwrites
+                const uint32_t d_half = d_tmem + static_cast<uint32_t>((j % kH) * Cfg::kMmaN);
+                if constexpr (PAIR) umma_pair<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
+                else umma<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
               }
               if (j == n_mma - 2) {
                 // Slot before the last MMA: everything the next stage needs, so that its first MMA
@@ -526,8 +544,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // Tile done: publish the accumulator to the epilogue (of both CTAs of a pair).
         if constexpr (PAIR) umma_commit_pair(&tmem_full_bar[acc], 3);
         else umma_commit(&tmem_full_bar[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
       }
       if (p.prof && blockIdx.x == 0) {
         p.prof[2] = prof_wfull; p.prof[5] = prof_wtmem;
@@ -668,8 +685,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) atomicAdd(p.sk_flags + worker, 1);
       }
       if (p.prof) prof_ebody += clock64() - e1;
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.prof && blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) { p.prof[7] = prof_ewait; p.prof[8] = prof_ebody; }
   }

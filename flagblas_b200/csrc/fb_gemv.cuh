@@ -16,9 +16,27 @@
 // of the additions is fixed, so results are reproducible run to run.
 #pragma once
 
+#include <cuda_fp8.h>
+
 #include "fb_gemm_tc.cuh"
 
 namespace fb {
+
+__device__ __forceinline__ float to_f32(__nv_fp8_e4m3 v) { return static_cast<float>(v); }
+__device__ __forceinline__ float to_f32(__nv_fp8_e5m2 v) { return static_cast<float>(v); }
+
+// One element through the read-only path, as fp32.
+template <class T> __device__ __forceinline__ float ld_f32(const T* p) { return to_f32(__ldg(p)); }
+template <> __device__ __forceinline__ float ld_f32<__nv_fp8_e4m3>(const __nv_fp8_e4m3* p) {
+  __nv_fp8_e4m3 v;
+  v.__x = __ldg(reinterpret_cast<const unsigned char*>(p));
+  return to_f32(v);
+}
+template <> __device__ __forceinline__ float ld_f32<__nv_fp8_e5m2>(const __nv_fp8_e5m2* p) {
+  __nv_fp8_e5m2 v;
+  v.__x = __ldg(reinterpret_cast<const unsigned char*>(p));
+  return to_f32(v);
+}
 
 struct GemvParams {
   int m, n;
@@ -49,6 +67,45 @@ __device__ __forceinline__ void load_vec(const T* __restrict__ p, int valid, boo
 #pragma unroll
     for (int j = 0; j < E; ++j) out[j] = j < valid ? to_f32(p[j]) : 0.f;
   }
+}
+
+// acc[j] += element j of the 16-byte vector `raw` (type T) * xs, in fp32.
+template <class T>
+__device__ __forceinline__ void fma_vec(const uint4& raw, float xs, float (&acc)[16 / sizeof(T)]) {
+  constexpr int E = 16 / sizeof(T);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int j = 0; j < E; ++j) acc[j] = fmaf(to_f32(e[j]), xs, acc[j]);
+}
+
+// fp32 += fp16 * fp16 in one instruction (the product of two fp16 values is exact in fp32).
+__device__ __forceinline__ float fma_f32_f16(unsigned short a, unsigned short b, float c) {
+  float d;
+  asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  return d;
+}
+
+// FP8: converting 16 elements one by one to fp32 costs more issue slots than the memory system leaves
+// room for.  Pairs are converted to fp16x2 (exact) and fed to the mixed-precision FMA together with x
+// as fp16 (x comes from an FP8 value, so that conversion is exact too).
+template <__nv_fp8_interpretation_t FMT>
+__device__ __forceinline__ void fma_vec_fp8(const uint4& raw, float xs, float (&acc)[16]) {
+  const unsigned short xh = __half_as_ushort(__float2half_rn(xs));
+  const unsigned short* pairs = reinterpret_cast<const unsigned short*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(pairs[q], FMT);
+    acc[2 * q] = fma_f32_f16(h2.x, xh, acc[2 * q]);
+    acc[2 * q + 1] = fma_f32_f16(h2.y, xh, acc[2 * q + 1]);
+  }
+}
+template <>
+__device__ __forceinline__ void fma_vec<__nv_fp8_e4m3>(const uint4& raw, float xs, float (&acc)[16]) {
+  fma_vec_fp8<__NV_E4M3>(raw, xs, acc);
+}
+template <>
+__device__ __forceinline__ void fma_vec<__nv_fp8_e5m2>(const uint4& raw, float xs, float (&acc)[16]) {
+  fma_vec_fp8<__NV_E5M2>(raw, xs, acc);
 }
 
 // Dot product of two 16-byte vectors of T, accumulated in fp32.
@@ -115,7 +172,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_n_kernel(const GemvParams p) {
       float xv[E];
       const int valid = static_cast<int>(min(static_cast<long long>(E), c1 - c));
 #pragma unroll
-      for (int j = 0; j < E; ++j) xv[j] = j < valid ? to_f32(__ldg(x + (c + j) * p.incx)) : 0.f;
+      for (int j = 0; j < E; ++j) xv[j] = j < valid ? ld_f32(x + (c + j) * p.incx) : 0.f;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float a[E];
@@ -178,7 +235,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_n_kernel(const GemvParams p) {
 // rows at a time -- a warp reads 512 contiguous bytes when the matrix is wide, and several whole rows
 // when it is narrow.  grid: (column panels of p.tx * E columns, splits over rows).  The ty partial sums
 // are combined through shared memory by a fixed-shape tree.
-template <class T, int U, int MINB>
+template <class T, int U, int MINB, class TX = T, class TY = T>
 __global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
   constexpr int E = 16 / sizeof(T);
   __shared__ float red[256 * E];
@@ -191,7 +248,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
   const bool live = col < p.n;
   const int valid = live ? static_cast<int>(min(static_cast<long long>(E), p.n - col)) : 0;
   const T* A = static_cast<const T*>(p.A) + col;
-  const T* x = static_cast<const T*>(p.x);
+  const TX* x = static_cast<const TX*>(p.x);
   const bool vec = p.a_vec != 0;
   float acc[E];
 #pragma unroll
@@ -206,19 +263,15 @@ __global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
 #pragma unroll
         for (int u = 0; u < U; ++u) a[u] = __ldcs(reinterpret_cast<const uint4*>(A + (r + u * ny) * p.lda));
 #pragma unroll
-        for (int u = 0; u < U; ++u) xs[u] = to_f32(__ldg(x + (r + u * ny) * p.incx));
+        for (int u = 0; u < U; ++u) xs[u] = ld_f32(x + (r + u * ny) * p.incx);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const T* e = reinterpret_cast<const T*>(&a[u]);
-#pragma unroll
-          for (int j = 0; j < E; ++j) acc[j] = fmaf(to_f32(e[j]), xs[u], acc[j]);
-        }
+        for (int u = 0; u < U; ++u) fma_vec<T>(a[u], xs[u], acc);
       }
     }
     for (; r < r1; r += ny) {
       float a0[E];
       load_vec<T>(A + r * p.lda, valid, vec, a0);
-      const float x0 = to_f32(__ldg(x + r * p.incx));
+      const float x0 = ld_f32(x + r * p.incx);
 #pragma unroll
       for (int j = 0; j < E; ++j) acc[j] = fmaf(a0[j], x0, acc[j]);
     }
@@ -247,33 +300,43 @@ __global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
       if (p.splits > 1) {
         p.partial[static_cast<long long>(blockIdx.y) * p.n + col + j] = acc[j];
       } else {
-        T* yp = static_cast<T*>(p.y) + (col + j) * p.incy;
+        TY* yp = static_cast<TY*>(p.y) + (col + j) * p.incy;
         float v = p.alpha * acc[j];
         if (p.beta != 0.f) v += p.beta * to_f32(*yp);
-        *yp = from_f32<T>(v);
+        *yp = from_f32<TY>(v);
       }
     }
   }
 }
 
 // y[i] = alpha * sum_s partial[s][i] + beta * y[i]
+// 256 threads = 32 outputs x 8 slices of the split index: a thread adds every eighth partial sum of its
+// output (independent loads, all in flight together), the eight slice sums are then added in slice
+// order.  The association is fixed by (splits, slice count) alone: results repeat bit for bit.
+constexpr int kFinishSlices = 8;
+
 template <class T>
-__global__ void gemv_finish_kernel(const float* __restrict__ partial, int splits, long long len, T* y, long long incy,
-                                   float alpha, float beta) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= len) return;
+__global__ void __launch_bounds__(256) gemv_finish_kernel(const float* __restrict__ partial, int splits, long long len,
+                                                          T* y, long long incy, float alpha, float beta) {
+  __shared__ float red[kFinishSlices][33];
+  const int o = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const long long i = static_cast<long long>(blockIdx.x) * 32 + o;
   float acc = 0.f;
-  int s = 0;
-  for (; s + 3 < splits; s += 4) {   // loads issued together, added in index order
-    const float v0 = partial[static_cast<long long>(s) * len + i], v1 = partial[static_cast<long long>(s + 1) * len + i];
-    const float v2 = partial[static_cast<long long>(s + 2) * len + i], v3 = partial[static_cast<long long>(s + 3) * len + i];
-    acc = (((acc + v0) + v1) + v2) + v3;
+  if (i < len) {
+#pragma unroll 4
+    for (int s = sl; s < splits; s += kFinishSlices) acc += __ldcs(partial + static_cast<long long>(s) * len + i);
   }
-  for (; s < splits; ++s) acc += partial[static_cast<long long>(s) * len + i];
-  T* yp = y + i * incy;
-  float r = alpha * acc;
-  if (beta != 0.f) r += beta * to_f32(*yp);
-  *yp = from_f32<T>(r);
+  red[sl][o] = acc;
+  __syncthreads();
+  if (sl == 0 && i < len) {
+    float t = red[0][o];
+#pragma unroll
+    for (int q = 1; q < kFinishSlices; ++q) t += red[q][o];
+    T* yp = y + i * incy;
+    float r = alpha * t;
+    if (beta != 0.f) r += beta * to_f32(*yp);
+    *yp = from_f32<T>(r);
+  }
 }
 
 // y[i] = beta * y[i]  (alpha == 0)

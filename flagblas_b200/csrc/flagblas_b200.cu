@@ -314,6 +314,7 @@ static int dispatch_tc(int dtype, int block_n, bool pair, const CUtensorMap& ma,
   if (tiles < 0) tiles = 1LL << 40;
 #define FB_CASE(KIND)                                                                              \
   if (pair) {                                                                                      \
+    if (block_n == 512) return launch_tc<KIND, 512, true>(ma, mb, p, tiles, sm_count, stream);     \
     if (block_n == 256) return launch_tc<KIND, 256, true>(ma, mb, p, tiles, sm_count, stream);     \
     return launch_tc<KIND, 128, true>(ma, mb, p, tiles, sm_count, stream);                         \
   }                                                                                                \
@@ -552,11 +553,57 @@ static int run_gemv(int trans, long long m, long long n, float alpha, const void
   }
   FB_CUDA_OK(cudaGetLastError());
   if (pl.splits > 1) {
-    gemv_finish_kernel<T><<<static_cast<unsigned>((len_y + 255) / 256), 256, 0, stream>>>(
+    gemv_finish_kernel<T><<<static_cast<unsigned>((len_y + 31) / 32), 256, 0, stream>>>(
         p.partial, pl.splits, len_y, static_cast<T*>(y), incy, alpha, beta);
     FB_CUDA_OK(cudaGetLastError());
   }
   return FB_OK;
+}
+
+// fp8 matrix and vector, trans = T only: y[n] (TY) = alpha * A^T x + beta * y.
+template <class TA, class TX, class TY>
+static int run_gemv_fp8(long long m, long long n, float alpha, const void* A, long long lda, const void* x,
+                        long long incx, float beta, void* y, long long incy, void* workspace, size_t workspace_bytes,
+                        int sms, cudaStream_t stream) {
+  if (alpha == 0.f) {
+    if (beta == 1.f) return FB_OK;
+    gemv_scale_kernel<TY><<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(static_cast<TY*>(y), n, incy, beta);
+    FB_CUDA_OK(cudaGetLastError());
+    return FB_OK;
+  }
+  const GemvPlan pl = plan_gemv(FB_OP_T, m, n, 1, sms);
+  GemvParams p{};
+  p.m = static_cast<int>(m); p.n = static_cast<int>(n); p.lda = lda;
+  p.A = A; p.x = x; p.y = y; p.incx = incx; p.incy = incy;
+  p.alpha = alpha; p.beta = beta;
+  p.splits = pl.splits; p.chunk = pl.chunk; p.tx = pl.lanes;
+  p.a_vec = aligned16(A, lda, 1) ? 1 : 0;
+  p.x_vec = 0;
+  if (pl.splits > 1) {
+    const size_t need = static_cast<size_t>(pl.splits) * static_cast<size_t>(n) * sizeof(float);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return FB_ERR_WORKSPACE;
+    p.partial = static_cast<float*>(workspace);
+  }
+  const dim3 grid(static_cast<unsigned>(pl.grid_x), static_cast<unsigned>(pl.splits));
+  gemv_t_kernel<TA, 8, 4, TX, TY><<<grid, pl.threads, 0, stream>>>(p);
+  FB_CUDA_OK(cudaGetLastError());
+  if (pl.splits > 1) {
+    gemv_finish_kernel<TY><<<static_cast<unsigned>((n + 31) / 32), 256, 0, stream>>>(
+        p.partial, pl.splits, n, static_cast<TY*>(y), incy, alpha, beta);
+    FB_CUDA_OK(cudaGetLastError());
+  }
+  return FB_OK;
+}
+
+template <class TA, class TX>
+static int run_gemv_fp8_y(int y_dtype, long long m, long long n, float alpha, const void* A, long long lda,
+                          const void* x, long long incx, float beta, void* y, long long incy, void* ws, size_t ws_bytes,
+                          int sms, cudaStream_t stream) {
+  switch (y_dtype) {
+    case FB_F16: return run_gemv_fp8<TA, TX, __half>(m, n, alpha, A, lda, x, incx, beta, y, incy, ws, ws_bytes, sms, stream);
+    case FB_BF16: return run_gemv_fp8<TA, TX, __nv_bfloat16>(m, n, alpha, A, lda, x, incx, beta, y, incy, ws, ws_bytes, sms, stream);
+    default: return run_gemv_fp8<TA, TX, float>(m, n, alpha, A, lda, x, incx, beta, y, incy, ws, ws_bytes, sms, stream);
+  }
 }
 
 }  // namespace fb
@@ -635,8 +682,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   const DensePlan dplan = plan_dense(m, n, k, esz, di->sm_count);
   const bool pair = dplan.pair;
   const int tile_m = dplan.tile_m;
-  const int block_n = dplan.block_n;
-  const int b_rows = pair ? block_n / 2 : block_n;  // rows of the B tile each CTA fetches
+  int block_n = dplan.block_n;
   const uint32_t span = kSwizzleBytes / esz;
   const bool a_mn = transa == FB_OP_T;  // stored [k, m]: M contiguous
   const bool b_mn = transb == FB_OP_N;  // stored [k, n]: N contiguous
@@ -650,6 +696,12 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   int ks = (a3d && b3d && k > static_cast<long long>(span)) ? 2 : 1;
   const int force_ks = env_int("FLAGBLAS_B200_KS", 0);
   if (force_ks == 1 || (force_ks == 2 && a3d && b3d)) ks = force_ks;
+  // 256 x 512 pair tiles (FLAGBLAS_B200_BLOCK_N=512): a quarter less operand traffic per FLOP than
+  // 256 x 256, paid for with a single-buffered accumulator (all 512 TMEM columns hold one tile).
+  // They need the one-copy-per-stage 3-D views of both operands.
+  if (pair && a3d && b3d && env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512) block_n = 512;
+  const int halves = block_n > 256 ? 2 : 1;
+  const int b_rows = (pair ? block_n / 2 : block_n) / halves;  // rows of B per copy (per column half of the tile)
 
   CUtensorMap ma, mb;
   const bool atom32 = esz == 4;  // MN-major fp32 operands use the 32-byte-atom swizzle
@@ -673,6 +725,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   int rc = encode_maps(use_a3d, use_b3d, ks);
   if (rc && (use_a3d || use_b3d)) {
     // the driver refused a 3-D view: fall back to plain 2-D boxes, one k-slab per stage
+    if (block_n > 256) return rc;  // (512-wide tiles are only chosen on request)
     use_a3d = use_b3d = false;
     ks = 1;
     rc = encode_maps(false, false, 1);
@@ -689,14 +742,14 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.group_m = env_int("FLAGBLAS_B200_GROUP_M", pair ? 8 : 16);
   if (p.group_m < 1) p.group_m = 1;
   p.alpha = alpha; p.beta = beta;
-  p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n);
+  p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n > 256 ? 256 : block_n);
   p.block_k = span * ks;
   p.ks = ks;
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
   // Optional stream-K scratch behind the packed operands: used only when the caller provided it.
-  if (dplan.want_streamk && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
+  if (dplan.want_streamk && block_n <= 256 && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
       workspace_bytes >= ws_used + streamk_bytes(di->sm_count, block_n)) {
     uint8_t* sk = static_cast<uint8_t*>(workspace) + ws_used;
     p.sk_flags = reinterpret_cast<int*>(sk);
@@ -944,6 +997,40 @@ int fb_gemv(int dtype, int trans, int64_t m, int64_t n, float alpha, const void*
       return run_gemv<float>(trans, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes,
                              di->sm_count, stream);
   }
+}
+
+size_t fb_gemv_fp8_workspace_bytes(int64_t m, int64_t n) {
+  if (m <= 0 || n <= 0) return 0;
+  const DeviceInfo* di = device_info();
+  if (!di) return 0;
+  const GemvPlan pl = plan_gemv(FB_OP_T, m, n, 1, di->sm_count);
+  return pl.splits <= 1 ? 0 : static_cast<size_t>(pl.splits) * static_cast<size_t>(n) * sizeof(float);
+}
+
+int fb_gemv_fp8(int a_format, int x_format, int y_dtype, int64_t m, int64_t n, float alpha, const void* A, int64_t lda,
+                const void* x, int64_t incx, float beta, void* y, int64_t incy, void* workspace,
+                size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if ((a_format != FB_FP8_E4M3 && a_format != FB_FP8_E5M2) || (x_format != FB_FP8_E4M3 && x_format != FB_FP8_E5M2))
+    return FB_ERR_INVALID_ARG;
+  if (y_dtype != FB_F32 && y_dtype != FB_F16 && y_dtype != FB_BF16) return FB_ERR_INVALID_ARG;
+  if (m < 0 || n < 0 || incx <= 0 || incy <= 0) return FB_ERR_INVALID_ARG;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return FB_OK;
+  if (!y) return FB_ERR_INVALID_ARG;
+  if (alpha != 0.f && (!A || !x || lda < n)) return FB_ERR_INVALID_ARG;
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+  const int sms = di->sm_count;
+  if (a_format == FB_FP8_E4M3) {
+    if (x_format == FB_FP8_E4M3)
+      return run_gemv_fp8_y<__nv_fp8_e4m3, __nv_fp8_e4m3>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
+    return run_gemv_fp8_y<__nv_fp8_e4m3, __nv_fp8_e5m2>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
+  }
+  if (x_format == FB_FP8_E4M3)
+    return run_gemv_fp8_y<__nv_fp8_e5m2, __nv_fp8_e4m3>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
+  return run_gemv_fp8_y<__nv_fp8_e5m2, __nv_fp8_e5m2>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
 }
 
 const char* fb_status_string(int status) {

@@ -1,3 +1,3 @@
-from .gemv import bfgemv, hgemv, sgemv
+from .gemv import bfgemv, fp8_gemv, hgemv, sgemv
 
-__all__ = ["sgemv", "hgemv", "bfgemv"]
+__all__ = ["sgemv", "hgemv", "bfgemv", "fp8_gemv"]

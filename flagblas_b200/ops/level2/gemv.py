@@ -1,4 +1,4 @@
-"""Matrix-vector operators: ``sgemv``, ``hgemv``, ``bfgemv``.
+"""Matrix-vector operators: ``sgemv``, ``hgemv``, ``bfgemv``, ``fp8_gemv``.
 
 Same call signature and semantics as the reference operators
 (``src/flag_blas/ops/level2/gemv.py:2285-2375, 2814-2926, 2929-3041``):
@@ -84,3 +84,46 @@ def hgemv(trans, m, n, alpha, A, lda, x, incx, beta, y, incy) -> None:
 def bfgemv(trans, m, n, alpha, A, lda, x, incx, beta, y, incy) -> None:
     """bf16 matrix-vector product, fp32 accumulate, one rounding (reference: ops/level2/gemv.py:2929-3041)."""
     _gemv(_lib.FB_BF16, torch.bfloat16, "bfgemv", trans, m, n, alpha, A, lda, x, incx, beta, y, incy)
+
+
+FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+_FP8_CODE = {torch.float8_e4m3fn: _lib.FB_FP8_E4M3, torch.float8_e5m2: _lib.FB_FP8_E5M2}
+_Y_CODE = {torch.float32: _lib.FB_F32, torch.float16: _lib.FB_F16, torch.bfloat16: _lib.FB_BF16}
+
+
+def fp8_gemv(trans, m, n, alpha, A, lda, x, incx, beta, y, incy) -> None:
+    """FP8 matrix and vector, ``y[n] = alpha * A.T @ x[m] + beta * y`` with ``y`` in fp32 / fp16 / bf16
+    (reference: ops/level2/gemv.py:3044-3124; only ``trans = CUBLAS_OP_T``)."""
+    if m == 0 or n == 0:
+        return
+    assert trans == CUBLAS_OP_T, "FP8 gemv only supports trans=CUBLAS_OP_T (TN format)"
+    assert A.stride(1) == 1, "A must be row-major contiguous in the inner dimension"
+    assert lda == A.stride(0), "lda must match the row stride of A"
+    assert A.dtype in FP8_DTYPES, f"A must be FP8 dtype, got {A.dtype}"
+    assert x.dtype in FP8_DTYPES, f"x must be FP8 dtype, got {x.dtype}"
+    assert y.dtype in (torch.float32, torch.float16, torch.bfloat16)
+    assert A.device == x.device == y.device
+    assert m % 16 == 0, f"Matrix dimension m ({m}) must be a multiple of 16 for 16-byte alignment"
+    assert n % 16 == 0, f"Matrix dimension n ({n}) must be a multiple of 16 for 16-byte alignment"
+    assert lda % 16 == 0, f"lda ({lda}) must be a multiple of 16 for 16-byte alignment"
+    assert A.data_ptr() % 16 == 0, "Pointer to A must be 16-byte aligned"
+    assert x.data_ptr() % 16 == 0, "Pointer to x must be 16-byte aligned"
+    assert y.data_ptr() % 16 == 0, "Pointer to y must be 16-byte aligned"
+    assert incx > 0 and incy > 0 and lda >= n
+    if not y.is_cuda:
+        raise RuntimeError("flagblas_b200.fp8_gemv: tensors must live on a CUDA device (there is no CPU path)")
+    alpha = _scalar(alpha)
+    beta = _scalar(beta)
+    assert y.numel() >= 1 + (n - 1) * incy
+    if alpha != 0.0:
+        assert x.numel() >= 1 + (m - 1) * incx
+    stream, prev = _lib.enter(A.device)
+    try:
+        ws_bytes = _cop.gemv_fp8_workspace_bytes(m, n) if alpha != 0.0 else 0
+        ws_ptr = _lib.scratch(A.device, stream, ws_bytes)
+        status = _cop.gemv_fp8(_FP8_CODE[A.dtype], _FP8_CODE[x.dtype], _Y_CODE[y.dtype], m, n, alpha, A.data_ptr(), lda,
+                               x.data_ptr(), incx, beta, y.data_ptr(), incy, ws_ptr, ws_bytes, stream)
+    finally:
+        _lib.leave(prev)
+    if status:
+        _lib.check(status, "fp8_gemv")

@@ -99,6 +99,24 @@ int fb_gemv(int dtype, int trans, int64_t m, int64_t n, float alpha, const void*
 
 size_t fb_gemv_workspace_bytes(int dtype, int trans, int64_t m, int64_t n);
 
+/* 8-bit floating-point storage formats of fb_gemv_fp8 (OCP FP8; e4m3 = torch.float8_e4m3fn). */
+enum { FB_FP8_E4M3 = 0, FB_FP8_E5M2 = 1 };
+
+/*
+ * Matrix-vector product with an FP8 matrix and an FP8 vector, transposed form only:
+ *     y[n] <- alpha * A^T * x[m] + beta * y
+ *   A stored [m, lda>=n] row-major in `a_format`, x in `x_format` (strided by incx), y of type
+ *   y_dtype = FB_F32 / FB_F16 / FB_BF16 (strided by incy); every product and sum in fp32, one rounding.
+ *   Early-outs as fb_gemv.  16-byte aligned A and lda use 16-byte loads, anything else works too.
+ * Replaces the body of fp8_gemv, src/flag_blas/ops/level2/gemv.py:3044-3124 (kernels :2158-2282).
+ * Scratch: fb_gemv_fp8_workspace_bytes(m, n) bytes, 16-byte aligned, when the rows are split.
+ */
+int fb_gemv_fp8(int a_format, int x_format, int y_dtype, int64_t m, int64_t n, float alpha, const void* A, int64_t lda,
+                const void* x, int64_t incx, float beta, void* y, int64_t incy, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+size_t fb_gemv_fp8_workspace_bytes(int64_t m, int64_t n);
+
 /*
  * Grouped GEMM:  for g in [0, group_count):
  *     out_g[m_g,n_g] <- alpha * A_g[m_g,k_g] * B_g + beta * C_g

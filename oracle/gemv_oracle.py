@@ -28,9 +28,14 @@ from .gemm_oracle import _ROUND_OUT, OP_N, OP_T
 _KIND = {"sgemv": "fp32", "hgemv": "fp16", "bfgemv": "bf16"}
 
 
-def gemv(name, trans, m, n, alpha, A, lda, x, incx, beta, y, incy):
-    """In place on the flat numpy buffer ``y``; returns None like the reference."""
-    kind = _KIND[name]
+def gemv(name, trans, m, n, alpha, A, lda, x, incx, beta, y, incy, out_kind=None):
+    """In place on the flat numpy buffer ``y``; returns None like the reference.
+
+    ``name = "fp8_gemv"`` (``gemv.py:3044-3124``; kernel 2158-2220): ``A`` and ``x`` hold decoded FP8
+    values, ``trans`` must be T, ``out_kind`` ("fp32" / "fp16" / "bf16") is the storage type of ``y``;
+    the arithmetic is the same fp32 accumulate and single rounding."""
+    kind = out_kind if name == "fp8_gemv" else _KIND[name]
+    assert name != "fp8_gemv" or trans == OP_T
     assert trans in (OP_N, OP_T) and incx > 0 and incy > 0 and lda >= n
     if m == 0 or n == 0:
         return None

@@ -75,6 +75,24 @@ def gemv_cases(name):
             yield "gemv_%s_t%d_c%d" % (name, trans, ci), (trans, m, n, lda, incx, incy, alpha, beta), A, x, y
 
 
+FP8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+# (m, n, lda - n, incx, incy, A format, x format, y kind, alpha, beta): plain, the reference's split-K
+# shape (n <= 64 and m >= 4096), e5m2 with fp16 output, mixed formats with strides.
+FP8_GEMV_SHAPES = ((256, 128, 0, 1, 1, "e4m3", "e4m3", "fp32", 1.5, 0.5), (4112, 48, 16, 1, 1, "e4m3", "e4m3", "bf16", 1.0, 0.0),
+                   (512, 1024, 0, 1, 1, "e5m2", "e5m2", "fp16", 2.0, 1.0), (320, 208, 32, 2, 2, "e4m3", "e5m2", "fp32", -0.5, 0.25))
+
+
+def fp8_gemv_cases():
+    """Yields (key, (m, n, lda, incx, incy, y kind, alpha, beta), A, x, y) as CPU tensors (A, x in FP8)."""
+    gen = torch.Generator(device="cpu").manual_seed(37)
+    for ci, (m, n, pad, incx, incy, fa, fx, ky, alpha, beta) in enumerate(FP8_GEMV_SHAPES):
+        lda = n + pad
+        A = torch.randn(m, lda, generator=gen).to(FP8[fa])
+        x = torch.randn(1 + (m - 1) * incx, generator=gen).to(FP8[fx])
+        y = torch.randn(1 + (n - 1) * incy, generator=gen).to(DTYPES[ky])
+        yield "fp8gemv_c%d" % ci, (m, n, lda, incx, incy, ky, alpha, beta), A, x, y
+
+
 def pack(t):
     """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
     if t.dtype in (torch.bfloat16, torch.float16):

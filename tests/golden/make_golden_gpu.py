@@ -112,7 +112,7 @@ def _import_reference():
     for name in ("group_bfgemm", "group_hgemm", "group_tf32gemm", "group_mm"):
         mods[name] = getattr(gg, name)
     gv = sys.modules["flag_blas.ops.level2.gemv"]
-    for name in ("sgemv", "hgemv", "bfgemv"):
+    for name in ("sgemv", "hgemv", "bfgemv", "fp8_gemv"):
         mods[name] = getattr(gv, name)
     return torch, mods
 
@@ -133,6 +133,14 @@ def main_gemv():
             out[key + "_y"] = gc.pack(yd.cpu())
             out[key + "_probe"] = np.concatenate([A.float().numpy().ravel()[:8], x.float().numpy().ravel()[:1]])
         print("gemv", name, "done", flush=True)
+    for key, (m, n, lda, incx, incy, ky, alpha, beta), A, x, y in gc.fp8_gemv_cases():
+        yd = y.to(dev)
+        # the reference asserts lda == A.stride(0): hand it the padded matrix as a column slice
+        ref["fp8_gemv"](1, m, n, alpha, A.to(dev)[:, :n], lda, x.to(dev), incx, beta, yd, incy)
+        torch.cuda.synchronize()
+        out[key + "_y"] = gc.pack(yd.cpu())
+        out[key + "_probe"] = np.concatenate([A.float().numpy().ravel()[:8], x.float().numpy().ravel()[:1]])
+    print("fp8_gemv done", flush=True)
     path = os.path.join(HERE, "gpu_reference_gemv.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

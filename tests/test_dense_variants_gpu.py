@@ -12,7 +12,8 @@ DEV = "cuda"
 
 @pytest.mark.parametrize("env", [{"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_TMA3D": "0"}, {"FLAGBLAS_B200_KS": "1"},
                                  {"FLAGBLAS_B200_BLOCK_N": "128"}, {"FLAGBLAS_B200_PAIR": "0", "FLAGBLAS_B200_BLOCK_N": "64"},
-                                 {"FLAGBLAS_B200_STAGES": "2"}, {"FLAGBLAS_B200_GROUP_M": "3"}])
+                                 {"FLAGBLAS_B200_STAGES": "2"}, {"FLAGBLAS_B200_GROUP_M": "3"},
+                                 {"FLAGBLAS_B200_BLOCK_N": "512"}, {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_KS": "1"}])
 @pytest.mark.parametrize("kind", ["bf16", "tf32"])
 def test_dense_plan_variants(env, kind, monkeypatch):
     for k, v in env.items():

@@ -269,3 +269,70 @@ def test_full_size_properties(name, trans):
     tol = NAMES[name][1] * (len_x ** 0.5)
     assert float((got - want).abs().max()) <= tol + NAMES[name][1] * float(want.abs().max())
     assert fb.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------- fp8_gemv
+def _fp8_oracle(m, n, lda, incx, incy, ky, alpha, beta, A, x, y):
+    yy = y.float().numpy().copy()
+    gvo.gemv("fp8_gemv", 1, m, n, alpha, A.float().numpy(), lda, x.float().numpy(), incx, beta, yy, incy, out_kind=ky)
+    return torch.from_numpy(yy)
+
+
+_FP8_TOL = {"fp32": 1e-5, "fp16": 1e-2, "bf16": 1e-2}
+
+
+def test_fp8_oracle_vs_reference_on_gpu(z):
+    for key, (m, n, lda, incx, incy, ky, alpha, beta), A, x, y in gc.fp8_gemv_cases():
+        probe = np.concatenate([A.float().numpy().ravel()[:8], x.float().numpy().ravel()[:1]])
+        np.testing.assert_array_equal(probe, z[key + "_probe"], err_msg="input generator differs from the fixture's")
+        ref = gc.unpack(z[key + "_y"], ky).float()
+        got = _fp8_oracle(m, n, lda, incx, incy, ky, alpha, beta, A, x, y)
+        assert_parity(got[::incy], ref[::incy], _FP8_TOL[ky], _scale(m, A[:, :n], x[::incx], y[::incy], alpha, beta), key)
+
+
+@pytest.mark.gpu
+def test_fp8_gemv_against_oracle_and_reference_vectors(z):
+    import flagblas_b200 as fb
+    for key, (m, n, lda, incx, incy, ky, alpha, beta), A, x, y in gc.fp8_gemv_cases():
+        yd = y.to(DEV)
+        fb.fp8_gemv(1, m, n, alpha, A.to(DEV)[:, :n], lda, x.to(DEV), incx, beta, yd, incy)
+        torch.cuda.synchronize()
+        got = yd.float().cpu()
+        sc = _scale(m, A[:, :n], x[::incx], y[::incy], alpha, beta)
+        assert_parity(got, _fp8_oracle(m, n, lda, incx, incy, ky, alpha, beta, A, x, y), _FP8_TOL[ky], sc, key)
+        ref = gc.unpack(z[key + "_y"], ky).float()
+        assert_parity(got[::incy], ref[::incy], _FP8_TOL[ky], sc, key + " vs reference")
+    assert fb.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("ky", ["fp32", "bf16"])
+def test_fp8_gemv_shapes_and_edges(fmt, ky):
+    import flagblas_b200 as fb
+    dt = gc.FP8[fmt]
+    g = torch.Generator(device="cpu").manual_seed(41)
+    for m, n in [(16, 16), (256, 4096), (8192, 32), (2048, 2048), (4096, 14336)]:
+        A = torch.randn(m, n, generator=g).to(dt)
+        x = torch.randn(m, generator=g).to(dt)
+        y = torch.randn(n, generator=g).to(gc.DTYPES[ky])
+        ref = _fp8_oracle(m, n, n, 1, 1, ky, 1.5, 0.5, A, x, y)
+        yd = y.to(DEV)
+        fb.fp8_gemv(1, m, n, 1.5, A.to(DEV), n, x.to(DEV), 1, 0.5, yd, 1)
+        torch.cuda.synchronize()
+        assert_parity(yd.float().cpu(), ref, _FP8_TOL[ky], _scale(m, A, x, y, 1.5, 0.5), "fp8 %s %s %dx%d" % (fmt, ky, m, n))
+    # beta == 0 never reads y; alpha == 0 only scales; m == 0 does nothing; N form is refused
+    yd = torch.full((64,), float("nan"), dtype=gc.DTYPES[ky], device=DEV)
+    A = torch.ones(32, 64).to(dt).to(DEV)
+    x = torch.ones(32).to(dt).to(DEV)
+    fb.fp8_gemv(1, 32, 64, 1.0, A, 64, x, 1, 0.0, yd, 1)
+    assert torch.equal(yd.float().cpu(), torch.full((64,), 32.0))
+    fb.fp8_gemv(1, 32, 64, 0.0, A, 64, x, 1, 0.5, yd, 1)
+    assert torch.equal(yd.float().cpu(), torch.full((64,), 16.0))
+    fb.fp8_gemv(1, 0, 64, 1.0, A, 64, x, 1, 0.0, yd, 1)
+    assert torch.equal(yd.float().cpu(), torch.full((64,), 16.0))
+    with pytest.raises(AssertionError):
+        fb.fp8_gemv(0, 32, 64, 1.0, A, 64, x, 1, 0.0, yd, 1)
+    with pytest.raises(AssertionError):
+        fb.fp8_gemv(1, 32, 60, 1.0, A, 64, x, 1, 0.0, yd, 1)     # n not a multiple of 16
+    assert fb.device_status() == 0
