@@ -10,8 +10,9 @@ column-sharded (N-split) across the ranks, one process per GPU, with no collecti
 data path (strong scaling: total work fixed).
 
 ``value``   : device-resident TFLOP/s (inputs in HBM, CUDA events, max over ranks).
-``e2e``     : the same metric through the public operator API with HOST buffers: per step
-              pinned-host -> device copies of A and B, the GEMM, and the device -> host copy of C.
+``e2e``     : the same metric through the public host-memory entry (``flagblas_b200.host.gemm_from_host``):
+              per step pinned-host -> device copies of A and B (and C when beta != 0), the GEMM, and the
+              device -> host copy of C, overlapped on CUDA streams (row blocks of A / C) where the layout allows.
 ``roofline``: tensor-core roofline of the GEMM kernel (2*m*n*k FLOPs per launch / event time).
 ``cpu_baseline``: torch.matmul fp32 on the host cores over a bounded row sample (rank 0, N=1).
 """
@@ -526,12 +527,12 @@ def main():
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
     hC = torch.empty(C.shape, dtype=dt).pin_memory()
 
+    from flagblas_b200 import host as fbhost
+
     def e2e_step():
-        A.copy_(hA, non_blocking=True)
-        B.copy_(hB, non_blocking=True)
+        # the library's host-memory entry: copies in, kernels and copies out overlapped on streams
         if nl > 0:
-            opfn(ta, tb, m, nl, k, alpha, A, lda, B, ldb, beta, C, ldc)
-        hC.copy_(C, non_blocking=True)
+            fbhost.gemm_from_host(op, ta, tb, m, nl, k, alpha, hA, lda, hB, ldb, beta, hC, ldc, A, B, C)
         torch.cuda.synchronize()
 
     e2e_step()
@@ -546,7 +547,7 @@ def main():
         t = torch.tensor([e2e_ms], device=dev)
         tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    h2d = (A.numel() + B.numel()) * esz
+    h2d = (A.numel() + B.numel() + (C.numel() if beta != 0 else 0)) * esz
     d2h = C.numel() * esz
 
     # ---- the other BASELINE configs, briefly (single GPU only; informational)

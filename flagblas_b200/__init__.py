@@ -17,6 +17,7 @@ from ._lib import FlagBlasError, device_status  # noqa: F401
 # ``flag_blas.c_operators`` is the name the reference reserves for a compiled extension
 # (src/flag_blas/config.py:35-41); here it is the pybind11 module over the C ABI.
 from . import c_operators  # noqa: E402,F401
+from . import host  # noqa: E402,F401
 from .aten import all_registered_keys, all_registered_ops, enable, only_enable, use_blas  # noqa: E402,F401
 
 device = runtime.device.name
@@ -24,5 +25,5 @@ vendor_name = runtime.device.vendor_name
 __version__ = "0.1.0"
 
 __all__ = list(_ops_all) + ["runtime", "testing", "device", "vendor_name", "c_operators", "FlagBlasError",
-                            "device_status", "enable", "only_enable", "use_blas", "all_registered_ops",
+                            "device_status", "host", "enable", "only_enable", "use_blas", "all_registered_ops",
                             "all_registered_keys"]

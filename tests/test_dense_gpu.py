@@ -234,3 +234,27 @@ def test_full_size_properties(cfg):
         refc = _cublas(kind, ta, tb, A, B)
         d = (C1.float() - refc).abs().max().item()
         assert d <= 2 * rtol * (k ** 0.5) * sa * sb + rtol * refc.abs().max().item(), d
+
+
+@pytest.mark.parametrize("kind,ta,tb,beta", [("bf16", 0, 1, 0.5), ("fp16", 0, 0, 0.0), ("tf32", 1, 0, 0.5), ("fp32", 0, 0, 0.0)])
+def test_gemm_from_host_matches_the_operator(kind, ta, tb, beta):
+    """Host-memory entry: row blocks streamed over three CUDA streams (transa = N) or the plain
+    copy / compute / copy sequence (transa = T) must give the operator's result bit for bit."""
+    from flagblas_b200 import host
+    m, n, k = 2304, 640, 512
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, pad=8, seed=5)
+    name = KINDS[kind][1]
+    Cd = C.to(DEV)
+    getattr(fb, name)(ta, tb, m, n, k, 1.5, A.to(DEV), lda, B.to(DEV), ldb, beta, Cd, ldc)
+    torch.cuda.synchronize()
+    hA, hB, hC = A.pin_memory(), B.pin_memory(), C.clone().pin_memory()
+    dA, dB, dC = torch.empty_like(A, device=DEV), torch.empty_like(B, device=DEV), torch.full_like(C, float("nan"), device=DEV)
+    for _ in range(2):   # twice: the second call reuses streams and scratch
+        hC.copy_(C)
+        host.gemm_from_host(name, ta, tb, m, n, k, 1.5, hA, lda, hB, ldb, beta, hC, ldc, dA, dB, dC, chunks=4)
+        torch.cuda.current_stream().synchronize()
+        if beta == 0.0:
+            assert torch.equal(hC[:, :n], Cd.cpu()[:, :n])
+        else:
+            assert torch.equal(hC, Cd.cpu())
+    assert fb.device_status() == 0
