@@ -171,4 +171,187 @@ __global__ void __launch_bounds__(256) sgemm_simt_kernel(const SimtParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant for 16-byte aligned operands: the k-slices travel global -> shared memory with
+// cp.async (no register staging), four slices deep, so that the load latency of a slice is hidden
+// behind the FFMAs of the three before it -- what the double-buffered kernel above cannot do when
+// few CTAs share an SM (a 512^3 problem is 64 CTAs on 148 SMs).
+//
+// Shared-memory layout of a slice follows the operand's storage, so that every 16-byte piece is one
+// cp.async: an operand stored with M (or N) contiguous lands as [16 k][tile] and is read back as float4
+// fragments; one stored with K contiguous lands as [tile][16 k + 4 pad] and is read back two k at a time
+// (float2).  For a K-contiguous B the thread's columns are interleaved (tx, tx + 16, ...) to keep those
+// reads spread over the banks.
+constexpr int kPipeK = 16;      // k per slice
+constexpr int kPipeStages = 4;
+constexpr int kPipeLdk = 20;    // floats per row of a K-contiguous tile (80 bytes: 16-byte aligned rows)
+
+template <int TILE, bool KMAJ>
+struct PipeTile {
+  static constexpr int kFloats = KMAJ ? TILE * kPipeLdk : kPipeK * TILE;
+};
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Issue this thread's share of the copies of one (TILE x 16) slice.  `kmaj`: stored [mn][k].
+template <int TILE, bool KMAJ>
+__device__ __forceinline__ void pipe_load(float* __restrict__ s, const float* __restrict__ base, long long ld, int mn0,
+                                          int k0, int mn_lim, int k_lim, int tid) {
+  constexpr int kChunks = TILE * kPipeK / 4;
+#pragma unroll
+  for (int c = tid; c < kChunks; c += 256) {
+    if (KMAJ) {
+      const int r = c >> 2, k4 = (c & 3) * 4;
+      const int valid = (mn0 + r < mn_lim) ? min(4, max(0, k_lim - (k0 + k4))) : 0;
+      const float* src = valid ? base + static_cast<long long>(mn0 + r) * ld + k0 + k4 : base;
+      cp_async16(s + r * kPipeLdk + k4, src, valid * 4);
+    } else {
+      const int kk = c / (TILE / 4), q = (c % (TILE / 4)) * 4;
+      const int valid = (k0 + kk < k_lim) ? min(4, max(0, mn_lim - (mn0 + q))) : 0;
+      const float* src = valid ? base + static_cast<long long>(k0 + kk) * ld + mn0 + q : base;
+      cp_async16(s + kk * TILE + q, src, valid * 4);
+    }
+  }
+}
+
+template <int BM, int BN, bool AK, bool BKM>
+__global__ void __launch_bounds__(256) sgemm_pipe_kernel(const SimtParams p) {
+  constexpr int TM = BM / 16, TN = BN / 16;
+  constexpr int RG = TM / 4, CG = TN / 4;
+  constexpr int kAFloats = PipeTile<BM, AK>::kFloats, kBFloats = PipeTile<BN, BKM>::kFloats;
+  extern __shared__ __align__(16) float pipe_smem[];
+  float* As = pipe_smem;
+  float* Bs = pipe_smem + kPipeStages * kAFloats;
+
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int tile_m = blockIdx.x / p.tiles_n, tile_n = blockIdx.x % p.tiles_n;
+  const int m0 = tile_m * BM, n0 = tile_n * BN;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+  // row / column of output (i, j) of this thread inside the tile
+  auto row_of = [&](int i) { return (i / 4) * (BM / RG) + ty * 4 + (i % 4); };
+  auto col_of = [&](int j) { return BKM ? tx + 16 * j : (j / 4) * (BN / CG) + tx * 4 + (j % 4); };
+
+  const int k_iters = (p.k + kPipeK - 1) / kPipeK;
+#pragma unroll
+  for (int s = 0; s < kPipeStages - 1; ++s) {
+    if (s < k_iters) {
+      pipe_load<BM, AK>(As + s * kAFloats, p.A, p.lda, m0, s * kPipeK, p.m, p.k, tid);
+      pipe_load<BN, BKM>(Bs + s * kBFloats, p.B, p.ldb, n0, s * kPipeK, p.n, p.k, tid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  for (int it = 0; it < k_iters; ++it) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPipeStages - 2) : "memory");
+    __syncthreads();  // slice `it` has landed for everyone; slice it-1's slot is free for the next copy
+    {
+      const int nx = it + kPipeStages - 1;
+      if (nx < k_iters) {
+        const int slot = nx % kPipeStages;
+        pipe_load<BM, AK>(As + slot * kAFloats, p.A, p.lda, m0, nx * kPipeK, p.m, p.k, tid);
+        pipe_load<BN, BKM>(Bs + slot * kBFloats, p.B, p.ldb, n0, nx * kPipeK, p.n, p.k, tid);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const float* as = As + (it % kPipeStages) * kAFloats;
+    const float* bs = Bs + (it % kPipeStages) * kBFloats;
+#pragma unroll
+    for (int kb = 0; kb < kPipeK / 2; ++kb) {
+      float af[2][TM], bf[2][TN];
+      if (AK) {
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+          const float2 v = *reinterpret_cast<const float2*>(as + row_of(i) * kPipeLdk + 2 * kb);
+          af[0][i] = v.x; af[1][i] = v.y;
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int g = 0; g < RG; ++g) {
+            const float4 v = *reinterpret_cast<const float4*>(as + (2 * kb + h) * BM + g * (BM / RG) + ty * 4);
+            af[h][g * 4 + 0] = v.x; af[h][g * 4 + 1] = v.y; af[h][g * 4 + 2] = v.z; af[h][g * 4 + 3] = v.w;
+          }
+      }
+      if (BKM) {
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          const float2 v = *reinterpret_cast<const float2*>(bs + col_of(j) * kPipeLdk + 2 * kb);
+          bf[0][j] = v.x; bf[1][j] = v.y;
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int g = 0; g < CG; ++g) {
+            const float4 v = *reinterpret_cast<const float4*>(bs + (2 * kb + h) * BN + g * (BN / CG) + tx * 4);
+            bf[h][g * 4 + 0] = v.x; bf[h][g * 4 + 1] = v.y; bf[h][g * 4 + 2] = v.z; bf[h][g * 4 + 3] = v.w;
+          }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(af[h][i], bf[h][j], acc[i][j]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // epilogue: alpha * acc + beta * C, C never read when beta == 0
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int row = m0 + row_of(i);
+    if (row >= p.m) continue;
+    float* crow = p.C + static_cast<long long>(row) * p.ldc;
+    if (!BKM) {
+#pragma unroll
+      for (int g = 0; g < CG; ++g) {
+        const int col = n0 + g * (BN / CG) + tx * 4;
+        if (col >= p.n) continue;
+        float* dst = crow + col;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = p.alpha * acc[i][g * 4 + j];
+        if (p.c_vec && col + 3 < p.n) {
+          if (p.beta != 0.f) {
+            const float4 c = *reinterpret_cast<const float4*>(dst);
+            v[0] += p.beta * c.x; v[1] += p.beta * c.y; v[2] += p.beta * c.z; v[3] += p.beta * c.w;
+          }
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col + j < p.n) {
+              float r = v[j];
+              if (p.beta != 0.f) r += p.beta * dst[j];
+              dst[j] = r;
+            }
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int col = n0 + col_of(j);
+        if (col < p.n) {
+          float r = p.alpha * acc[i][j];
+          if (p.beta != 0.f) r += p.beta * crow[col];
+          crow[col] = r;
+        }
+      }
+    }
+  }
+}
+
 }  // namespace fb

@@ -384,6 +384,31 @@ static int run_scale(void* C, long long ldc, long long m, long long n, float bet
   return FB_OK;
 }
 
+template <int BM, int BN, bool AK, bool BKM>
+static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t stream) {
+  auto kern = sgemm_pipe_kernel<BM, BN, AK, BKM>;
+  constexpr int kBytes = kPipeStages * (PipeTile<BM, AK>::kFloats + PipeTile<BN, BKM>::kFloats) * 4;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    attr_set[dev] = true;
+  }
+  kern<<<static_cast<unsigned>(tiles), 256, kBytes, stream>>>(p);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+template <int BM, int BN>
+static int dispatch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t stream) {
+  const bool ak = !p.a_mn_contig, bk = !p.b_mn_contig;  // K-contiguous storage
+  if (ak) return bk ? launch_sgemm_pipe<BM, BN, true, true>(p, tiles, stream)
+                    : launch_sgemm_pipe<BM, BN, true, false>(p, tiles, stream);
+  return bk ? launch_sgemm_pipe<BM, BN, false, true>(p, tiles, stream)
+            : launch_sgemm_pipe<BM, BN, false, false>(p, tiles, stream);
+}
+
 static int run_sgemm_simt(int transa, int transb, long long m, long long n, long long k, float alpha, const float* A,
                           long long lda, const float* B, long long ldb, float beta, float* C, long long ldc, int sms,
                           cudaStream_t stream) {
@@ -395,14 +420,15 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   p.b_mn_contig = transb ? 0 : 1;
   p.a_vec = aligned16(A, lda, 4); p.b_vec = aligned16(B, ldb, 4); p.c_vec = aligned16(C, ldc, 4);
   const long long big_tiles = ((m + 127) / 128) * ((n + 127) / 128);
-  if (big_tiles >= 2LL * sms) {
-    p.tiles_n = static_cast<int>((n + 127) / 128);
-    sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(big_tiles), 256, 0, stream>>>(p);
-  } else {
-    p.tiles_n = static_cast<int>((n + 63) / 64);
-    const long long tiles = ((m + 63) / 64) * p.tiles_n;
-    sgemm_simt_kernel<64, 64, 16><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
-  }
+  const bool big = big_tiles >= 2LL * sms;
+  p.tiles_n = static_cast<int>(big ? (n + 127) / 128 : (n + 63) / 64);
+  const long long tiles = big ? big_tiles : ((m + 63) / 64) * p.tiles_n;
+  // 16-byte aligned operands take the cp.async pipeline; FLAGBLAS_B200_SGEMM_PIPE=0 forces the
+  // register-staged kernel (profiling sweeps), which also serves everything unaligned.
+  if (p.a_vec && p.b_vec && env_int("FLAGBLAS_B200_SGEMM_PIPE", 1) != 0)
+    return big ? dispatch_sgemm_pipe<128, 128>(p, tiles, stream) : dispatch_sgemm_pipe<64, 64>(p, tiles, stream);
+  if (big) sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
+  else sgemm_simt_kernel<64, 64, 16><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
   FB_CUDA_OK(cudaGetLastError());
   return FB_OK;
 }
