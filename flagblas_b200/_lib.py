@@ -15,6 +15,7 @@ from . import build as _build
 FB_F32, FB_TF32, FB_F16, FB_BF16 = 0, 1, 2, 3
 FB_OK = 0
 FB_FP8_E4M3, FB_FP8_E5M2 = 0, 1
+FB_F64, FB_C64, FB_C128 = 4, 5, 6
 
 
 class FlagBlasError(RuntimeError):
@@ -41,6 +42,9 @@ def _load():
     handle.fb_gemm.argtypes = [i32, i32, i32, i64, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
     handle.fb_gemm_workspace_bytes.restype = sz
     handle.fb_gemm_workspace_bytes.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64]
+    handle.fb_gemm_ex.restype = i32
+    handle.fb_gemm_ex.argtypes = [i32, i32, i32, i64, i64, i64, c.POINTER(c.c_double), vp, i64, vp, i64,
+                                  c.POINTER(c.c_double), vp, i64, vp]
     handle.fb_gemv.restype = i32
     handle.fb_gemv.argtypes = [i32, i32, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
     handle.fb_gemv_workspace_bytes.restype = sz
@@ -82,6 +86,7 @@ from . import c_operators as cop  # noqa: E402  (pybind11 module; links against 
 EXPORTED_SYMBOLS = (
     "fb_gemm",
     "fb_gemm_workspace_bytes",
+    "fb_gemm_ex",
     "fb_gemv",
     "fb_gemv_workspace_bytes",
     "fb_gemv_fp8",

@@ -17,6 +17,7 @@ __device__ int g_fb_status = 0;
 #include "fb_group_setup.cuh"
 #include "fb_sgemm_simt.cuh"
 #include "fb_gemv.cuh"
+#include "fb_xgemm_simt.cuh"
 
 namespace fb {
 
@@ -632,6 +633,35 @@ static int run_gemv_fp8_y(int y_dtype, long long m, long long n, float alpha, co
   }
 }
 
+// --------------------------------------------------- double / complex GEMM on the CUDA cores
+template <class T>
+static int run_xgemm(int transa, int transb, long long m, long long n, long long k, const double* alpha, const void* A,
+                     long long lda, const void* B, long long ldb, const double* beta, void* C, long long ldc,
+                     bool complex_type, cudaStream_t stream) {
+  const double ar = alpha[0], ai = complex_type ? alpha[1] : 0.0;
+  const double br = beta[0], bi = complex_type ? beta[1] : 0.0;
+  if (k == 0 || (ar == 0.0 && ai == 0.0)) {
+    if (br == 1.0 && bi == 0.0) return FB_OK;
+    long long blocks = (m * n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    xgemm_scale_kernel<T><<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<T*>(C), ldc, static_cast<int>(m),
+                                                                        static_cast<int>(n), br, bi);
+    FB_CUDA_OK(cudaGetLastError());
+    return FB_OK;
+  }
+  XgemmParams p{};
+  p.m = static_cast<int>(m); p.n = static_cast<int>(n); p.k = static_cast<int>(k);
+  p.alpha_re = ar; p.alpha_im = ai; p.beta_re = br; p.beta_im = bi;
+  p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
+  p.transa = transa; p.transb = transb;
+  p.tiles_n = static_cast<int>((n + kXTile - 1) / kXTile);
+  const long long tiles = ((m + kXTile - 1) / kXTile) * p.tiles_n;
+  if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  xgemm_simt_kernel<T><<<static_cast<unsigned>(tiles), 256, 0, stream>>>(p);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -1057,6 +1087,32 @@ int fb_gemv_fp8(int a_format, int x_format, int y_dtype, int64_t m, int64_t n, f
   if (x_format == FB_FP8_E4M3)
     return run_gemv_fp8_y<__nv_fp8_e5m2, __nv_fp8_e4m3>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
   return run_gemv_fp8_y<__nv_fp8_e5m2, __nv_fp8_e5m2>(y_dtype, m, n, alpha, A, lda, x, incx, beta, y, incy, workspace, workspace_bytes, sms, stream);
+}
+
+int fb_gemm_ex(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const double* alpha, const void* A,
+               int64_t lda, const void* B, int64_t ldb, const double* beta, void* C, int64_t ldc, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (dtype != FB_F64 && dtype != FB_C64 && dtype != FB_C128) return FB_ERR_INVALID_ARG;
+  const bool cplx = dtype != FB_F64;
+  const int max_op = cplx ? FB_OP_C : FB_OP_T;
+  if (transa < 0 || transa > max_op || transb < 0 || transb > max_op) return FB_ERR_INVALID_ARG;
+  if (m < 0 || n < 0 || k < 0 || !alpha || !beta) return FB_ERR_INVALID_ARG;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return FB_OK;
+  if (!C || ldc < n) return FB_ERR_INVALID_ARG;
+  const bool scale_only = k == 0 || (alpha[0] == 0.0 && (!cplx || alpha[1] == 0.0));
+  if (!scale_only) {
+    if (!A || !B) return FB_ERR_INVALID_ARG;
+    if (lda < (transa ? m : k) || ldb < (transb ? k : n)) return FB_ERR_INVALID_ARG;
+  }
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+  switch (dtype) {
+    case FB_F64: return run_xgemm<double>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, false, stream);
+    case FB_C64: return run_xgemm<cfloat>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, true, stream);
+    default: return run_xgemm<cdouble>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, true, stream);
+  }
 }
 
 const char* fb_status_string(int status) {

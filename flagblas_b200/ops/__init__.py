@@ -2,7 +2,7 @@
 (reference: ``src/flag_blas/ops/__init__.py:35-52,75-94,151-158``)."""
 from ._constants import CUBLAS_OP_C, CUBLAS_OP_N, CUBLAS_OP_T
 from .level2 import bfgemv, fp8_gemv, hgemv, sgemv
-from .level3 import (bfgemm, group_bfgemm, group_gemm, group_hgemm, group_mm, group_tf32gemm, hgemm, sgemm,
+from .level3 import (bfgemm, cgemm, dgemm, zgemm, group_bfgemm, group_gemm, group_hgemm, group_mm, group_tf32gemm, hgemm, sgemm,
                      tf32gemm)
 
 __all__ = [
@@ -10,4 +10,5 @@ __all__ = [
     "sgemm", "hgemm", "bfgemm", "tf32gemm",
     "group_bfgemm", "group_hgemm", "group_tf32gemm", "group_mm", "group_gemm",
     "sgemv", "hgemv", "bfgemv", "fp8_gemv",
+    "dgemm", "cgemm", "zgemm",
 ]

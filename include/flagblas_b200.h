@@ -77,6 +77,26 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
 size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
                                int64_t lda, const void* B, int64_t ldb);
 
+/* Element types of fb_gemm_ex (the GEMMs outside the tensor-core path). */
+enum { FB_F64 = 4, FB_C64 = 5, FB_C128 = 6 };
+/* Conjugate transpose, accepted by fb_gemm_ex for the complex types
+ * (CUBLAS_OP_C, src/flag_blas/ops/level3/cgemm.py:59-60). */
+enum { FB_OP_C = 2 };
+
+/*
+ * Dense GEMM in double, complex<float> or complex<double>, on the CUDA cores (IEEE FMAs in the
+ * operand's own precision):   C[m,n] <- alpha * op(A) * op(B) + beta * C,   op = N, T (or C, complex only).
+ * Same layout rules and early-outs as fb_gemm.  alpha and beta point to HOST memory: {re, im}
+ * (im ignored for FB_F64).  Complex matrices are interleaved (re, im) pairs; ld* count complex elements.
+ * Replaces the bodies of
+ *   dgemm  src/flag_blas/ops/level3/dgemm.py:160-208
+ *   cgemm  src/flag_blas/ops/level3/cgemm.py:192-254
+ *   zgemm  src/flag_blas/ops/level3/zgemm.py:192-254
+ * Never needs a workspace.
+ */
+int fb_gemm_ex(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const double* alpha, const void* A,
+               int64_t lda, const void* B, int64_t ldb, const double* beta, void* C, int64_t ldc, void* stream);
+
 /*
  * Matrix-vector product (the one-column limit of the GEMM path):
  *     trans = N:  y[m] <- alpha * A * x[n]   + beta * y

@@ -164,3 +164,54 @@ def group_mm(kind, A, B, offs):
             C[start:end] = _epilogue(acc, 1.0, 0.0, None, kind)
         start = end
     return C
+
+
+# ------------------------------------------------------- double / complex dense GEMM
+_X_DTYPE = {"fp64": np.float64, "c64": np.complex64, "c128": np.complex128}
+
+
+def gemm_x(kind, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):
+    """``dgemm`` / ``cgemm`` / ``zgemm`` (``ops/level3/dgemm.py:160-208``, ``cgemm.py:192-254``,
+    ``zgemm.py:192-254``) on flat row-major numpy buffers of dtype float64 / complex64 / complex128,
+    in place on ``C``.  ``trans`` 0 = N, 1 = T, 2 = C (conjugate transpose, complex kinds only).  The same
+    early-outs as the other dense operators: a degenerate call scales the whole ``C`` buffer.  The
+    contraction is formed in float64 / complex128 and rounded once to the storage type."""
+    dt = _X_DTYPE[kind]
+    cplx = kind != "fp64"
+    assert transa in ((0, 1, 2) if cplx else (0, 1)) and transb in ((0, 1, 2) if cplx else (0, 1))
+    alpha = complex(alpha) if cplx else float(alpha)
+    beta = complex(beta) if cplx else float(beta)
+    cf = C.reshape(-1)
+    if m == 0 or n == 0 or k == 0 or alpha == 0:
+        if beta == 0:
+            cf[...] = 0
+        elif beta != 1:
+            cf[...] = (beta * cf.astype(np.complex128 if cplx else np.float64)).astype(dt)
+        return None
+    wide = np.complex128 if cplx else np.float64
+    af, bf = A.reshape(-1).astype(wide), B.reshape(-1).astype(wide)
+
+    def view(buf, rows, cols, ld):
+        full = np.zeros(rows * ld, dtype=wide)
+        need = (rows - 1) * ld + cols
+        full[:need] = buf[:need]
+        return full.reshape(rows, ld)[:, :cols]
+
+    a = view(af, m, k, lda) if transa == 0 else view(af, k, m, lda).T
+    b = view(bf, k, n, ldb) if transb == 0 else view(bf, n, k, ldb).T
+    if transa == 2:
+        a = a.conj()
+    if transb == 2:
+        b = b.conj()
+    acc = a @ b
+    need_c = (m - 1) * ldc + n
+    cfull = np.zeros(m * ldc, dtype=wide)
+    cfull[:need_c] = cf[:need_c]
+    cv = cfull.reshape(m, ldc)[:, :n]
+    res = alpha * acc + (beta * cv if beta != 0 else 0)
+    out = np.zeros(m * ldc, dtype=dt)
+    out[:need_c] = cf[:need_c]
+    out2 = out.reshape(m, ldc)
+    out2[:, :n] = res.astype(dt)
+    cf[:need_c] = out[:need_c]
+    return None

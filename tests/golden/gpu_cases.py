@@ -93,10 +93,31 @@ def fp8_gemv_cases():
         yield "fp8gemv_c%d" % ci, (m, n, lda, incx, incy, ky, alpha, beta), A, x, y
 
 
+XGEMM = {"dgemm": ("fp64", torch.float64, 2.5, 0.5), "cgemm": ("c64", torch.complex64, 2.5 + 0.5j, 0.5 - 0.25j),
+         "zgemm": ("c128", torch.complex128, 2.5 + 0.5j, 0.5 - 0.25j)}
+XGEMM_SHAPES = ((40, 72, 45, 3), (33, 17, 64, 0))
+XGEMM_OPS = {False: ((0, 0), (0, 1), (1, 0), (1, 1)), True: ((0, 0), (1, 0), (0, 2), (2, 1), (2, 2))}
+
+
+def xgemm_cases(name):
+    """Yields (key, (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C) as CPU tensors."""
+    kind, dt, alpha, beta = XGEMM[name]
+    gen = torch.Generator(device="cpu").manual_seed(38)
+    for ta, tb in XGEMM_OPS[dt.is_complex]:
+        for ci, (m, n, k, pad) in enumerate(XGEMM_SHAPES):
+            lda, ldb, ldc = (m if ta else k) + pad, (k if tb else n) + pad, n + pad
+            A = torch.randn((k if ta else m), lda, generator=gen, dtype=dt)
+            B = torch.randn((n if tb else k), ldb, generator=gen, dtype=dt)
+            C = torch.randn(m, ldc, generator=gen, dtype=dt)
+            yield "%s_t%d%d_c%d" % (name, ta, tb, ci), (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C
+
+
 def pack(t):
     """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
     if t.dtype in (torch.bfloat16, torch.float16):
         return t.contiguous().view(torch.int16).numpy()
+    if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return t.contiguous().view(torch.uint8).numpy()
     return t.contiguous().numpy()
 
 

@@ -29,7 +29,9 @@ import types
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("FLAGBLAS_REFERENCE", "/root/reference")
+REF = os.environ.get("FLAGBLAS_REFERENCE")  # checkout of the reference project (its `src/` is put on sys.path)
+if not REF:
+    raise SystemExit("set FLAGBLAS_REFERENCE to a checkout of flagos-ai/FlagBLAS")
 
 
 def _import_reference():

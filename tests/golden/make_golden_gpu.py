@@ -9,6 +9,7 @@ Needs an installed copy of the reference (it is not shipped with this repo), e.g
     python -m pip install --no-deps --no-build-isolation --target baseline/_ref /path/to/FlagBLAS
     FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py          # gpu_reference.npz
     FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py gemv     # gpu_reference_gemv.npz
+    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py xgemm    # gpu_reference_xgemm.npz
 
 and a CUDA device.  The same import shims as ``make_golden.py`` apply (stub ``sqlalchemy``,
 ``BLAS_VENDOR`` / ``ARCH`` / ``FLAGGEMS_DB_URL``, pass-through ``libentry`` that launches every kernel
@@ -114,7 +115,30 @@ def _import_reference():
     gv = sys.modules["flag_blas.ops.level2.gemv"]
     for name in ("sgemv", "hgemv", "bfgemv", "fp8_gemv"):
         mods[name] = getattr(gv, name)
+    for name in ("dgemm", "cgemm", "zgemm"):
+        mods[name] = getattr(sys.modules["flag_blas.ops.level3." + name], name)
     return torch, mods
+
+
+def main_xgemm():
+    """``gpu_reference_xgemm.npz``: the reference's generic dgemm / cgemm / zgemm on the seeded cases."""
+    torch, ref = _import_reference()
+    sys.path.insert(0, HERE)
+    import gpu_cases as gc
+
+    dev = "cuda"
+    out = {"device": np.array(torch.cuda.get_device_name(0)), "triton": np.array(__import__("triton").__version__)}
+    for name in ("dgemm", "cgemm", "zgemm"):
+        for key, (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C in gc.xgemm_cases(name):
+            Cd = C.to(dev)
+            ref[name](ta, tb, m, n, k, alpha, A.to(dev), lda, B.to(dev), ldb, beta, Cd, ldc)
+            torch.cuda.synchronize()
+            out[key + "_C"] = Cd.cpu().numpy()
+            out[key + "_probe"] = np.concatenate([A.numpy().ravel()[:4], B.numpy().ravel()[:4]])
+        print(name, "done", flush=True)
+    path = os.path.join(HERE, "gpu_reference_xgemm.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
 
 
 def main_gemv():
@@ -210,5 +234,7 @@ def main():
 if __name__ == "__main__":
     if sys.argv[1:] == ["gemv"]:
         main_gemv()
+    elif sys.argv[1:] == ["xgemm"]:
+        main_xgemm()
     else:
         main()
