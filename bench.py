@@ -39,6 +39,24 @@ WORKLOADS = {
 # BASELINE config 4: 64 experts sharing K and N, token counts ~ Multinomial(T, Zipf(1.2)), seed 3
 MOE = {"name": "group_bfgemm_moe64", "experts": 64, "k": 4096, "n": 1536, "tokens": 32768, "zipf": 1.2, "seed": 3}
 HEADLINE = "hgemm_8192_nn"
+
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    """Keep stdout for the one JSON line: whatever else writes to file descriptor 1 from here on (the NCCL
+    version banner, library chatter) is sent to stderr instead."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line):
+    out = _REAL_STDOUT if _REAL_STDOUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 FALLBACK_TENSOR_PEAK = 1590.0  # TFLOP/s, earlier measurement on this pool, used only without MEASURED_PEAKS.json
 
 
@@ -315,7 +333,7 @@ def run_grouped(args, rank, world, local_rank):
             tf, rows, secs, threads = cpu_baseline.time_dense_rows(T, N, K, 0, 0, target_seconds=12.0, seed=MOE["seed"], scale=1.0)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": "torch.matmul fp32 on %d token rows against one expert's [4096, 1536] weights (inputs upcast), repeated for %.1f s" % (rows, secs)}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if use_dist:
         tdist.destroy_process_group()
 
@@ -393,7 +411,7 @@ def run_gemv(args, local_rank):
                 "ms_per_step": e2e_ms},
         "gpu_launches": args.steps * (2 if ws else 1), "clocks": clk.summary(), "device_status": fb.device_status(),
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_reference(args, rank, world):
@@ -409,7 +427,7 @@ def run_reference(args, rank, world):
         WORKLOADS[MOE["name"]] = ("group_bfgemm", "bf16", 0, 0, MOE["tokens"], MOE["n"], MOE["k"], 1.0, 0.0, 1.0, 0.02, MOE["seed"])
 
     op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
-    per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    per_step = max(0.5, min(20.0, 60.0 / max(1, args.steps + args.warmup)))  # the whole run stays near a minute
     vals, rows, threads = [], 0, 1
     for i in range(args.warmup + args.steps):
         tf, rows, secs, threads = cpu_baseline.time_dense_rows(m, n, k, ta, tb, target_seconds=per_step, seed=seed, scale=sa)
@@ -426,7 +444,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
@@ -441,6 +459,7 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the brief runs of the other BASELINE configs")
     args = ap.parse_args()
+    claim_stdout()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -583,7 +602,7 @@ def main():
             tf, rows, secs, threads = cpu_baseline.time_dense_rows(m, n, k, ta, tb, target_seconds=12.0, seed=seed, scale=sa)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": "torch.matmul fp32 on %d of %d output rows of %s (inputs upcast), repeated for %.1f s" % (rows, m, args.workload, secs)}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if use_dist:
         tdist.destroy_process_group()
 
