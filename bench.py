@@ -35,6 +35,7 @@ WORKLOADS = {
     "tf32gemm_8192_tn": ("tf32gemm", "tf32", 1, 0, 8192, 8192, 8192, 1.5, 0.5, 0.577, 0.577, 4),
     "tf32gemm_16384_tn": ("tf32gemm", "tf32", 1, 0, 16384, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
     "sgemm_512_nn": ("sgemm", "fp32", 0, 0, 512, 512, 512, 1.0, 0.0, 0.577, 0.577, 0),
+    "sgemm_4096_nn": ("sgemm", "fp32", 0, 0, 4096, 4096, 4096, 1.0, 0.0, 0.577, 0.577, 0),
 }
 # BASELINE config 4: 64 experts sharing K and N, token counts ~ Multinomial(T, Zipf(1.2)), seed 3
 MOE = {"name": "group_bfgemm_moe64", "experts": 64, "k": 4096, "n": 1536, "tokens": 32768, "zipf": 1.2, "seed": 3}
@@ -179,7 +180,9 @@ def other_configs(fb, torch, dev):
         elif kind == "tf32":
             rec.update(bound="tensor", frac=tf / (peak / 2), peak=peak / 2)   # TF32 runs at half the 16-bit rate
         elif kind == "fp32":
-            rec.update(bound="fp32 FFMA (latency bound at this size)", frac=None)
+            ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12   # SMs x FP32 lanes x 2 FLOP x max SM clock
+            rec.update(bound="fp32 FFMA" + (" (latency bound at this size)" if m <= 512 else ""), frac=tf / ffma_peak,
+                       peak=ffma_peak)
         else:
             rec.update(bound="tensor", frac=tf / peak, peak=peak)
         out[name] = rec
