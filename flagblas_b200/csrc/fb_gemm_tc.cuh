@@ -330,6 +330,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  // Grouped calls are launched as programmatic dependents of the table builder: everything above ran
+  // while it was still working; its table and tensor maps may be read only from here on.
+  if (grouped) grid_dependency_wait();
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
   const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
 

@@ -72,6 +72,19 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+static int env_int(const char* name, int dflt);
+
+// L2 sector promotion of the tensor maps; FLAGBLAS_B200_L2PROMO = 0 (none), 1 (64 B), 2 (128 B), 3 (256 B,
+// the default) for profiling sweeps.
+static CUtensorMapL2promotion l2_promotion() {
+  switch (env_int("FLAGBLAS_B200_L2PROMO", 3)) {
+    case 0: return CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    case 1: return CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
+    case 2: return CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    default: return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  }
+}
+
 static int elem_size(int dtype) { return (dtype == FB_F16 || dtype == FB_BF16) ? 2 : 4; }
 
 static CUtensorMapDataType map_dtype(int dtype) {
@@ -94,7 +107,7 @@ static int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inn
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, map_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  l2_promotion(),
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     t_last_cuda_error = static_cast<int>(r);
@@ -115,7 +128,7 @@ static int encode_3d(CUtensorMap* map, int dtype, const void* base, uint64_t d0,
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, map_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  l2_promotion(), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     t_last_cuda_error = static_cast<int>(r);
     return FB_ERR_DRIVER;
@@ -223,7 +236,7 @@ static int choose_block_n(long long m, long long n, int tile_m, int workers, boo
   return best_bn;
 }
 
-static int env_int(const char* name, int dflt) {
+int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return (v && *v) ? atoi(v) : dflt;
 }
@@ -272,18 +285,26 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     }
   }
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attrs[1];
+  cudaLaunchAttribute attrs[2];
   const long long workers = PAIR ? st.max_clusters : sm_count;
   const long long use = tiles < workers ? tiles : workers;
   cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * use : use));
   cfg.blockDim = dim3(kNumThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
+  unsigned n_attrs = 0;
   if (PAIR) {
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = 2; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
-    cfg.attrs = attrs; cfg.numAttrs = 1;
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
   }
+  if (p.num_groups > 0 && env_int("FLAGBLAS_B200_PDL", 1) != 0) {
+    // grouped: overlap this kernel's launch and prologue with the table builder queued just before it
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
+  }
+  if (n_attrs) { cfg.attrs = attrs; cfg.numAttrs = n_attrs; }
   TcGemmParams pp = p;
   pp.sk_enabled = 0;
   if (p.num_groups == 0 && p.sk_partials && env_int("FLAGBLAS_B200_STREAMK", 0) != 0) {
@@ -848,6 +869,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   ga.span = static_cast<int>(span);
   ga.allow3d = env_int("FLAGBLAS_B200_TMA3D", 1) != 0 ? 1 : 0;
   ga.b_k_contig = b_k_contig;
+  ga.publish_each = env_int("FLAGBLAS_B200_GROUP_PUBLISH", 1);
   ga.esz = esz;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);

@@ -109,6 +109,8 @@ def test_grouped_tile_plan_variants(env, monkeypatch):
 
 def test_grouped_many_groups():
     _run_group("bf16", [((7 * i) % 90) for i in range(600)], 128, 256, 1.0, 0.0, seed=7)
+    # more groups than the table builder keeps in shared memory (its tile counts then go through global memory)
+    _run_group("fp16", [((5 * i) % 23) for i in range(1500)], 64, 128, 1.0, 0.0, seed=8)
 
 
 def test_group_mm_and_group_gemm():
