@@ -45,6 +45,8 @@ def _load():
     handle.fb_gemm_ex.restype = i32
     handle.fb_gemm_ex.argtypes = [i32, i32, i32, i64, i64, i64, c.POINTER(c.c_double), vp, i64, vp, i64,
                                   c.POINTER(c.c_double), vp, i64, vp]
+    handle.fb_trmm.restype = i32
+    handle.fb_trmm.argtypes = [i32, i32, i32, i32, i32, i64, i64, c.POINTER(c.c_double), vp, i64, vp, i64, vp, i64, vp]
     handle.fb_gemv.restype = i32
     handle.fb_gemv.argtypes = [i32, i32, i64, i64, f32, vp, i64, vp, i64, f32, vp, i64, vp, sz, vp]
     handle.fb_gemv_workspace_bytes.restype = sz
@@ -87,6 +89,7 @@ EXPORTED_SYMBOLS = (
     "fb_gemm",
     "fb_gemm_workspace_bytes",
     "fb_gemm_ex",
+    "fb_trmm",
     "fb_gemv",
     "fb_gemv_workspace_bytes",
     "fb_gemv_fp8",

@@ -27,6 +27,11 @@ PYBIND11_MODULE(c_operators, m) {
     const double alpha[2] = {alpha_re, alpha_im}, beta[2] = {beta_re, beta_im};
     return fb_gemm_ex(dtype, ta, tb, mm, nn, kk, alpha, p(a), lda, p(b), ldb, beta, p(c), ldc, p(stream));
   });
+  m.def("trmm", [](int dtype, int side, int uplo, int trans, int diag, int64_t mm, int64_t nn, double alpha_re, double alpha_im,
+                   addr a, int64_t lda, addr b, int64_t ldb, addr c, int64_t ldc, addr stream) {
+    const double alpha[2] = {alpha_re, alpha_im};
+    return fb_trmm(dtype, side, uplo, trans, diag, mm, nn, alpha, p(a), lda, p(b), ldb, p(c), ldc, p(stream));
+  });
   m.def("gemv", [](int dtype, int trans, int64_t mm, int64_t nn, float alpha, addr a, int64_t lda, addr x, int64_t incx,
                    float beta, addr y, int64_t incy, addr ws, size_t ws_bytes, addr stream) {
     return fb_gemv(dtype, trans, mm, nn, alpha, p(a), lda, p(x), incx, beta, p(y), incy, p(ws), ws_bytes, p(stream));

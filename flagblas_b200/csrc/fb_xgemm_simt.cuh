@@ -1,7 +1,9 @@
 // GEMM on the CUDA cores for the element types the tensor-core path does not cover:
-// double (dgemm), complex<float> (cgemm), complex<double> (zgemm).
+// double (dgemm), complex<float> (cgemm), complex<double> (zgemm) -- and, with one operand read through a
+// triangular mask, the triangular products strmm / dtrmm / ctrmm / ztrmm.
 //
 //   C[m,n] = alpha * op(A) * op(B) + beta * C       op = N, T or C (conjugate transpose)
+//   trmm:  C = alpha * op(tri(A)) * B   (left)   or   C = alpha * B * op(tri(A))   (right)
 //
 // Row-major, any leading dimension and alignment.  64 x 64 output tile per 256-thread CTA, 4 x 4 outputs
 // per thread, k-slices of 8 double buffered through shared memory in k-major order (an operand whose
@@ -19,9 +21,20 @@ struct cfloat { float x, y; };
 struct cdouble { double x, y; };
 
 template <class T> struct XNum;
+template <> struct XNum<float> {
+  using Real = float;
+  static __device__ __forceinline__ float zero() { return 0.f; }
+  static __device__ __forceinline__ float one() { return 1.f; }
+  static __device__ __forceinline__ float make(double re, double) { return static_cast<float>(re); }
+  static __device__ __forceinline__ float conj(float a) { return a; }
+  static __device__ __forceinline__ float fma(float a, float b, float c) { return fmaf(a, b, c); }
+  static __device__ __forceinline__ float mul(float a, float b) { return a * b; }
+  static __device__ __forceinline__ bool is_zero(float a) { return a == 0.f; }
+};
 template <> struct XNum<double> {
   using Real = double;
   static __device__ __forceinline__ double zero() { return 0.0; }
+  static __device__ __forceinline__ double one() { return 1.0; }
   static __device__ __forceinline__ double make(double re, double) { return re; }
   static __device__ __forceinline__ double conj(double a) { return a; }
   static __device__ __forceinline__ double fma(double a, double b, double c) { return ::fma(a, b, c); }
@@ -31,6 +44,7 @@ template <> struct XNum<double> {
 template <> struct XNum<cfloat> {
   using Real = float;
   static __device__ __forceinline__ cfloat zero() { return cfloat{0.f, 0.f}; }
+  static __device__ __forceinline__ cfloat one() { return cfloat{1.f, 0.f}; }
   static __device__ __forceinline__ cfloat make(double re, double im) { return cfloat{static_cast<float>(re), static_cast<float>(im)}; }
   static __device__ __forceinline__ cfloat conj(cfloat a) { return cfloat{a.x, -a.y}; }
   static __device__ __forceinline__ cfloat fma(cfloat a, cfloat b, cfloat c) {
@@ -44,6 +58,7 @@ template <> struct XNum<cfloat> {
 template <> struct XNum<cdouble> {
   using Real = double;
   static __device__ __forceinline__ cdouble zero() { return cdouble{0.0, 0.0}; }
+  static __device__ __forceinline__ cdouble one() { return cdouble{1.0, 0.0}; }
   static __device__ __forceinline__ cdouble make(double re, double im) { return cdouble{re, im}; }
   static __device__ __forceinline__ cdouble conj(cdouble a) { return cdouble{a.x, -a.y}; }
   static __device__ __forceinline__ cdouble fma(cdouble a, cdouble b, cdouble c) {
@@ -66,6 +81,14 @@ struct XgemmParams {
   long long ldc;
   int transa, transb;  // 0 = N, 1 = T, 2 = C
   int tiles_n;
+  // Triangular operand (trmm): 0 = none, 1 = A (left product), 2 = B (right product).  The mask applies to
+  // the matrix as STORED (before op()): `tri_upper` keeps col >= row, else col <= row; `tri_unit` reads the
+  // diagonal as 1 without touching memory.
+  int tri_operand, tri_upper, tri_unit;
+};
+
+struct TriMask {
+  bool on, upper, unit;
 };
 
 constexpr int kXTile = 64, kXK = 8;
@@ -75,7 +98,7 @@ constexpr int kXTile = 64, kXK = 8;
 //   MN-contiguous storage [k][mn] (A with trans = T / C, B with trans = N): thread -> (k = tid / 32, mn = 2 * (tid % 32))
 template <class T>
 __device__ __forceinline__ void xgemm_fetch(const T* __restrict__ base, long long ld, bool k_contig, bool conj, int mn0,
-                                            int k0, int mn_lim, int k_lim, int tid, T (&r)[2]) {
+                                            int k0, int mn_lim, int k_lim, int tid, TriMask tri, T (&r)[2]) {
   using N = XNum<T>;
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -83,8 +106,13 @@ __device__ __forceinline__ void xgemm_fetch(const T* __restrict__ base, long lon
     if (k_contig) { mn = mn0 + tid / 4; kk = k0 + 2 * (tid % 4) + j; }
     else { kk = k0 + tid / 32; mn = mn0 + 2 * (tid % 32) + j; }
     T v = N::zero();
-    if (mn < mn_lim && kk < k_lim)
-      v = k_contig ? base[static_cast<long long>(mn) * ld + kk] : base[static_cast<long long>(kk) * ld + mn];
+    bool read = mn < mn_lim && kk < k_lim;
+    if (tri.on && read) {
+      const int row = k_contig ? mn : kk, col = k_contig ? kk : mn;  // position in the stored matrix
+      if (row == col && tri.unit) { v = N::one(); read = false; }
+      else if (tri.upper ? col < row : col > row) read = false;
+    }
+    if (read) v = k_contig ? base[static_cast<long long>(mn) * ld + kk] : base[static_cast<long long>(kk) * ld + mn];
     r[j] = conj ? N::conj(v) : v;
   }
 }
@@ -110,6 +138,18 @@ __global__ void __launch_bounds__(256) xgemm_simt_kernel(const XgemmParams p) {
   const T* B = static_cast<const T*>(p.B);
   const bool a_kc = p.transa == 0, b_kc = p.transb != 0;
   const bool a_cj = p.transa == 2, b_cj = p.transb == 2;
+  const TriMask tri_a{p.tri_operand == 1, p.tri_upper != 0, p.tri_unit != 0};
+  const TriMask tri_b{p.tri_operand == 2, p.tri_upper != 0, p.tri_unit != 0};
+  // k range in which this tile's slice of the triangular operand can be non-zero.  op(A) is upper
+  // triangular when the stored matrix is upper and not transposed, or lower and transposed.
+  int k_begin = 0, k_end = p.k;
+  if (p.tri_operand == 1) {          // op(A)(i, kk): upper keeps kk >= i
+    const bool up = (p.tri_upper != 0) != (p.transa != 0);
+    if (up) k_begin = m0 / kXK * kXK; else k_end = min(p.k, m0 + kXTile);
+  } else if (p.tri_operand == 2) {   // op(A)(kk, j): upper keeps kk <= j
+    const bool up = (p.tri_upper != 0) != (p.transb != 0);
+    if (up) k_end = min(p.k, n0 + kXTile); else k_begin = n0 / kXK * kXK;
+  }
 
   T acc[4][4];
 #pragma unroll
@@ -118,17 +158,17 @@ __global__ void __launch_bounds__(256) xgemm_simt_kernel(const XgemmParams p) {
     for (int j = 0; j < 4; ++j) acc[i][j] = N::zero();
 
   T ra[2], rb[2];
-  const int k_iters = (p.k + kXK - 1) / kXK;
-  xgemm_fetch<T>(A, p.lda, a_kc, a_cj, m0, 0, p.m, p.k, tid, ra);
-  xgemm_fetch<T>(B, p.ldb, b_kc, b_cj, n0, 0, p.n, p.k, tid, rb);
+  const int k_iters = k_end > k_begin ? (k_end - k_begin + kXK - 1) / kXK : 0;
+  xgemm_fetch<T>(A, p.lda, a_kc, a_cj, m0, k_begin, p.m, k_end, tid, tri_a, ra);
+  xgemm_fetch<T>(B, p.ldb, b_kc, b_cj, n0, k_begin, p.n, k_end, tid, tri_b, rb);
   xgemm_stash<T>(As[0], a_kc, tid, ra);
   xgemm_stash<T>(Bs[0], b_kc, tid, rb);
   __syncthreads();
   for (int it = 0; it < k_iters; ++it) {
     const int cur = it & 1;
     if (it + 1 < k_iters) {
-      xgemm_fetch<T>(A, p.lda, a_kc, a_cj, m0, (it + 1) * kXK, p.m, p.k, tid, ra);
-      xgemm_fetch<T>(B, p.ldb, b_kc, b_cj, n0, (it + 1) * kXK, p.n, p.k, tid, rb);
+      xgemm_fetch<T>(A, p.lda, a_kc, a_cj, m0, k_begin + (it + 1) * kXK, p.m, k_end, tid, tri_a, ra);
+      xgemm_fetch<T>(B, p.ldb, b_kc, b_cj, n0, k_begin + (it + 1) * kXK, p.n, k_end, tid, tri_b, rb);
     }
     const T* as = As[cur];
     const T* bs = Bs[cur];

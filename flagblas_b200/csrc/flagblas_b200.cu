@@ -658,7 +658,7 @@ static int run_gemv_fp8_y(int y_dtype, long long m, long long n, float alpha, co
 template <class T>
 static int run_xgemm(int transa, int transb, long long m, long long n, long long k, const double* alpha, const void* A,
                      long long lda, const void* B, long long ldb, const double* beta, void* C, long long ldc,
-                     bool complex_type, cudaStream_t stream) {
+                     bool complex_type, cudaStream_t stream, int tri_operand = 0, int tri_upper = 0, int tri_unit = 0) {
   const double ar = alpha[0], ai = complex_type ? alpha[1] : 0.0;
   const double br = beta[0], bi = complex_type ? beta[1] : 0.0;
   if (k == 0 || (ar == 0.0 && ai == 0.0)) {
@@ -675,6 +675,7 @@ static int run_xgemm(int transa, int transb, long long m, long long n, long long
   p.alpha_re = ar; p.alpha_im = ai; p.beta_re = br; p.beta_im = bi;
   p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
   p.transa = transa; p.transb = transb;
+  p.tri_operand = tri_operand; p.tri_upper = tri_upper; p.tri_unit = tri_unit;
   p.tiles_n = static_cast<int>((n + kXTile - 1) / kXTile);
   const long long tiles = ((m + kXTile - 1) / kXTile) * p.tiles_n;
   if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
@@ -1134,6 +1135,39 @@ int fb_gemm_ex(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t 
     case FB_F64: return run_xgemm<double>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, false, stream);
     case FB_C64: return run_xgemm<cfloat>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, true, stream);
     default: return run_xgemm<cdouble>(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, true, stream);
+  }
+}
+
+int fb_trmm(int dtype, int side, int uplo, int trans, int diag, int64_t m, int64_t n, const double* alpha, const void* A,
+            int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (dtype != FB_F32 && dtype != FB_F64 && dtype != FB_C64 && dtype != FB_C128) return FB_ERR_INVALID_ARG;
+  const bool cplx = dtype == FB_C64 || dtype == FB_C128;
+  if ((side != 0 && side != 1) || (uplo != 0 && uplo != 1) || (diag != 0 && diag != 1)) return FB_ERR_INVALID_ARG;
+  if (trans < 0 || trans > (cplx ? FB_OP_C : FB_OP_T)) return FB_ERR_INVALID_ARG;
+  if (m < 0 || n < 0 || !alpha) return FB_ERR_INVALID_ARG;
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return FB_OK;
+  const int64_t kdim = side == 0 ? m : n;
+  if (!C || ldc < n) return FB_ERR_INVALID_ARG;
+  const bool zero = alpha[0] == 0.0 && (!cplx || alpha[1] == 0.0);
+  if (!zero && (!A || !B || lda < kdim || ldb < n)) return FB_ERR_INVALID_ARG;
+  const DeviceInfo* di = device_info();
+  if (!di) return FB_ERR_LAUNCH;
+  if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
+  const double beta[2] = {0.0, 0.0};
+  // left:  C[m,n] = alpha * op(tri A)[m,m] * B[m,n]  -> GEMM operands (A, trans) x (B, N), k = m
+  // right: C[m,n] = alpha * B[m,n] * op(tri A)[n,n]  -> GEMM operands (B, N) x (A, trans), k = n
+  const void* ga = side == 0 ? A : B;
+  const void* gb = side == 0 ? B : A;
+  const int64_t glda = side == 0 ? lda : ldb, gldb = side == 0 ? ldb : lda;
+  const int ta = side == 0 ? trans : 0, tb = side == 0 ? 0 : trans;
+  const int tri = zero ? 0 : (side == 0 ? 1 : 2);
+  switch (dtype) {
+    case FB_F32: return run_xgemm<float>(ta, tb, m, n, kdim, alpha, ga, glda, gb, gldb, beta, C, ldc, false, stream, tri, uplo, diag);
+    case FB_F64: return run_xgemm<double>(ta, tb, m, n, kdim, alpha, ga, glda, gb, gldb, beta, C, ldc, false, stream, tri, uplo, diag);
+    case FB_C64: return run_xgemm<cfloat>(ta, tb, m, n, kdim, alpha, ga, glda, gb, gldb, beta, C, ldc, true, stream, tri, uplo, diag);
+    default: return run_xgemm<cdouble>(ta, tb, m, n, kdim, alpha, ga, glda, gb, gldb, beta, C, ldc, true, stream, tri, uplo, diag);
   }
 }
 

@@ -98,6 +98,20 @@ int fb_gemm_ex(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t 
                int64_t lda, const void* B, int64_t ldb, const double* beta, void* C, int64_t ldc, void* stream);
 
 /*
+ * Triangular matrix product, out of place (the reference's row-major strmm / dtrmm / ctrmm / ztrmm):
+ *     side = 0 (left):   C[m,n] <- alpha * op(tri(A))[m,m] * B[m,n]
+ *     side = 1 (right):  C[m,n] <- alpha * B[m,n] * op(tri(A))[n,n]
+ *   A row-major [k, lda >= k] (k = m or n); only its lower (uplo = 0: col <= row) or upper (uplo = 1)
+ *   triangle is read; diag = 1 reads the diagonal as 1; trans = N, T (or C for the complex types).
+ *   dtype FB_F32 / FB_F64 / FB_C64 / FB_C128; alpha = host {re, im}.  alpha == 0 zero-fills the m x n block of C.
+ *   B and C must not overlap (the Python wrappers copy B first when they do).
+ * Replaces the bodies of strmm / dtrmm / ctrmm / ztrmm, src/flag_blas/ops/level3/trmm.py:2095-2231,
+ * 2234-2329, 3161-3292, 4743-4939 (generic kernel :39-196).
+ */
+int fb_trmm(int dtype, int side, int uplo, int trans, int diag, int64_t m, int64_t n, const double* alpha, const void* A,
+            int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, void* stream);
+
+/*
  * Matrix-vector product (the one-column limit of the GEMM path):
  *     trans = N:  y[m] <- alpha * A * x[n]   + beta * y
  *     trans = T:  y[n] <- alpha * A^T * x[m] + beta * y

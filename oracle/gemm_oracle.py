@@ -215,3 +215,36 @@ def gemm_x(kind, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc):
     out2[:, :n] = res.astype(dt)
     cf[:need_c] = out[:need_c]
     return None
+
+
+_T_DTYPE = {"fp32": np.float32, "fp64": np.float64, "c64": np.complex64, "c128": np.complex128}
+
+
+def trmm(kind, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, C, ldc):
+    """``strmm`` / ``dtrmm`` / ``ctrmm`` / ``ztrmm`` (``ops/level3/trmm.py:39-196`` generic kernel, wrappers
+    ``:2095-2231`` ...): ``C[:m, :n] = alpha * op(tri(A)) @ B`` (``side`` 0) or ``alpha * B @ op(tri(A))``
+    (``side`` 1) on flat row-major numpy buffers, in place on ``C``; ``uplo`` 0 = lower, 1 = upper triangle of
+    the stored ``A``; ``diag`` 1 = unit diagonal; ``trans`` 0 / 1 / 2 = N / T / C.  ``m == 0 or n == 0``
+    leaves ``C`` alone, ``alpha == 0`` zero-fills the block.  Formed in float64 / complex128, rounded once."""
+    dt = _T_DTYPE[kind]
+    if m == 0 or n == 0:
+        return None
+    wide = np.complex128 if kind in ("c64", "c128") else np.float64
+    kdim = m if side == 0 else n
+    cf = C.reshape(-1)
+    cv = cf[: m * ldc].reshape(m, ldc)[:, :n]
+    if alpha == 0:
+        cv[...] = 0
+        return None
+    a = A.reshape(-1)[: kdim * lda].reshape(kdim, lda)[:, :kdim].astype(wide)
+    a = np.triu(a) if uplo == 1 else np.tril(a)
+    if diag == 1:
+        a = a - np.diag(np.diag(a)) + np.eye(kdim, dtype=wide)
+    if trans == 1:
+        a = a.T
+    elif trans == 2:
+        a = a.conj().T
+    b = B.reshape(-1)[: m * ldb].reshape(m, ldb)[:, :n].astype(wide)
+    res = alpha * (a @ b if side == 0 else b @ a)
+    cv[...] = res.astype(dt)
+    return None

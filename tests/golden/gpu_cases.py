@@ -112,6 +112,28 @@ def xgemm_cases(name):
             yield "%s_t%d%d_c%d" % (name, ta, tb, ci), (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C
 
 
+TRMM = {"strmm": ("fp32", torch.float32, 1.5), "dtrmm": ("fp64", torch.float64, 1.5),
+        "ctrmm": ("c64", torch.complex64, 1.5 - 0.5j), "ztrmm": ("c128", torch.complex128, 1.5 - 0.5j)}
+# (side, uplo, trans, diag, m, n, pad)
+TRMM_MODES = ((0, 0, 0, 0, 70, 40, 2), (0, 1, 1, 1, 70, 40, 0), (1, 1, 0, 0, 36, 72, 3), (1, 0, 1, 1, 36, 72, 0),
+              (0, 1, 2, 0, 33, 20, 0), (1, 0, 2, 1, 20, 33, 1))
+
+
+def trmm_cases(name):
+    """Yields (key, (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C) as CPU tensors."""
+    kind, dt, alpha = TRMM[name]
+    gen = torch.Generator(device="cpu").manual_seed(39)
+    for ci, (side, uplo, trans, diag, m, n, pad) in enumerate(TRMM_MODES):
+        if trans == 2 and not dt.is_complex:
+            continue
+        k = m if side == 0 else n
+        lda, ldb, ldc = k + pad, n + pad, n + pad
+        A = torch.randn(k, lda, generator=gen, dtype=dt)
+        B = torch.randn(m, ldb, generator=gen, dtype=dt)
+        C = torch.randn(m, ldc, generator=gen, dtype=dt)
+        yield "%s_c%d" % (name, ci), (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C
+
+
 def pack(t):
     """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
     if t.dtype in (torch.bfloat16, torch.float16):

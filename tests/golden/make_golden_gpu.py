@@ -117,11 +117,14 @@ def _import_reference():
         mods[name] = getattr(gv, name)
     for name in ("dgemm", "cgemm", "zgemm"):
         mods[name] = getattr(sys.modules["flag_blas.ops.level3." + name], name)
+    for name in ("strmm", "dtrmm", "ctrmm", "ztrmm"):
+        mods[name] = getattr(sys.modules["flag_blas.ops.level3.trmm"], name)
     return torch, mods
 
 
 def main_xgemm():
-    """``gpu_reference_xgemm.npz``: the reference's generic dgemm / cgemm / zgemm on the seeded cases."""
+    """``gpu_reference_xgemm.npz``: the reference's dgemm / cgemm / zgemm and strmm / dtrmm / ctrmm / ztrmm on the
+    seeded cases."""
     torch, ref = _import_reference()
     sys.path.insert(0, HERE)
     import gpu_cases as gc
@@ -132,6 +135,14 @@ def main_xgemm():
         for key, (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta), A, B, C in gc.xgemm_cases(name):
             Cd = C.to(dev)
             ref[name](ta, tb, m, n, k, alpha, A.to(dev), lda, B.to(dev), ldb, beta, Cd, ldc)
+            torch.cuda.synchronize()
+            out[key + "_C"] = Cd.cpu().numpy()
+            out[key + "_probe"] = np.concatenate([A.numpy().ravel()[:4], B.numpy().ravel()[:4]])
+        print(name, "done", flush=True)
+    for name in ("strmm", "dtrmm", "ctrmm", "ztrmm"):
+        for key, (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C in gc.trmm_cases(name):
+            Cd = C.to(dev)
+            ref[name](side, uplo, trans, diag, m, n, alpha, A.to(dev), lda, B.to(dev), ldb, Cd, ldc)
             torch.cuda.synchronize()
             out[key + "_C"] = Cd.cpu().numpy()
             out[key + "_probe"] = np.concatenate([A.numpy().ravel()[:4], B.numpy().ravel()[:4]])

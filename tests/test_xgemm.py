@@ -122,3 +122,82 @@ def test_shapes_edges_and_early_outs(name):
         with pytest.raises(AssertionError):
             op(2, 0, 4, 4, 4, 1.0, A, 4, A, 4, 0.0, C, 4)             # no conjugate transpose for real types
     assert fb.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------- trmm
+TRMM_RTOL = {"strmm": 1e-5, "dtrmm": 1e-12, "ctrmm": 1e-5, "ztrmm": 1e-12}
+
+
+def _trmm_oracle(name, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, C, ldc):
+    c = C.numpy().copy()
+    go.trmm(gc.TRMM[name][0], side, uplo, trans, diag, m, n, alpha, A.numpy(), lda, B.numpy(), ldb, c, ldc)
+    return torch.from_numpy(c)
+
+
+@pytest.mark.parametrize("name", ["strmm", "dtrmm", "ctrmm", "ztrmm"])
+def test_trmm_oracle_vs_reference_on_gpu(z, name):
+    for key, (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C in gc.trmm_cases(name):
+        np.testing.assert_array_equal(np.concatenate([A.numpy().ravel()[:4], B.numpy().ravel()[:4]]), z[key + "_probe"])
+        ref = torch.from_numpy(z[key + "_C"])
+        got = _trmm_oracle(name, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, C, ldc)
+        assert torch.equal(ref[:, n:], C[:, n:])
+        k = m if side == 0 else n
+        scale = abs(alpha) * k ** 0.5 * _rms(A) * _rms(B)
+        _close(got[:, :n], ref[:, :n], 1e-5 if name in ("strmm", "ctrmm") else 1e-10, scale, key)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["strmm", "dtrmm", "ctrmm", "ztrmm"])
+def test_trmm_against_oracle_and_reference_vectors(z, name):
+    import flagblas_b200 as fb
+    for key, (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C in gc.trmm_cases(name):
+        Cd = C.to(DEV)
+        getattr(fb, name)(side, uplo, trans, diag, m, n, alpha, A.to(DEV), lda, B.to(DEV), ldb, Cd, ldc)
+        torch.cuda.synchronize()
+        got = Cd.cpu()
+        k = m if side == 0 else n
+        scale = abs(alpha) * k ** 0.5 * _rms(A) * _rms(B)
+        assert torch.equal(got[:, n:], C[:, n:])
+        _close(got[:, :n], _trmm_oracle(name, side, uplo, trans, diag, m, n, alpha, A, lda, B, ldb, C, ldc)[:, :n],
+               TRMM_RTOL[name], scale, key)
+        _close(got[:, :n], torch.from_numpy(z[key + "_C"])[:, :n], 1e-5 if name in ("strmm", "ctrmm") else 1e-10, scale,
+               key + " vs reference")
+    assert fb.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["strmm", "ztrmm"])
+def test_trmm_all_modes_in_place_and_poisoned_triangle(name):
+    """Every (side, uplo, trans, diag) combination on ragged sizes; the unused triangle (and, for unit
+    diagonals, the diagonal) of A holds NaN and must never be read; B and C may be the same tensor."""
+    import flagblas_b200 as fb
+    kind, dt, alpha = gc.TRMM[name]
+    g = torch.Generator(device="cpu").manual_seed(11)
+    for side in (0, 1):
+        for uplo in (0, 1):
+            for trans in ((0, 1, 2) if dt.is_complex else (0, 1)):
+                for diag in (0, 1):
+                    m, n = (150, 70) if side == 0 else (70, 150)
+                    k = m if side == 0 else n
+                    A = torch.randn(k, k, generator=g, dtype=dt)
+                    B = torch.randn(m, n, generator=g, dtype=dt)
+                    ref = _trmm_oracle(name, side, uplo, trans, diag, m, n, alpha, A, k, B, n, torch.zeros(m, n, dtype=dt), n)
+                    Ap = A.clone()
+                    mask = torch.tril(torch.ones(k, k), -1).bool() if uplo == 1 else torch.triu(torch.ones(k, k), 1).bool()
+                    if diag == 1:
+                        mask |= torch.eye(k).bool()
+                    Ap[mask] = float("nan")
+                    Bd = B.to(DEV)
+                    getattr(fb, name)(side, uplo, trans, diag, m, n, alpha, Ap.to(DEV), k, Bd, n, Bd, n)   # in place
+                    torch.cuda.synchronize()
+                    _close(Bd.cpu(), ref, TRMM_RTOL[name], abs(alpha) * k ** 0.5 * _rms(A) * _rms(B),
+                           "%s side=%d uplo=%d trans=%d diag=%d" % (name, side, uplo, trans, diag))
+    C = torch.full((8, 8), float("nan"), dtype=dt, device=DEV)
+    A = torch.ones(8, 8, dtype=dt, device=DEV)
+    getattr(fb, name)(0, 0, 0, 0, 8, 8, 0.0, A, 8, A, 8, C, 8)             # alpha == 0: zero fill
+    assert torch.equal(C.cpu(), torch.zeros(8, 8, dtype=dt))
+    getattr(fb, name)(0, 0, 0, 0, 0, 8, 1.0, A, 8, A, 8, C, 8)             # m == 0: untouched
+    assert torch.equal(C.cpu(), torch.zeros(8, 8, dtype=dt))
+    with pytest.raises(AssertionError):
+        getattr(fb, name)(2, 0, 0, 0, 8, 8, 1.0, A, 8, A, 8, C, 8)
+    assert fb.device_status() == 0
