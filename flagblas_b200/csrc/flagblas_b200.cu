@@ -8,6 +8,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 namespace fb {
 __device__ int g_fb_status = 0;
@@ -18,6 +19,7 @@ __device__ int g_fb_status = 0;
 #include "fb_sgemm_simt.cuh"
 #include "fb_gemv.cuh"
 #include "fb_xgemm_simt.cuh"
+#include "fb_dgemm_mma.cuh"
 
 namespace fb {
 
@@ -655,6 +657,31 @@ static int run_gemv_fp8_y(int y_dtype, long long m, long long n, float alpha, co
 }
 
 // --------------------------------------------------- double / complex GEMM on the CUDA cores
+template <bool AK, bool BKM>
+static int launch_dgemm_mma_t(XgemmParams p, cudaStream_t stream) {
+  auto kern = dgemm_mma_kernel<AK, BKM>;
+  constexpr int kBytes = kDmStages * (DmTile<kDmBM, AK>::kDoubles + DmTile<kDmBN, BKM>::kDoubles) * 8;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    attr_set[dev] = true;
+  }
+  p.tiles_n = (p.n + kDmBN - 1) / kDmBN;
+  const long long tiles = static_cast<long long>((p.m + kDmBM - 1) / kDmBM) * p.tiles_n;
+  if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  kern<<<static_cast<unsigned>(tiles), 256, kBytes, stream>>>(p);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+// fp64 tensor path for 16-byte aligned operands; a_kc / b_kc: the operand is stored with K contiguous.
+static int launch_dgemm_mma(const XgemmParams& p, bool a_kc, bool b_kc, cudaStream_t stream) {
+  if (a_kc) return b_kc ? launch_dgemm_mma_t<true, true>(p, stream) : launch_dgemm_mma_t<true, false>(p, stream);
+  return b_kc ? launch_dgemm_mma_t<false, true>(p, stream) : launch_dgemm_mma_t<false, false>(p, stream);
+}
+
 template <class T>
 static int run_xgemm(int transa, int transb, long long m, long long n, long long k, const double* alpha, const void* A,
                      long long lda, const void* B, long long ldb, const double* beta, void* C, long long ldc,
@@ -676,6 +703,9 @@ static int run_xgemm(int transa, int transb, long long m, long long n, long long
   p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
   p.transa = transa; p.transb = transb;
   p.tri_operand = tri_operand; p.tri_upper = tri_upper; p.tri_unit = tri_unit;
+  if (std::is_same<T, double>::value && tri_operand == 0 && aligned16(A, lda, 8) && aligned16(B, ldb, 8) &&
+      env_int("FLAGBLAS_B200_DGEMM_MMA", 1) != 0)
+    return launch_dgemm_mma(p, transa == 0, transb != 0, stream);
   p.tiles_n = static_cast<int>((n + kXTile - 1) / kXTile);
   const long long tiles = ((m + kXTile - 1) / kXTile) * p.tiles_n;
   if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;

@@ -201,3 +201,32 @@ def test_trmm_all_modes_in_place_and_poisoned_triangle(name):
     with pytest.raises(AssertionError):
         getattr(fb, name)(2, 0, 0, 0, 8, 8, 1.0, A, 8, A, 8, C, 8)
     assert fb.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_dgemm_tensor_path_and_cuda_core_path_agree(monkeypatch):
+    """16-byte aligned fp64 operands take the DMMA kernel; FLAGBLAS_B200_DGEMM_MMA=0 forces the CUDA-core
+    kernel.  Both do IEEE FMAs: same tolerance against the oracle, and close agreement with each other."""
+    import flagblas_b200 as fb
+    g = torch.Generator(device="cpu").manual_seed(17)
+    for (m, n, k) in [(128, 64, 16), (130, 66, 50), (512, 384, 1000), (64, 1000, 72), (1000, 30, 256)]:
+        for ta in (0, 1):
+            for tb in (0, 1):
+                lda = ((m if ta else k) + 1) // 2 * 2 + 2
+                ldb = ((k if tb else n) + 1) // 2 * 2 + 2
+                ldc = n + 1                                           # C may have any pitch
+                A = torch.randn((k if ta else m), lda, generator=g, dtype=torch.float64)
+                B = torch.randn((n if tb else k), ldb, generator=g, dtype=torch.float64)
+                C = torch.randn(m, ldc, generator=g, dtype=torch.float64)
+                ref = _oracle("dgemm", ta, tb, m, n, k, 2.5, A, lda, B, ldb, 0.5, C, ldc)
+                outs = []
+                for mma in ("1", "0"):
+                    monkeypatch.setenv("FLAGBLAS_B200_DGEMM_MMA", mma)
+                    Cd = C.to(DEV)
+                    fb.dgemm(ta, tb, m, n, k, 2.5, A.to(DEV), lda, B.to(DEV), ldb, 0.5, Cd, ldc)
+                    torch.cuda.synchronize()
+                    outs.append(Cd.cpu())
+                    scale = 2.5 * k ** 0.5 * _rms(A) * _rms(B) + 0.5 * _rms(C)
+                    _close(outs[-1], ref, 1e-12, scale, "dgemm mma=%s %dx%dx%d t%d%d" % (mma, m, n, k, ta, tb))
+                assert torch.equal(outs[0][:, n:], C[:, n:])
+    assert fb.device_status() == 0
