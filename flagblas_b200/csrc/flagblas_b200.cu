@@ -676,6 +676,30 @@ static int launch_dgemm_mma_t(XgemmParams p, cudaStream_t stream) {
   return FB_OK;
 }
 
+template <bool AK, bool BKM>
+static int launch_zgemm_mma_t(XgemmParams p, cudaStream_t stream) {
+  auto kern = zgemm_mma_kernel<AK, BKM>;
+  constexpr int kBytes = kZmStages * (ZmTile<AK>::kElems + ZmTile<BKM>::kElems) * 16;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    attr_set[dev] = true;
+  }
+  p.tiles_n = (p.n + kZmT - 1) / kZmT;
+  const long long tiles = static_cast<long long>((p.m + kZmT - 1) / kZmT) * p.tiles_n;
+  if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;
+  kern<<<static_cast<unsigned>(tiles), 256, kBytes, stream>>>(p);
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
+}
+
+static int launch_zgemm_mma(const XgemmParams& p, bool a_kc, bool b_kc, cudaStream_t stream) {
+  if (a_kc) return b_kc ? launch_zgemm_mma_t<true, true>(p, stream) : launch_zgemm_mma_t<true, false>(p, stream);
+  return b_kc ? launch_zgemm_mma_t<false, true>(p, stream) : launch_zgemm_mma_t<false, false>(p, stream);
+}
+
 // fp64 tensor path for 16-byte aligned operands; a_kc / b_kc: the operand is stored with K contiguous.
 static int launch_dgemm_mma(const XgemmParams& p, bool a_kc, bool b_kc, cudaStream_t stream) {
   if (a_kc) return b_kc ? launch_dgemm_mma_t<true, true>(p, stream) : launch_dgemm_mma_t<true, false>(p, stream);
@@ -706,6 +730,9 @@ static int run_xgemm(int transa, int transb, long long m, long long n, long long
   if (std::is_same<T, double>::value && tri_operand == 0 && aligned16(A, lda, 8) && aligned16(B, ldb, 8) &&
       env_int("FLAGBLAS_B200_DGEMM_MMA", 1) != 0)
     return launch_dgemm_mma(p, transa == 0, transb != 0, stream);
+  if (std::is_same<T, cdouble>::value && tri_operand == 0 && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
+      env_int("FLAGBLAS_B200_DGEMM_MMA", 1) != 0)
+    return launch_zgemm_mma(p, transa == 0, transb != 0, stream);
   p.tiles_n = static_cast<int>((n + kXTile - 1) / kXTile);
   const long long tiles = ((m + kXTile - 1) / kXTile) * p.tiles_n;
   if (tiles > 0x7fffffffLL) return FB_ERR_UNSUPPORTED;

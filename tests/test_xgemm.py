@@ -230,3 +230,29 @@ def test_dgemm_tensor_path_and_cuda_core_path_agree(monkeypatch):
                     _close(outs[-1], ref, 1e-12, scale, "dgemm mma=%s %dx%dx%d t%d%d" % (mma, m, n, k, ta, tb))
                 assert torch.equal(outs[0][:, n:], C[:, n:])
     assert fb.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_zgemm_tensor_path_and_cuda_core_path_agree(monkeypatch):
+    """complex128 on the DMMA kernel (four real MMAs per complex multiply-add) vs the CUDA-core kernel
+    (FLAGBLAS_B200_DGEMM_MMA=0): every op combination, ragged sizes, complex alpha and beta."""
+    import flagblas_b200 as fb
+    g = torch.Generator(device="cpu").manual_seed(19)
+    dt = torch.complex128
+    alpha, beta = 2.5 + 0.5j, 0.5 - 0.25j
+    for (m, n, k) in [(64, 64, 8), (70, 50, 33), (300, 200, 257)]:
+        for ta in (0, 1, 2):
+            for tb in (0, 1, 2):
+                lda, ldb, ldc = (m if ta else k) + 1, (k if tb else n) + 3, n + 1
+                A = torch.randn((k if ta else m), lda, generator=g, dtype=dt)
+                B = torch.randn((n if tb else k), ldb, generator=g, dtype=dt)
+                C = torch.randn(m, ldc, generator=g, dtype=dt)
+                ref = _oracle("zgemm", ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
+                scale = abs(alpha) * k ** 0.5 * _rms(A) * _rms(B) + abs(beta) * _rms(C)
+                for mma in ("1", "0"):
+                    monkeypatch.setenv("FLAGBLAS_B200_DGEMM_MMA", mma)
+                    Cd = C.to(DEV)
+                    fb.zgemm(ta, tb, m, n, k, alpha, A.to(DEV), lda, B.to(DEV), ldb, beta, Cd, ldc)
+                    torch.cuda.synchronize()
+                    _close(Cd.cpu(), ref, 1e-12, scale, "zgemm mma=%s %dx%dx%d t%d%d" % (mma, m, n, k, ta, tb))
+    assert fb.device_status() == 0
