@@ -217,8 +217,12 @@ __device__ __forceinline__ void pipe_load(float* __restrict__ s, const float* __
   }
 }
 
-template <int BM, int BN, bool AK, bool BKM>
-__global__ void __launch_bounds__(256) sgemm_pipe_kernel(const SimtParams p) {
+// PACK: the FMAs are issued as packed pairs (fma.rn.f32x2, two IEEE fp32 FMAs per instruction on sm_100):
+// the same arithmetic in half the issue slots, which leaves room for the shared-memory loads next to them.
+// 1 = pairs of neighbouring columns (B fragments arrive as float4: the pair is already adjacent in registers),
+// 2 = pairs of neighbouring rows (the same for A), 0 = scalar FMAs.
+template <int BM, int BN, bool AK, bool BKM, int PACK>
+__global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) {
   constexpr int TM = BM / 16, TN = BN / 16;
   constexpr int RG = TM / 4, CG = TN / 4;
   constexpr int kAFloats = PipeTile<BM, AK>::kFloats, kBFloats = PipeTile<BN, BKM>::kFloats;
@@ -298,12 +302,38 @@ __global__ void __launch_bounds__(256) sgemm_pipe_kernel(const SimtParams p) {
             bf[h][g * 4 + 0] = v.x; bf[h][g * 4 + 1] = v.y; bf[h][g * 4 + 2] = v.z; bf[h][g * 4 + 3] = v.w;
           }
       }
+      if (PACK == 1) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int i = 0; i < TM; ++i)
+          for (int i = 0; i < TM; ++i) {
+            const float2 a2 = make_float2(af[h][i], af[h][i]);
 #pragma unroll
-          for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(af[h][i], bf[h][j], acc[i][j]);
+            for (int j = 0; j < TN; j += 2) {
+              const float2 r = __ffma2_rn(a2, make_float2(bf[h][j], bf[h][j + 1]), make_float2(acc[i][j], acc[i][j + 1]));
+              acc[i][j] = r.x; acc[i][j + 1] = r.y;
+            }
+          }
+      } else if (PACK == 2) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) {
+            const float2 b2 = make_float2(bf[h][j], bf[h][j]);
+#pragma unroll
+            for (int i = 0; i < TM; i += 2) {
+              const float2 r = __ffma2_rn(make_float2(af[h][i], af[h][i + 1]), b2, make_float2(acc[i][j], acc[i + 1][j]));
+              acc[i][j] = r.x; acc[i + 1][j] = r.y;
+            }
+          }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(af[h][i], bf[h][j], acc[i][j]);
+      }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");

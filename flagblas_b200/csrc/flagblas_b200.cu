@@ -408,9 +408,9 @@ static int run_scale(void* C, long long ldc, long long m, long long n, float bet
   return FB_OK;
 }
 
-template <int BM, int BN, bool AK, bool BKM>
+template <int BM, int BN, bool AK, bool BKM, int PACK>
 static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t stream) {
-  auto kern = sgemm_pipe_kernel<BM, BN, AK, BKM>;
+  auto kern = sgemm_pipe_kernel<BM, BN, AK, BKM, PACK>;
   constexpr int kBytes = kPipeStages * (PipeTile<BM, AK>::kFloats + PipeTile<BN, BKM>::kFloats) * 4;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -424,13 +424,22 @@ static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t 
   return FB_OK;
 }
 
+// Packed FMAs pair outputs along the dimension whose fragments arrive as float4 (an operand stored with M / N
+// contiguous); with both operands K-contiguous there is no such dimension and the FMAs stay scalar.
+// FLAGBLAS_B200_SGEMM_FFMA2 = 0 forces scalar FMAs everywhere (profiling comparison).
 template <int BM, int BN>
 static int dispatch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t stream) {
   const bool ak = !p.a_mn_contig, bk = !p.b_mn_contig;  // K-contiguous storage
-  if (ak) return bk ? launch_sgemm_pipe<BM, BN, true, true>(p, tiles, stream)
-                    : launch_sgemm_pipe<BM, BN, true, false>(p, tiles, stream);
-  return bk ? launch_sgemm_pipe<BM, BN, false, true>(p, tiles, stream)
-            : launch_sgemm_pipe<BM, BN, false, false>(p, tiles, stream);
+  const bool pack = env_int("FLAGBLAS_B200_SGEMM_FFMA2", 1) != 0;
+  if (ak) {
+    if (bk) return launch_sgemm_pipe<BM, BN, true, true, 0>(p, tiles, stream);
+    return pack ? launch_sgemm_pipe<BM, BN, true, false, 1>(p, tiles, stream)
+                : launch_sgemm_pipe<BM, BN, true, false, 0>(p, tiles, stream);
+  }
+  if (bk) return pack ? launch_sgemm_pipe<BM, BN, false, true, 2>(p, tiles, stream)
+                      : launch_sgemm_pipe<BM, BN, false, true, 0>(p, tiles, stream);
+  return pack ? launch_sgemm_pipe<BM, BN, false, false, 1>(p, tiles, stream)
+              : launch_sgemm_pipe<BM, BN, false, false, 0>(p, tiles, stream);
 }
 
 static int run_sgemm_simt(int transa, int transb, long long m, long long n, long long k, float alpha, const float* A,
