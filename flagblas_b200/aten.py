@@ -3,7 +3,7 @@
 Mirrors the registration scaffolding of the reference (``src/flag_blas/__init__.py:49-189``: ``enable``,
 ``only_enable``, ``use_blas``, ``all_registered_ops``, ``all_registered_keys``; ``runtime/register.py:21-145``:
 the ``Register`` class walking a ``(aten key, function[, condition])`` table).  In the reference the table
-(``_FULL_CONFIG``) is empty, so nothing is ever registered; here it lists the five operators below.
+(``_FULL_CONFIG``) is empty, so nothing is ever registered; here it lists the operators below.
 
 The functions take whatever strides ``torch`` hands them: a matrix that is row-major, or the transpose
 of a row-major matrix, is passed in place with ``trans = N / T`` and its pitch as the leading dimension;
@@ -79,13 +79,60 @@ def addmm(self, mat1, mat2, *, beta=1, alpha=1):
     return _mm_into(out, mat1, mat2, alpha, beta)
 
 
+_offs_cache = {}
+
+
+def _equal_offsets(device, batch, rows):
+    """int32 device tensor [rows, 2 * rows, ..., batch * rows] (cached: it only depends on the shape)."""
+    key = (device, batch, rows)
+    t = _offs_cache.get(key)
+    if t is None:
+        if len(_offs_cache) > 256:
+            _offs_cache.clear()
+        t = (torch.arange(1, batch + 1, device=device, dtype=torch.int64) * rows).to(torch.int32)
+        _offs_cache[key] = t
+    return t
+
+
 def bmm(self, mat2):
-    """aten::bmm(Tensor self, Tensor mat2) -> Tensor: one GEMM per batch entry on the current stream."""
+    """aten::bmm(Tensor self, Tensor mat2) -> Tensor.
+
+    Tensor-core types run as ONE grouped launch: the batch is a grouped matmul over equal row segments of
+    ``self`` viewed as ``[batch * m, k]`` (``group_mm``).  IEEE fp32, unaligned rows and tiny batches run
+    one GEMM per batch entry."""
     assert self.dim() == 3 and mat2.dim() == 3 and self.shape[0] == mat2.shape[0] and self.shape[2] == mat2.shape[1]
-    out = torch.empty((self.shape[0], self.shape[1], mat2.shape[2]), dtype=self.dtype, device=self.device)
-    for i in range(self.shape[0]):
+    assert self.dtype == mat2.dtype
+    batch, m, k = self.shape
+    n = mat2.shape[2]
+    code = _code(self.dtype)
+    esz = self.element_size()
+    if (batch >= 3 and code != _lib.FB_F32 and m > 0 and n > 0 and k > 0 and (k * esz) % 16 == 0 and (n * esz) % 16 == 0):
+        from .ops.level3.group_gemm import group_mm
+
+        a2 = self.reshape(batch * m, k)
+        b3 = mat2 if (mat2.stride(2) == 1 or mat2.stride(1) == 1) else mat2.contiguous()
+        ok = a2.data_ptr() % 16 == 0 and b3.data_ptr() % 16 == 0 and (b3.stride(0) * esz) % 16 == 0 and \
+            (max(b3.stride(1), b3.stride(2)) * esz) % 16 == 0
+        if ok:
+            return group_mm(a2.contiguous(), b3, _equal_offsets(self.device, batch, m)).view(batch, m, n)
+    out = torch.empty((batch, m, n), dtype=self.dtype, device=self.device)
+    for i in range(batch):
         _mm_into(out[i], self[i], mat2[i], 1.0, 0.0)
     return out
+
+
+def _grouped_mm(self, mat2, offs=None, bias=None, out_dtype=None):
+    """aten::_grouped_mm(Tensor self, Tensor mat2, Tensor? offs, Tensor? bias, ScalarType? out_dtype) -> Tensor:
+    the 2-D x 3-D form (row segments of ``self`` ending at ``offs`` times ``mat2[g]``) and the 3-D x 3-D form."""
+    if bias is not None or (out_dtype is not None and out_dtype != self.dtype):
+        raise NotImplementedError("flag_blas _grouped_mm: bias and out_dtype conversions are not provided")
+    if self.dim() == 3 and mat2.dim() == 3 and offs is None:
+        return bmm(self, mat2)
+    if self.dim() == 2 and mat2.dim() == 3 and offs is not None:
+        from .ops.level3.group_gemm import group_mm
+
+        return group_mm(self, mat2, offs)
+    raise NotImplementedError("flag_blas _grouped_mm: only [M, K] x [G, K, N] with row offsets and [B, M, K] x [B, K, N]")
 
 
 def _mv_into(out, a, x, alpha, beta):
@@ -129,6 +176,7 @@ _FULL_CONFIG = (
     ("bmm", bmm),
     ("mv", mv),
     ("addmv", addmv),
+    ("_grouped_mm", _grouped_mm, lambda: hasattr(torch.ops.aten, "_grouped_mm")),
 )
 FULL_CONFIG_BY_FUNC = {}
 for _item in _FULL_CONFIG:

@@ -69,7 +69,8 @@ def group_tf32gemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_s
                   d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
 
 
-_CODES = {torch.bfloat16: _lib.FB_BF16, torch.float16: _lib.FB_F16}
+# fp32 tensors run with TF32 tensor-core products (fp32 accumulate), like the reference's fp32 `tl.dot`
+_CODES = {torch.bfloat16: _lib.FB_BF16, torch.float16: _lib.FB_F16, torch.float32: _lib.FB_TF32}
 
 
 def group_mm(A: torch.Tensor, B: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
