@@ -258,3 +258,47 @@ def test_gemm_from_host_matches_the_operator(kind, ta, tb, beta):
         else:
             assert torch.equal(hC, Cd.cpu())
     assert fb.device_status() == 0
+
+
+def test_cuda_graph_capture_and_replay():
+    """A launch-bound sequence (small GEMM, matrix-vector product, grouped GEMM) captured once in a CUDA graph
+    and replayed on new input data gives what eager calls give."""
+    g = torch.Generator(device="cpu").manual_seed(77)
+    m, n, k = 256, 384, 320
+    A = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    B = torch.randn(k, n, generator=g).bfloat16().to(DEV)
+    C = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    x = torch.randn(n, generator=g).bfloat16().to(DEV)
+    y = torch.zeros(m, dtype=torch.bfloat16, device=DEV)
+    ms, K, N = [100, 0, 156], 320, 128
+    Bg = (torch.randn(3 * K, N, generator=g) / 16).bfloat16().to(DEV)
+    O = torch.zeros(sum(ms), N, dtype=torch.bfloat16, device=DEV)
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=DEV)  # noqa: E731
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+    starts = [0, 100, 100]
+    ga = (O, i64([A.data_ptr() + s * K * 2 for s in starts]), i64([Bg.data_ptr() + e * K * N * 2 for e in range(3)]),
+          i64([O.data_ptr() + s * N * 2 for s in starts]), i64([O.data_ptr() + s * N * 2 for s in starts]), i32(ms),
+          i32([N] * 3), i32([K] * 3), i32([K] * 3), i32([N] * 3), i32([N] * 3), 3, sum(ms), N, K, 1.0, 0.0)
+
+    def run():
+        fb.bfgemm(0, 0, m, n, k, 1.0, A, k, B, n, 0.0, C, n)
+        fb.bfgemv(0, m, n, 1.0, C, n, x, 1, 0.0, y, 1)         # consumes the GEMM's output
+        fb.group_bfgemm(*ga)
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        run()                                                   # first call on this stream: outside any capture
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        run()
+    A.copy_(torch.randn(m, k, generator=g).bfloat16())         # new data, same buffers
+    x.copy_(torch.randn(n, generator=g).bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    got = (C.clone(), y.clone(), O.clone())
+    run()
+    torch.cuda.synchronize()
+    assert torch.equal(got[0], C) and torch.equal(got[1], y) and torch.equal(got[2], O)
+    assert float(C.float().abs().max()) > 0 and float(O.float().abs().max()) > 0
+    assert fb.device_status() == 0
