@@ -74,7 +74,11 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-static int env_int(const char* name, int dflt);
+// Integer environment switch (profiling sweeps and opt-in variants), `dflt` when unset or empty.
+static int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
 
 // L2 sector promotion of the tensor maps; FLAGBLAS_B200_L2PROMO = 0 (none), 1 (64 B), 2 (128 B), 3 (256 B,
 // the default) for profiling sweeps.
@@ -238,10 +242,6 @@ static int choose_block_n(long long m, long long n, int tile_m, int workers, boo
   return best_bn;
 }
 
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : dflt;
-}
 
 constexpr size_t kStreamKFlagBytes = 1024;  // one int per worker (at most 148), padded
 
