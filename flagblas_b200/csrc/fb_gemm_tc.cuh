@@ -101,6 +101,12 @@ struct TcGemmParams {
   int sk_enabled, sk_dp, sk_rem;
   float* sk_partials;  // [workers][tile rows][BLOCK_N]
   int* sk_flags;       // [workers], zeroed before the launch
+  // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
+  // by different CTAs; each writes its raw fp32 sums to `splitk_out + part * m * n` (row pitch n) and a second
+  // kernel adds the parts in order and applies alpha, beta and the output cast.  For shapes with too few
+  // output tiles to occupy the GPU (a handful of tokens against a large weight matrix).
+  int splitk;
+  float* splitk_out;
   // Profiling switches (results are meaningless when set): bit 0 = issue no MMA, bit 1 = issue no TMA copy.
   int debug;
   int stages;  // pipeline stages actually used (<= the compiled maximum)
@@ -192,11 +198,12 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
 }
 
 // One unit of work of a persistent worker: stages [sb, se) of the k loop of one output tile.
-enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2 };
+enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3 };
 struct WorkItem {
   int tile;
   int sb, se;
   int kind;
+  int part;  // ITEM_SPLIT: which k part
 };
 
 // The idx-th work item of `worker` in dense mode (see the stream-K fields of TcGemmParams).
@@ -204,6 +211,18 @@ struct WorkItem {
 __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worker, int workers, int stages, int idx,
                                                 WorkItem& it) {
   const int tiles = p.tiles_m * p.tiles_n;
+  it.part = 0;
+  if (p.splitk > 1) {
+    const int w = worker + idx * workers;
+    if (w >= tiles * p.splitk) return false;
+    it.tile = w % tiles;
+    it.part = w / tiles;
+    const int base = stages / p.splitk, rem = stages % p.splitk;
+    it.sb = it.part * base + min(it.part, rem);
+    it.se = it.sb + base + (it.part < rem ? 1 : 0);
+    it.kind = ITEM_SPLIT;
+    return true;
+  }
   if (!p.sk_enabled) {
     it.tile = worker + idx * workers;
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
@@ -678,6 +697,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < 8; ++q)
             __stcg(dst + q, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
                                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
+        } else if (item.kind == ITEM_SPLIT) {
+          Problem part = pr;
+          part.out = p.splitk_out + static_cast<size_t>(item.part) * pr.m * pr.n;
+          part.ldo = pr.n; part.cin = nullptr; part.ldcin = 0;
+          part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
+          epilogue_chunk<float>(r, part, row, tn * BLOCK_N + c * 32, 1.f, 0.f);
         } else if (!(p.debug & 4) && ok) {
           epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
         }
@@ -711,6 +736,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
     else tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// Second kernel of a split-K call: out = alpha * (part 0 + part 1 + ...) + beta * C, parts added in index order.
+template <class OutT>
+__global__ void splitk_finish_kernel(const float* __restrict__ parts, int splitk, int m, int n, float alpha, float beta,
+                                     OutT* out, long long ldo) {
+  const long long total = static_cast<long long>(m) * n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splitk; ++s) acc += __ldcs(parts + static_cast<long long>(s) * total + i);
+    const long long r = i / n, c = i - r * n;
+    OutT* dst = out + r * ldo + c;
+    float v = alpha * acc;
+    if (beta != 0.f) v += beta * to_f32(*dst);
+    *dst = from_f32<OutT>(v);
   }
 }
 

@@ -472,6 +472,7 @@ struct DensePlan {
   int tile_m, block_n;
   long long tiles;
   bool want_streamk;  // the call can use stream-K scratch if the caller provides it
+  int splitk;         // > 1: cut every tile's k range into that many parts (needs fp32 scratch for the parts)
 };
 
 static DensePlan plan_dense(long long m, long long n, long long k, int esz, int sm_count) {
@@ -487,9 +488,33 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   pl.block_n = choose_block_n(m, n, pl.tile_m, workers, !pl.pair);
   const int force_bn = env_int("FLAGBLAS_B200_BLOCK_N", 0);
   if (force_bn == 256 || force_bn == 128 || (force_bn == 64 && !pl.pair)) pl.block_n = force_bn;
-  pl.tiles = ((m + pl.tile_m - 1) / pl.tile_m) * ((n + pl.block_n - 1) / pl.block_n);
   const long long span = kSwizzleBytes / esz;
   const long long stages = (k + 2 * span - 1) / (2 * span);  // with two k-slabs per stage
+  pl.splitk = 1;
+  // A few rows against a large matrix (m <= 128: one row block): the call is bound by streaming B from HBM,
+  // which wants every SM busy AND wide copies in flight; whole-k tiles give one or the other.  Tile width and
+  // k split are therefore picked together: cost = waves x (stages per CTA + fill) x width / efficiency, plus the
+  // second kernel that adds the parts (measured: 16 x 8192 x 8192 48 -> 34 us, 1 x 8192 x 8192 69 -> 34 us,
+  // config 5b 194 -> 191 us).  FLAGBLAS_B200_SPLITK = 0 disables, N forces N parts.
+  const int force_split = env_int("FLAGBLAS_B200_SPLITK", -1);
+  if (!pl.pair && force_bn == 0 && force_split != 0 && stages >= 8) {
+    const int cand[3] = {256, 128, 64};
+    const double eff[3] = {1.0, 0.6, 0.35};
+    double best = 1e300;
+    for (int i = 0; i < 3; ++i) {
+      const long long tl = (n + cand[i] - 1) / cand[i];
+      for (int sp = 1; sp <= 32; ++sp) {
+        if (sp > 1 && stages / sp < 4) break;  // keep at least four stages per part
+        const long long ctas = tl * sp;
+        const long long waves = (ctas + sm_count - 1) / sm_count;
+        const double per_cta = static_cast<double>((stages + sp - 1) / sp + 4);
+        const double cost = waves * per_cta * cand[i] / eff[i] + (sp > 1 ? 2300.0 : 0.0);
+        if (cost < best) { best = cost; pl.block_n = cand[i]; pl.splitk = sp; }
+      }
+    }
+  }
+  if (force_split > 1 && !pl.pair && stages >= 2LL * force_split) pl.splitk = force_split;
+  pl.tiles = ((m + pl.tile_m - 1) / pl.tile_m) * ((n + pl.block_n - 1) / pl.block_n);
   const long long dp = pl.tiles / workers, rem = pl.tiles - dp * workers;
   pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * workers &&
                     env_int("FLAGBLAS_B200_STREAMK", 0) != 0;
@@ -766,6 +791,7 @@ size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int
     if (di) {
       const DensePlan dp = plan_dense(m, n, k, elem_size(dtype), di->sm_count);
       if (dp.want_streamk) bytes += streamk_bytes(di->sm_count, dp.block_n);
+      if (dp.splitk > 1) bytes = round_up(bytes, 256) + static_cast<size_t>(dp.splitk) * m * n * sizeof(float);
     }
   }
   return bytes;
@@ -899,8 +925,38 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     p.sk_flags = reinterpret_cast<int*>(sk);
     p.sk_partials = reinterpret_cast<float*>(sk + kStreamKFlagBytes);
   }
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  return dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
+  long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  // Split-K for skinny calls: used only when the caller provided the scratch fb_gemm_workspace_bytes asked for.
+  int splitk = dplan.splitk;
+  const long long k_stages = (k + p.block_k - 1) / p.block_k;
+  while (splitk > 1 && k_stages / splitk < 2) --splitk;
+  const size_t split_off = round_up(ws_used, 256);
+  if (splitk > 1 && !p.sk_partials && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
+      workspace_bytes >= split_off + static_cast<size_t>(splitk) * m * n * sizeof(float)) {
+    p.splitk = splitk;
+    p.splitk_out = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + split_off);
+    tiles *= splitk;
+  }
+  rc = dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
+  if (rc || p.splitk <= 1) return rc;
+  long long blocks = (m * n + 255) / 256;
+  if (blocks > 4LL * di->sm_count) blocks = 4LL * di->sm_count;
+  switch (dtype) {
+    case FB_F16:
+      splitk_finish_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<__half*>(C), ldc);
+      break;
+    case FB_BF16:
+      splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<__nv_bfloat16*>(C), ldc);
+      break;
+    default:
+      splitk_finish_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<float*>(C), ldc);
+      break;
+  }
+  FB_CUDA_OK(cudaGetLastError());
+  return FB_OK;
 }
 
 // Workspace of one pass: records, the tile count, tensor maps.

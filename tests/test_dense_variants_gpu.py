@@ -64,3 +64,40 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
         assert_parity(outs[sk], ref, KINDS[kind][2], sc, "stream-k=%s %s %dx%dx%d" % (sk, kind, m, n, k))
     # different summation order: the two schedules may differ by a rounding step of the output type
     assert_parity(outs["1"], outs["0"], KINDS[kind][2], sc, "stream-k vs whole tiles")
+
+
+@pytest.mark.parametrize("kind,ta,tb,m,n,k,beta", [
+    ("bf16", 0, 1, 16, 4096, 4096, 0.0),     # a few tokens against a square weight matrix, stored [n, k]
+    ("bf16", 0, 0, 64, 2048, 8192, 0.5),     # stored [k, n], beta != 0
+    ("fp16", 0, 1, 1, 4104, 4096, 0.0),      # one row, ragged n
+    ("tf32", 1, 0, 33, 1000, 6144, 0.5),     # A transposed, n not a multiple of 4 (scalar stores of the parts)
+    ("bf16", 0, 1, 128, 512, 16384, 0.0),    # very long k, four tiles
+])
+def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
+    """Shapes with one row block and few column tiles are cut along k (parts in fp32 scratch, second kernel adds
+    them in order).  Same tolerance as every dense test; FLAGBLAS_B200_SPLITK=0 (whole-k tiles) and a forced
+    part count must agree with the automatic plan."""
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=41, scale=0.25)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    opA = (Ad.t() if ta else Ad).double()
+    opB = (Bd.t() if tb else Bd).double()
+    if kind == "tf32":
+        trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+        opA, opB = trunc(opA), trunc(opB)
+    ref = (1.5 * (opA @ opB) + beta * C.to(DEV).double()).float().cpu()
+    sc = result_scale(k, A, B, 1.5) + abs(beta)
+    outs = {}
+    for mode in ("auto", "0", "3"):
+        if mode == "auto":
+            monkeypatch.delenv("FLAGBLAS_B200_SPLITK", raising=False)
+        else:
+            monkeypatch.setenv("FLAGBLAS_B200_SPLITK", mode)
+        Cd = C.to(DEV) if beta != 0 else torch.full_like(C, float("nan")).to(DEV)
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, beta, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        outs[mode] = Cd.float().cpu()
+        assert_parity(outs[mode], ref, KINDS[kind][2], sc, "split-k=%s %s %dx%dx%d" % (mode, kind, m, n, k))
+    need = fb.c_operators.gemm_workspace_bytes(fb._lib.FB_BF16, 0, 1, 16, 4096, 4096, 256, 4096, 512, 4096)
+    assert need >= 2 * 16 * 4096 * 4          # the automatic plan of the first shape asks for scratch for >= 2 parts
