@@ -690,6 +690,37 @@ static int run_gemv_fp8_y(int y_dtype, long long m, long long n, float alpha, co
   }
 }
 
+// A GEMM with one output row or column is a matrix-vector product: it goes to the HBM-bound gemv kernels (fp32
+// accumulate and one rounding, like the tensor-core path) instead of a tile that is 127/128 padding.
+// FB_TF32 stays on the tensor cores (its contract is TF32 products).
+struct GemvView {
+  bool ok;
+  int trans;
+  long long m, n, lda, incx, incy;
+  const void* A;
+  const void* x;
+};
+
+static GemvView gemm_as_gemv(int dtype, int transa, int transb, long long m, long long n, long long k, const void* A,
+                             long long lda, const void* B, long long ldb, long long ldc) {
+  GemvView v{};
+  if (dtype == FB_TF32 || env_int("FLAGBLAS_B200_GEMM_AS_GEMV", 1) == 0) return v;
+  if (m == 1) {
+    // C[1, n] = a[k] * op(B): B stored [n, k] (transb = T) -> y = B a;  stored [k, n] -> y = B^T a
+    v.ok = true; v.A = B; v.lda = ldb; v.x = A;
+    v.incx = transa ? lda : 1;  // a is a row of A[1, k], or a column of A stored [k, 1]
+    v.incy = 1;
+    if (transb) { v.trans = FB_OP_N; v.m = n; v.n = k; } else { v.trans = FB_OP_T; v.m = k; v.n = n; }
+  } else if (n == 1) {
+    // C[m, 1] = op(A) * b[k]: A stored [m, k] -> y = A b;  stored [k, m] (transa = T) -> y = A^T b
+    v.ok = true; v.A = A; v.lda = lda; v.x = B;
+    v.incx = transb ? 1 : ldb;  // b is a column of B stored [k, 1] (stride ldb), or the row B[1, k]
+    v.incy = ldc;
+    if (transa) { v.trans = FB_OP_T; v.m = k; v.n = m; } else { v.trans = FB_OP_N; v.m = m; v.n = k; }
+  }
+  return v;
+}
+
 // --------------------------------------------------- double / complex GEMM on the CUDA cores
 template <bool AK, bool BKM>
 static int launch_dgemm_mma_t(XgemmParams p, cudaStream_t stream) {
@@ -784,6 +815,10 @@ extern "C" {
 size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
                                int64_t lda, const void* B, int64_t ldb) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
+  {
+    const GemvView gv = gemm_as_gemv(dtype, transa, transb, m, n, k, A, lda, B, ldb, n);
+    if (gv.ok) return fb_gemv_workspace_bytes(dtype, gv.trans, gv.m, gv.n);
+  }
   const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
   size_t bytes = pl.a_bytes + pl.b_bytes;
   if (dtype != FB_F32) {
@@ -822,6 +857,12 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   if (!A || !B) return FB_ERR_INVALID_ARG;
   if (lda < (transa ? m : k) || ldb < (transb ? k : n)) return FB_ERR_INVALID_ARG;
 
+  {
+    const GemvView gv = gemm_as_gemv(dtype, transa, transb, m, n, k, A, lda, B, ldb, ldc);
+    if (gv.ok)
+      return fb_gemv(dtype, gv.trans, gv.m, gv.n, alpha, gv.A, gv.lda, gv.x, gv.incx, beta, C, gv.incy, workspace,
+                     workspace_bytes, stream_);
+  }
   if (dtype == FB_F32)
     return run_sgemm_simt(transa, transb, m, n, k, alpha, static_cast<const float*>(A), lda,
                           static_cast<const float*>(B), ldb, beta, static_cast<float*>(C), ldc, di->sm_count, stream);

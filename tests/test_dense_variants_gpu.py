@@ -101,3 +101,24 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
         assert_parity(outs[mode], ref, KINDS[kind][2], sc, "split-k=%s %s %dx%dx%d" % (mode, kind, m, n, k))
     need = fb.c_operators.gemm_workspace_bytes(fb._lib.FB_BF16, 0, 1, 16, 4096, 4096, 256, 4096, 512, 4096)
     assert need >= 2 * 16 * 4096 * 4          # the automatic plan of the first shape asks for scratch for >= 2 parts
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp32"])
+def test_one_row_or_column_goes_through_gemv(kind, monkeypatch):
+    """m == 1 or n == 1: the call is a matrix-vector product and runs on the gemv kernels; same results (within the
+    dense tolerance) as the tile kernels (FLAGBLAS_B200_GEMM_AS_GEMV=0), for every transposition and padded pitches."""
+    op = getattr(fb, KINDS[kind][1])
+    for (m, n, k) in [(1, 1000, 520), (700, 1, 264), (1, 1, 40)]:
+        for ta in (0, 1):
+            for tb in (0, 1):
+                A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, pad=8, seed=51)
+                ref = oracle_dense(kind, ta, tb, m, n, k, 1.5, A, lda, B, ldb, 0.5, C, ldc)
+                for mode in ("1", "0"):
+                    monkeypatch.setenv("FLAGBLAS_B200_GEMM_AS_GEMV", mode)
+                    Cd = C.to(DEV)
+                    op(ta, tb, m, n, k, 1.5, A.to(DEV), lda, B.to(DEV), ldb, 0.5, Cd, ldc)
+                    torch.cuda.synchronize()
+                    assert fb.device_status() == 0
+                    assert torch.equal(Cd.cpu()[:, n:], C[:, n:])
+                    assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], result_scale(k, A, B, 1.5) + 0.5,
+                                  "%s gemv=%s %dx%dx%d ta=%d tb=%d" % (kind, mode, m, n, k, ta, tb))
