@@ -12,14 +12,9 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflagblas_b200.so")
 _SRC = os.path.join(_HERE, "csrc", "flagblas_b200.cu")
-_DEPS = [
-    _SRC,
-    os.path.join(_HERE, "csrc", "fb_ptx.cuh"),
-    os.path.join(_HERE, "csrc", "fb_gemm_tc.cuh"),
-    os.path.join(_HERE, "csrc", "fb_group_setup.cuh"),
-    os.path.join(_HERE, "csrc", "fb_sgemm_simt.cuh"),
-    os.path.join(os.path.dirname(_HERE), "include", "flagblas_b200.h"),
-]
+_DEPS = sorted(
+    os.path.join(_HERE, "csrc", f) for f in os.listdir(os.path.join(_HERE, "csrc")) if f.endswith((".cu", ".cuh"))
+) + [os.path.join(os.path.dirname(_HERE), "include", "flagblas_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

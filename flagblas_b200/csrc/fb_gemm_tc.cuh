@@ -197,6 +197,100 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   }
 }
 
+// Bytes of shared memory one epilogue warp stages its rows through: 32 rows x 128 bytes.
+constexpr int kEpiStageBytes = 32 * 128;
+
+// Epilogue of one warp's 32 rows x BLOCK_N columns of an accumulator whose TMEM address is `t_row`.
+// A thread owns a row of the accumulator, so direct stores would touch 32 rows with 16 bytes each per
+// instruction.  Instead the warp passes 128 bytes per row at a time through its private staging block
+// (16-byte units XOR-swizzled by the row, which keeps both directions free of bank conflicts) and
+// reads it back so that eight neighbouring lanes write one whole 128-byte row segment; the C operand
+// of a beta term comes in the same way.  Column spans that are ragged or unaligned fall back to the
+// per-thread path.  `hand_back` runs once, right after the last TMEM read.
+template <class T, int BLOCK_N, class HandBack>
+__device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* stage, const Problem& pr, int row0,
+                                                     int col_base, float alpha, float beta, int lane, bool zero_acc,
+                                                     HandBack hand_back) {
+  constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
+  constexpr int kLoads = kW / 32;
+  constexpr int kSteps = BLOCK_N / kW;
+  constexpr int kPerVec = 16 / static_cast<int>(sizeof(T));
+  const uint32_t stage_addr = smem_u32(stage);
+  const uint32_t own_row = stage_addr + static_cast<uint32_t>(lane) * 128u;
+  const int sub_row = lane >> 3, unit = lane & 7;  // read-out role: row within a group of four, 16-byte unit
+  const bool with_c = beta != 0.f;
+#pragma unroll 1
+  for (int s = 0; s < kSteps; ++s) {
+    const int col0 = col_base + s * kW;
+    const bool fast = pr.vec_ok && col0 + kW <= pr.n;
+    if (fast && with_c) {
+      // the C rows of this step, whole row segments per instruction, into the staging block
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int lr = j * 4 + sub_row;
+        if (row0 + lr < pr.m) {
+          const uint4 c = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(pr.cin) +
+                                                               static_cast<size_t>(row0 + lr) * pr.ldcin + col0) + unit);
+          st_shared_v4(stage_addr + static_cast<uint32_t>(lr * 128 + ((unit ^ (lr & 7)) << 4)), c);
+        }
+      }
+      __syncwarp();
+    }
+    uint32_t r[kLoads][32];
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) tmem_ld_32x32(t_row + static_cast<uint32_t>(s * kW + q * 32), r[q]);
+    tmem_ld_wait();
+    if (s == kSteps - 1) hand_back();
+    if (zero_acc) {
+#pragma unroll
+      for (int q = 0; q < kLoads; ++q)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[q][j] = 0u;
+    }
+    if (!fast) {
+#pragma unroll
+      for (int q = 0; q < kLoads; ++q) epilogue_chunk<T>(r[q], pr, row0 + lane, col0 + q * 32, alpha, beta);
+      continue;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float v[kPerVec];
+#pragma unroll
+      for (int j = 0; j < kPerVec; ++j) {
+        const int e = u * kPerVec + j;  // column of this step
+        v[j] = alpha * __uint_as_float(r[e >> 5][e & 31]);
+      }
+      const uint32_t slot = own_row + static_cast<uint32_t>((u ^ (lane & 7)) << 4);
+      if (with_c) {
+        const uint4 raw = ld_shared_v4(slot);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < kPerVec; ++j) v[j] += beta * to_f32(e[j]);
+      }
+      uint4 raw;
+      if constexpr (sizeof(T) == 4) {
+        raw.x = __float_as_uint(v[0]); raw.y = __float_as_uint(v[1]);
+        raw.z = __float_as_uint(v[2]); raw.w = __float_as_uint(v[3]);
+      } else {
+        raw.x = pack2(from_f32<T>(v[0]), from_f32<T>(v[1]));
+        raw.y = pack2(from_f32<T>(v[2]), from_f32<T>(v[3]));
+        raw.z = pack2(from_f32<T>(v[4]), from_f32<T>(v[5]));
+        raw.w = pack2(from_f32<T>(v[6]), from_f32<T>(v[7]));
+      }
+      st_shared_v4(slot, raw);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int lr = j * 4 + sub_row;
+      const uint4 raw = ld_shared_v4(stage_addr + static_cast<uint32_t>(lr * 128 + ((unit ^ (lr & 7)) << 4)));
+      if (row0 + lr < pr.m)
+        *(reinterpret_cast<uint4*>(reinterpret_cast<T*>(pr.out) + static_cast<size_t>(row0 + lr) * pr.ldo + col0) + unit) = raw;
+    }
+    __syncwarp();  // the block is rewritten by the next step
+  }
+}
+
 // One unit of work of a persistent worker: stages [sb, se) of the k loop of one output tile.
 enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3 };
 struct WorkItem {
@@ -265,10 +359,11 @@ struct TcCfg {
   static constexpr int kBBytes = kBRows * kSwizzleBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kCtlBytes = 1024;
-  static constexpr int kStages = (kSmemLimit - 1024 - kCtlBytes) / kStageBytes > 8
+  static constexpr int kEpiBytes = 4 * kEpiStageBytes;  // staging blocks of the four epilogue warps
+  static constexpr int kStages = (kSmemLimit - 1024 - kCtlBytes - kEpiBytes) / kStageBytes > 8
                                      ? 8
-                                     : (kSmemLimit - 1024 - kCtlBytes) / kStageBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kCtlBytes + 1024;
+                                     : (kSmemLimit - 1024 - kCtlBytes - kEpiBytes) / kStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kCtlBytes + kEpiBytes + 1024;
   // One MMA instruction covers at most 256 columns; a 512-wide tile is two halves side by side in
   // TMEM and fills all 512 columns, so its accumulator cannot be double buffered.
   static constexpr int kMmaN = BLOCK_N > 256 ? 256 : BLOCK_N;
@@ -313,6 +408,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[3] = clock64();  // timeline: entry
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -348,6 +444,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[4] = clock64();  // timeline: set-up done
 
   // Grouped calls are launched as programmatic dependents of the table builder: everything above ran
   // while it was still working; its table and tensor maps may be read only from here on.
@@ -453,8 +550,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       if (p.prof && blockIdx.x == 0) {
-        p.prof[load_a ? 0 : 9] = prof_wait;
-        p.prof[load_a ? 1 : 10] = prof_issue;
+        if (load_a) { p.prof[0] = prof_wait; p.prof[1] = prof_issue; }
+        else p.prof[10] = prof_wait + prof_issue;
       }
     }
     __syncwarp();
@@ -487,7 +584,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a), p.a.lbo, p.a.sbo, p.a.layout);
       const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b), p.b.lbo, p.b.sbo, p.b.layout);
       const uint32_t a_stage_units = (p.ks * Cfg::kABytes) >> 4, b_stage_units = (p.ks * Cfg::kBBytes) >> 4;
-      long long prof_wfull = 0, prof_wtmem = 0;
+      long long prof_wfull = 0, prof_wtmem = 0, prof_mma_issue = 0;
       const long long cstart = p.prof ? clock64() : 0;
       unsigned long long gstart = 0;
       if (p.prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gstart));
@@ -523,6 +620,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long c0 = p.prof ? clock64() : 0;
             if (!mbar_wait(&full_bar[stage], phase, wctl, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
             if (p.prof) prof_wfull += clock64() - c0;
+            if (p.prof && blockIdx.x == 0 && idx == 0 && kb == 0) p.prof[12] = clock64();  // timeline: first operands
             tc_fence_after();
             a_desc = a_desc0 + static_cast<uint32_t>(stage) * a_stage_units;
             b_desc = b_desc0 + static_cast<uint32_t>(stage) * b_stage_units;
@@ -531,6 +629,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint32_t next_phase = phase;
           if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1u; }
           uint64_t a_next = 0, b_next = 0;
+          const long long ci0 = p.prof ? clock64() : 0;
 #pragma unroll
           for (int j = 0; j < kMaxMma; ++j) {
             if (j < n_mma) {
@@ -557,6 +656,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             }
           }
+          if (p.prof) prof_mma_issue += clock64() - ci0;
           stage = next_stage;
           phase = next_phase;
           a_desc = a_next;
@@ -570,6 +670,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if (p.prof && blockIdx.x == 0) {
         p.prof[2] = prof_wfull; p.prof[5] = prof_wtmem;
+        p.prof[9] = prof_mma_issue;
         p.prof[6] = clock64() - cstart;
         unsigned long long gend;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gend));
@@ -624,6 +725,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const long long e1 = p.prof ? clock64() : 0;
       prof_ewait += e1 - e0;
+      if (p.prof && blockIdx.x == 0 && idx == 0 && threadIdx.x == kEpiWarp0 * 32) p.prof[13] = e1;  // timeline: first accumulator
       const int row = row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
@@ -658,6 +760,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) ok = false;  // still drain TMEM below so that the MMA issuer is not left waiting
+      }
+      if (item.kind == ITEM_FULL || item.kind == ITEM_SPLIT) {
+        // the usual case: this warp's 32 rows leave through its staging block as whole row segments
+        uint8_t* stage = ctl + Cfg::kCtlBytes + (warp - kEpiWarp0) * kEpiStageBytes;
+        const int row0 = row - lane;
+        auto hand_back = [&]() {
+          // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+            else mbar_arrive(&tmem_empty_bar[acc]);
+          }
+        };
+        if (item.kind == ITEM_SPLIT) {
+          Problem part = pr;
+          part.out = p.splitk_out + static_cast<size_t>(item.part) * pr.m * pr.n;
+          part.ldo = pr.n; part.cin = nullptr; part.ldcin = 0;
+          part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
+          epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back);
+        } else if (!(p.debug & 4) && ok) {
+          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back);
+        } else {
+          hand_back();
+        }
+        if (p.prof) prof_ebody += clock64() - e1;
+        if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
+        continue;
       }
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N / 32; ++c) {
@@ -697,12 +827,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < 8; ++q)
             __stcg(dst + q, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
                                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
-        } else if (item.kind == ITEM_SPLIT) {
-          Problem part = pr;
-          part.out = p.splitk_out + static_cast<size_t>(item.part) * pr.m * pr.n;
-          part.ldo = pr.n; part.cin = nullptr; part.ldcin = 0;
-          part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
-          epilogue_chunk<float>(r, part, row, tn * BLOCK_N + c * 32, 1.f, 0.f);
         } else if (!(p.debug & 4) && ok) {
           epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
         }
@@ -715,7 +839,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (p.prof) prof_ebody += clock64() - e1;
       if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) { p.prof[7] = prof_ewait; p.prof[8] = prof_ebody; }
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
+      p.prof[7] = prof_ewait; p.prof[8] = prof_ebody;
+      p.prof[14] = clock64();  // timeline: last store issued
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -737,6 +864,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
     else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[15] = clock64();  // timeline: exit
 }
 
 // Second kernel of a split-K call: out = alpha * (part 0 + part 1 + ...) + beta * C, parts added in index order.

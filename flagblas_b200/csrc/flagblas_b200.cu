@@ -513,8 +513,18 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
       }
     }
   }
-  if (force_split > 1 && !pl.pair && stages >= 2LL * force_split) pl.splitk = force_split;
   pl.tiles = ((m + pl.tile_m - 1) / pl.tile_m) * ((n + pl.block_n - 1) / pl.block_n);
+  // CTA-pair tiles with a deep k and few output tiles (200 x 200 x 20000: one tile; 129 x 4096 x 4096: 16): give the
+  // idle pairs a part of every tile's k range, as long as a part keeps four stages and the fp32 parts stay small.
+  // (Measured: below 32 stages the second kernel costs more than the shorter k loop saves.)
+  if (pl.pair && force_split != 0 && stages >= 32 && 2 * pl.tiles <= workers) {
+    long long sp = workers / pl.tiles;
+    if (sp > stages / 4) sp = stages / 4;
+    if (sp > 32) sp = 32;
+    while (sp > 1 && sp * m * n * 4 > (64LL << 20)) --sp;
+    if (sp >= 2) pl.splitk = static_cast<int>(sp);
+  }
+  if (force_split > 1 && stages >= 2LL * force_split) pl.splitk = force_split;
   const long long dp = pl.tiles / workers, rem = pl.tiles - dp * workers;
   pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * workers &&
                     env_int("FLAGBLAS_B200_STREAMK", 0) != 0;

@@ -72,6 +72,9 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
     ("fp16", 0, 1, 1, 4104, 4096, 0.0),      # one row, ragged n
     ("tf32", 1, 0, 33, 1000, 6144, 0.5),     # A transposed, n not a multiple of 4 (scalar stores of the parts)
     ("bf16", 0, 1, 128, 512, 16384, 0.0),    # very long k, four tiles
+    ("bf16", 0, 1, 200, 200, 20000, 0.5),    # CTA-pair tile, one output tile, deep k
+    ("fp16", 0, 0, 129, 2048, 4096, 0.0),    # CTA-pair tiles, eight output tiles
+    ("tf32", 1, 1, 300, 520, 8192, 0.5),     # CTA-pair tiles, ragged
 ])
 def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
     """Shapes with one row block and few column tiles are cut along k (parts in fp32 scratch, second kernel adds
