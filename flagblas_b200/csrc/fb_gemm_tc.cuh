@@ -107,6 +107,11 @@ struct TcGemmParams {
   // output tiles to occupy the GPU (a handful of tokens against a large weight matrix).
   int splitk;
   float* splitk_out;
+  // Cluster split-K (dense mode, 128-row tiles, `cluster_k` = 2, 4 or 8 = the launch's cluster size): the CTAs of a
+  // cluster share one output tile and take consecutive parts of its k range.  Each leaves its fp32 sums in its own
+  // shared memory; after a cluster barrier every CTA adds, over distributed shared memory and in rank order, the
+  // 128 / cluster_k rows it is responsible for and writes them out.  No scratch memory, no second kernel.
+  int cluster_k;
   // Profiling switches (results are meaningless when set): bit 0 = issue no MMA, bit 1 = issue no TMA copy.
   int debug;
   int stages;  // pipeline stages actually used (<= the compiled maximum)
@@ -291,8 +296,101 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
   }
 }
 
+// Cluster split-K, after the k loops.  The CTAs of a cluster hold fp32 sums of different k parts of one
+// 128 x BLOCK_N tile in TMEM.  CTA r of the cluster finishes columns [r * BLOCK_N / parts, +BLOCK_N / parts) of it:
+//   1. every CTA parks its sums in its own shared memory (the operand ring is idle by now), all eight warps
+//      taking part: warp w reads TMEM lanes 32 * (w % 4) .. +32 and the column half w / 4;
+//   2. cluster barrier;
+//   3. every CTA reads its columns of the valid rows from all CTAs of the cluster over distributed shared
+//      memory (the reads of all parts are issued before the first is used), adds them in rank order, applies
+//      alpha, beta and the cast, and stores them;
+//   4. cluster barrier: nobody leaves while a peer may still read its shared memory.
+// Layout of a parked tile: [128 rows][BLOCK_N] fp32, 16-byte units XOR-swizzled by the row.
+template <class OutT, int BLOCK_N>
+__device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint32_t parked, uint32_t tmem_base,
+                                                    int tile, bool store) {
+  constexpr int kUnits = BLOCK_N / 4;  // 16-byte units (four fp32 sums) per row
+  constexpr uint32_t kPitch = BLOCK_N * 4;
+  const int parts = p.cluster_k;
+  const uint32_t rank = cluster_ctarank();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  tc_fence_after();
+  {
+    const int quadrant = warp & 3, half = warp >> 2;
+    const int lrow = quadrant * 32 + lane;
+    const uint32_t row_addr = parked + static_cast<uint32_t>(lrow) * kPitch;
+    constexpr int kChunks = BLOCK_N / 64;  // 32-column chunks per column half
+#pragma unroll 1
+    for (int cc = 0; cc < kChunks; ++cc) {
+      const int c = half * kChunks + cc;
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(c * 32), r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        st_shared_v4(row_addr + static_cast<uint32_t>(((c * 8 + q) ^ (lrow & 7)) << 4),
+                     make_uint4(r[q * 4 + 0], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]));
+    }
+  }
+  tc_fence_before();
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[7] = clock64();  // timeline: parked
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[8] = clock64();  // timeline: cluster barrier passed
+
+  if (store) {
+    int tm, tn;
+    swizzled_tile(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+    const Problem& pr = p.prob;
+    // this CTA's share: BLOCK_N / parts columns of every valid row (a column slice spreads the work evenly
+    // over the cluster however few of the 128 rows exist)
+    const int slice_units = kUnits / parts;
+    const int rows_valid = min(kBlockM, pr.m - tm * kBlockM);
+    uint32_t peer[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) peer[q] = mapa_shared(parked, static_cast<uint32_t>(q < parts ? q : 0));
+#pragma unroll 2
+    for (int i = threadIdx.x; i < rows_valid * slice_units; i += kNumThreads) {
+      const int lrow = i / slice_units, u = static_cast<int>(rank) * slice_units + i % slice_units;
+      const int row = tm * kBlockM + lrow, col = tn * BLOCK_N + u * 4;
+      if (col >= pr.n) continue;
+      const uint32_t off = static_cast<uint32_t>(lrow) * kPitch + static_cast<uint32_t>((u ^ (lrow & 7)) << 4);
+      float4 x[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < parts) x[q] = ld_cluster_v4(peer[q] + off);
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < parts) { v[0] += x[q].x; v[1] += x[q].y; v[2] += x[q].z; v[3] += x[q].w; }
+      OutT* orow = reinterpret_cast<OutT*>(pr.out) + static_cast<size_t>(row) * pr.ldo + col;
+      const OutT* crow = reinterpret_cast<const OutT*>(pr.cin) + static_cast<size_t>(row) * pr.ldcin + col;
+      const int valid = min(4, pr.n - col);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[j] *= p.alpha;
+        if (p.beta != 0.f && j < valid) v[j] += p.beta * to_f32(crow[j]);
+      }
+      if (pr.vec_ok && valid == 4) {
+        if constexpr (sizeof(OutT) == 4) {
+          *reinterpret_cast<float4*>(orow) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+          *reinterpret_cast<uint2*>(orow) = make_uint2(pack2(from_f32<OutT>(v[0]), from_f32<OutT>(v[1])),
+                                                       pack2(from_f32<OutT>(v[2]), from_f32<OutT>(v[3])));
+        }
+      } else {
+        for (int j = 0; j < valid; ++j) orow[j] = from_f32<OutT>(v[j]);
+      }
+    }
+  }
+  if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64();  // timeline: rows stored
+  cluster_arrive_release();
+  cluster_wait_acquire();
+}
+
 // One unit of work of a persistent worker: stages [sb, se) of the k loop of one output tile.
-enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3 };
+enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3, ITEM_CLUSTER = 4 };
 struct WorkItem {
   int tile;
   int sb, se;
@@ -306,6 +404,17 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
                                                 WorkItem& it) {
   const int tiles = p.tiles_m * p.tiles_n;
   it.part = 0;
+  if (p.cluster_k > 1) {
+    // the grid is exactly tiles x cluster_k CTAs: one work item each, the cluster rank picks the k part
+    if (idx > 0) return false;
+    it.tile = worker / p.cluster_k;
+    it.part = worker % p.cluster_k;
+    const int base = stages / p.cluster_k, rem = stages % p.cluster_k;
+    it.sb = it.part * base + min(it.part, rem);
+    it.se = it.sb + base + (it.part < rem ? 1 : 0);
+    it.kind = ITEM_CLUSTER;
+    return true;
+  }
   if (p.splitk > 1) {
     const int w = worker + idx * workers;
     if (w >= tiles * p.splitk) return false;
@@ -761,6 +870,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) ok = false;  // still drain TMEM below so that the MMA issuer is not left waiting
       }
+      if (item.kind == ITEM_CLUSTER) break;  // the accumulator is complete; the whole CTA finishes the tile below
       if (item.kind == ITEM_FULL || item.kind == ITEM_SPLIT) {
         // the usual case: this warp's 32 rows leave through its staging block as whole row segments
         uint8_t* stage = ctl + Cfg::kCtlBytes + (warp - kEpiWarp0) * kEpiStageBytes;
@@ -858,6 +968,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // Neither CTA may retire while its partner can still signal its barriers or read its operands.
     cluster_arrive_release();
     cluster_wait_acquire();
+  } else {
+    if (p.cluster_k > 1)
+      cluster_finish_tile<OutT, BLOCK_N>(p, smem_u32(smem), tmem_base, static_cast<int>(blockIdx.x) / p.cluster_k,
+                                         !*abort_flag);
   }
   if (warp == 2) {
     tc_fence_after();

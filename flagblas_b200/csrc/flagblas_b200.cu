@@ -8,6 +8,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <cstdio>
 #include <type_traits>
 
 namespace fb {
@@ -295,6 +296,14 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   unsigned n_attrs = 0;
+  if (!PAIR && p.cluster_k > 1) {
+    // cluster split-K: `tiles` counts one CTA per (tile, k part); the CTAs of a tile form one cluster
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles));
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = static_cast<unsigned>(p.cluster_k);
+    attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
   if (PAIR) {
     attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
     attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
@@ -473,7 +482,38 @@ struct DensePlan {
   long long tiles;
   bool want_streamk;  // the call can use stream-K scratch if the caller provides it
   int splitk;         // > 1: cut every tile's k range into that many parts (needs fp32 scratch for the parts)
+  int cluster_k;      // > 1: the parts of a tile go to the CTAs of one cluster, which add them up in shared memory
 };
+
+// CTAs of 128-row tiles that can run at once when launched in clusters of `size` (a cluster needs `size` free SMs
+// in one GPC, so the larger the cluster the more SMs stay empty).
+static int cluster_capacity(int size, int sm_count) {
+  static int cached[64][9];
+  static std::mutex mu;
+  if (size < 2 || size > 8) return sm_count;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[dev][size] == 0) {
+    using Cfg = TcCfg<1, 256, false>;
+    auto kern = gemm_tc_kernel<1, 256, false>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) == cudaSuccess) {
+      cudaLaunchConfig_t q{};
+      q.gridDim = dim3(static_cast<unsigned>(sm_count / size * size));
+      q.blockDim = dim3(kNumThreads);
+      q.dynamicSmemBytes = Cfg::kSmemBytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = static_cast<unsigned>(size); qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) n = 0;
+    }
+    cudaGetLastError();
+    cached[dev][size] = n > 0 ? n * size : sm_count / size * size * 3 / 4;
+  }
+  return cached[dev][size];
+}
 
 static DensePlan plan_dense(long long m, long long n, long long k, int esz, int sm_count) {
   DensePlan pl{};
@@ -491,42 +531,88 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const long long span = kSwizzleBytes / esz;
   const long long stages = (k + 2 * span - 1) / (2 * span);  // with two k-slabs per stage
   pl.splitk = 1;
-  // A few rows against a large matrix (m <= 128: one row block): the call is bound by streaming B from HBM,
-  // which wants every SM busy AND wide copies in flight; whole-k tiles give one or the other.  Tile width and
-  // k split are therefore picked together: cost = waves x (stages per CTA + fill) x width / efficiency, plus the
-  // second kernel that adds the parts (measured: 16 x 8192 x 8192 48 -> 34 us, 1 x 8192 x 8192 69 -> 34 us,
-  // config 5b 194 -> 191 us).  FLAGBLAS_B200_SPLITK = 0 disables, N forces N parts.
+  pl.cluster_k = 1;
+  // Few output tiles and a long k (a handful of rows against a large matrix, or a small square problem): whole-k
+  // tiles leave most SMs idle, and a CTA needs the same ~0.3 us per 64-deep stage whatever its tile width.  So the
+  // tile width and a split of the k range are picked together over 128-row tiles:
+  //   cost = waves x (stages per CTA + fill) x width / efficiency + the cost of adding the parts,
+  // where the parts are added either by the CTAs of a cluster in shared memory (2, 4 or 8 parts, cheap) or by a
+  // second kernel from fp32 scratch (any count up to 32; pays off only for very long k).
+  // FLAGBLAS_B200_SPLITK = 0 / FLAGBLAS_B200_CLUSTER_K = 0 disable a method, N forces N parts.
   const int force_split = env_int("FLAGBLAS_B200_SPLITK", -1);
-  if (!pl.pair && force_bn == 0 && force_split != 0 && stages >= 8) {
+  const int force_cluster = env_int("FLAGBLAS_B200_CLUSTER_K", -1);
+  const long long row_blocks = (m + kBlockM - 1) / kBlockM;
+  const bool gpu_is_full = row_blocks * ((n + 255) / 256) >= 2LL * sm_count;  // whole-k tiles already fill it
+  if (force_bn == 0 && force_pair != 1 && stages >= 8 && !gpu_is_full && (force_split != 0 || force_cluster != 0)) {
     const int cand[3] = {256, 128, 64};
     const double eff[3] = {1.0, 0.6, 0.35};
     double best = 1e300;
+    int best_bn = 0, best_sp = 1, best_ck = 1;
     for (int i = 0; i < 3; ++i) {
-      const long long tl = (n + cand[i] - 1) / cand[i];
+      const long long tl = row_blocks * ((n + cand[i] - 1) / cand[i]);
       for (int sp = 1; sp <= 32; ++sp) {
-        if (sp > 1 && stages / sp < 4) break;  // keep at least four stages per part
-        const long long ctas = tl * sp;
-        const long long waves = (ctas + sm_count - 1) / sm_count;
-        const double per_cta = static_cast<double>((stages + sp - 1) / sp + 4);
-        const double cost = waves * per_cta * cand[i] / eff[i] + (sp > 1 ? 2300.0 : 0.0);
-        if (cost < best) { best = cost; pl.block_n = cand[i]; pl.splitk = sp; }
+        if (sp > 1 && stages / sp < 2) break;
+        for (int in_cluster = 0; in_cluster < 2; ++in_cluster) {
+          if (in_cluster && (force_cluster == 0 || (sp != 2 && sp != 4 && sp != 8))) continue;
+          if (!in_cluster && sp > 1 && (force_split == 0 || stages / sp < 4)) continue;
+          if (sp == 1 && in_cluster) continue;
+          const long long at_once = in_cluster ? cluster_capacity(sp, sm_count) : sm_count;
+          const long long ctas = tl * sp;
+          const long long waves = (ctas + at_once - 1) / at_once;
+          const double per_cta = static_cast<double>((stages + sp - 1) / sp + 4);
+          double cost = waves * per_cta * cand[i] / eff[i];
+          // measured: two cluster barriers and parking the sums ~0.8 us more than a plain epilogue, and the
+          // reads over distributed shared memory run at ~16 bytes per clock per SM
+          const double rows = static_cast<double>(m < kBlockM ? m : kBlockM);
+          if (sp > 1) cost += in_cluster ? 350.0 + 0.054 * rows * cand[i] : 2300.0 + 2.1e-4 * static_cast<double>(m) * n * sp * 4.0;
+          if (cost < best) { best = cost; best_bn = cand[i]; best_sp = in_cluster ? 1 : sp; best_ck = in_cluster ? sp : 1; }
+        }
       }
     }
+    bool take = !pl.pair;
+    if (pl.pair) {
+      // more than one row block: CTA-pair tiles are the default; 128-row tiles (narrower, or with a split k)
+      // take over when the model says they are clearly faster (1024^3: 16 pair tiles on 148 SMs against 128
+      // tiles of 128 x 64; 129 x 4096 x 4096: 16 pair tiles against 32 x 4 CTAs)
+      const long long pair_tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + pl.block_n - 1) / pl.block_n);
+      const long long pair_waves = (pair_tiles + workers - 1) / workers;
+      double pair_cost = static_cast<double>(pair_waves) * static_cast<double>(stages + 4) * 256.0;
+      if (force_split != 0 && stages >= 32 && 2 * pair_tiles <= workers) {
+        // the CTA-pair tiles would themselves be split through scratch (the rule further down)
+        long long sp = workers / pair_tiles;
+        if (sp > stages / 4) sp = stages / 4;
+        if (sp > 32) sp = 32;
+        const double split_cost = static_cast<double>((stages + sp - 1) / sp + 4) * 256.0 + 2300.0 +
+                                  2.1e-4 * static_cast<double>(m) * n * sp * 4.0;
+        if (sp >= 2 && split_cost < pair_cost) pair_cost = split_cost;
+      }
+      take = best_sp == 1 && best < 0.8 * pair_cost;
+    }
+    if (take) {
+      pl.pair = false;
+      pl.tile_m = kBlockM;
+      pl.block_n = best_bn; pl.splitk = best_sp; pl.cluster_k = best_ck;
+    }
   }
+  const int split_workers = pl.pair ? sm_count / 2 : sm_count;
   pl.tiles = ((m + pl.tile_m - 1) / pl.tile_m) * ((n + pl.block_n - 1) / pl.block_n);
   // CTA-pair tiles with a deep k and few output tiles (200 x 200 x 20000: one tile; 129 x 4096 x 4096: 16): give the
   // idle pairs a part of every tile's k range, as long as a part keeps four stages and the fp32 parts stay small.
   // (Measured: below 32 stages the second kernel costs more than the shorter k loop saves.)
-  if (pl.pair && force_split != 0 && stages >= 32 && 2 * pl.tiles <= workers) {
-    long long sp = workers / pl.tiles;
+  if (pl.pair && force_split != 0 && stages >= 32 && 2 * pl.tiles <= split_workers) {
+    long long sp = split_workers / pl.tiles;
     if (sp > stages / 4) sp = stages / 4;
     if (sp > 32) sp = 32;
     while (sp > 1 && sp * m * n * 4 > (64LL << 20)) --sp;
     if (sp >= 2) pl.splitk = static_cast<int>(sp);
   }
-  if (force_split > 1 && stages >= 2LL * force_split) pl.splitk = force_split;
-  const long long dp = pl.tiles / workers, rem = pl.tiles - dp * workers;
-  pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * workers &&
+  if (force_split > 1 && stages >= 2LL * force_split) { pl.splitk = force_split; pl.cluster_k = 1; }
+  if ((force_cluster == 2 || force_cluster == 4 || force_cluster == 8) && !pl.pair && stages >= force_cluster) {
+    pl.cluster_k = force_cluster;
+    pl.splitk = 1;
+  }
+  const long long dp = pl.tiles / split_workers, rem = pl.tiles - dp * split_workers;
+  pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * split_workers && pl.cluster_k == 1 &&
                     env_int("FLAGBLAS_B200_STREAMK", 0) != 0;
   return pl;
 }
@@ -988,6 +1074,19 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     p.splitk_out = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + split_off);
     tiles *= splitk;
   }
+  if (p.splitk <= 1 && !p.sk_partials && !pair && block_n <= 256) {
+    // Cluster split-K: needs no scratch.  Every part must own at least one stage.
+    int ck = dplan.cluster_k;
+    while (ck > 1 && k_stages < ck) ck /= 2;
+    if (ck > 1) {
+      p.cluster_k = ck;
+      tiles *= ck;
+    }
+  }
+  if (env_int("FLAGBLAS_B200_PLAN_DEBUG", 0) != 0)
+    fprintf(stderr, "fb_gemm plan: %lld x %lld x %lld pair=%d block_n=%d ks=%d stages=%lld split=%d cluster=%d ctas=%lld\n",
+            static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k), pair ? 1 : 0, block_n, ks,
+            k_stages, p.splitk, p.cluster_k, tiles);
   rc = dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
   if (rc || p.splitk <= 1) return rc;
   long long blocks = (m * n + 255) / 256;

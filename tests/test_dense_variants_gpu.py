@@ -75,11 +75,14 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
     ("bf16", 0, 1, 200, 200, 20000, 0.5),    # CTA-pair tile, one output tile, deep k
     ("fp16", 0, 0, 129, 2048, 4096, 0.0),    # CTA-pair tiles, eight output tiles
     ("tf32", 1, 1, 300, 520, 8192, 0.5),     # CTA-pair tiles, ragged
+    ("bf16", 0, 1, 1024, 1024, 1024, 0.5),   # small square problem: 128-row tiles in clusters instead of CTA pairs
+    ("bf16", 1, 0, 100, 264, 1024, 0.0),     # k barely long enough, ragged rows and columns
 ])
 def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
-    """Shapes with one row block and few column tiles are cut along k (parts in fp32 scratch, second kernel adds
-    them in order).  Same tolerance as every dense test; FLAGBLAS_B200_SPLITK=0 (whole-k tiles) and a forced
-    part count must agree with the automatic plan."""
+    """Shapes with few output tiles and a long k are cut along k.  The parts are added either by the CTAs of a
+    cluster over distributed shared memory (2, 4 or 8 parts) or by a second kernel from fp32 scratch.  Same
+    tolerance as every dense test; whole-k tiles, every forced cluster size and a forced part count of the
+    scratch method must agree with the automatic plan."""
     A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=41, scale=0.25)
     Ad, Bd = A.to(DEV), B.to(DEV)
     op = getattr(fb, KINDS[kind][1])
@@ -90,20 +93,26 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
         opA, opB = trunc(opA), trunc(opB)
     ref = (1.5 * (opA @ opB) + beta * C.to(DEV).double()).float().cpu()
     sc = result_scale(k, A, B, 1.5) + abs(beta)
-    outs = {}
-    for mode in ("auto", "0", "3"):
-        if mode == "auto":
-            monkeypatch.delenv("FLAGBLAS_B200_SPLITK", raising=False)
-        else:
-            monkeypatch.setenv("FLAGBLAS_B200_SPLITK", mode)
+    # (FLAGBLAS_B200_SPLITK, FLAGBLAS_B200_CLUSTER_K, FLAGBLAS_B200_PAIR); None = unset
+    modes = {"auto": (None, None, None), "whole-k": ("0", "0", None), "scratch-3": ("3", "0", None),
+             "scratch-auto": (None, "0", None), "cluster-2": ("0", "2", "0"), "cluster-4": ("0", "4", "0"),
+             "cluster-8": ("0", "8", "0")}
+    for mode, envs in modes.items():
+        for name, val in zip(("FLAGBLAS_B200_SPLITK", "FLAGBLAS_B200_CLUSTER_K", "FLAGBLAS_B200_PAIR"), envs):
+            if val is None:
+                monkeypatch.delenv(name, raising=False)
+            else:
+                monkeypatch.setenv(name, val)
         Cd = C.to(DEV) if beta != 0 else torch.full_like(C, float("nan")).to(DEV)
         op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, beta, Cd, ldc)
         torch.cuda.synchronize()
         assert fb.device_status() == 0
-        outs[mode] = Cd.float().cpu()
-        assert_parity(outs[mode], ref, KINDS[kind][2], sc, "split-k=%s %s %dx%dx%d" % (mode, kind, m, n, k))
+        assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], sc, "split-k %s %s %dx%dx%d" % (mode, kind, m, n, k))
+    monkeypatch.setenv("FLAGBLAS_B200_CLUSTER_K", "0")
+    monkeypatch.delenv("FLAGBLAS_B200_SPLITK", raising=False)
+    monkeypatch.delenv("FLAGBLAS_B200_PAIR", raising=False)
     need = fb.c_operators.gemm_workspace_bytes(fb._lib.FB_BF16, 0, 1, 16, 4096, 4096, 256, 4096, 512, 4096)
-    assert need >= 2 * 16 * 4096 * 4          # the automatic plan of the first shape asks for scratch for >= 2 parts
+    assert need >= 2 * 16 * 4096 * 4          # without clusters the first shape's plan asks for scratch for >= 2 parts
 
 
 @pytest.mark.parametrize("kind", ["bf16", "fp16", "fp32"])
