@@ -1006,7 +1006,21 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   // 256 x 512 pair tiles (FLAGBLAS_B200_BLOCK_N=512): a quarter less operand traffic per FLOP than
   // 256 x 256, paid for with a single-buffered accumulator (all 512 TMEM columns hold one tile).
   // They need the one-copy-per-stage 3-D views of both operands.
-  if (pair && a3d && b3d && env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512) block_n = 512;
+  // Chosen by itself for large beta = 0 calls: with random data the GPU is power-limited, the smaller operand stream
+  // leaves more of the budget to the tensor pipe (8192^3, 300 launches back to back: 0.955 -> 0.884 ms, SM clock
+  // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower).  It needs at least four
+  // waves of tiles, and a wave count that wastes no more than the 256-wide tiling does.
+  bool wide = false;
+  if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && k >= 2048 &&
+      env_int("FLAGBLAS_B200_BLOCK_N", 0) == 0 && env_int("FLAGBLAS_B200_WIDE_TILES", 1) != 0) {
+    const long long pairs = di->sm_count / 2;
+    const long long rows = (m + 2 * kBlockM - 1) / (2 * kBlockM);
+    const long long t256 = rows * ((n + 255) / 256), t512 = rows * ((n + 511) / 512);
+    const double e256 = static_cast<double>(t256) / static_cast<double>((t256 + pairs - 1) / pairs * pairs);
+    const double e512 = static_cast<double>(t512) / static_cast<double>((t512 + pairs - 1) / pairs * pairs);
+    wide = t512 >= 4 * pairs && e512 >= e256 - 0.02 && n % 512 == 0;
+  }
+  if (pair && a3d && b3d && (wide || env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512)) block_n = 512;
   const int halves = block_n > 256 ? 2 : 1;
   const int b_rows = (pair ? block_n / 2 : block_n) / halves;  // rows of B per copy (per column half of the tile)
 
