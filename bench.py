@@ -34,6 +34,8 @@ WORKLOADS = {
     "tf32gemm_skinny_tn": ("tf32gemm", "tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
     "tf32gemm_8192_tn": ("tf32gemm", "tf32", 1, 0, 8192, 8192, 8192, 1.5, 0.5, 0.577, 0.577, 4),
     "tf32gemm_16384_tn": ("tf32gemm", "tf32", 1, 0, 16384, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4),
+    # a decode step's shape: 64 tokens against a square weight matrix stored [n, k] (latency and HBM bound)
+    "bfgemm_decode64_nt": ("bfgemm", "bf16", 0, 1, 64, 4096, 4096, 1.0, 0.0, 1.0, 0.02, 6),
     "sgemm_512_nn": ("sgemm", "fp32", 0, 0, 512, 512, 512, 1.0, 0.0, 0.577, 0.577, 0),
     "sgemm_4096_nn": ("sgemm", "fp32", 0, 0, 4096, 4096, 4096, 1.0, 0.0, 0.577, 0.577, 0),
 }
@@ -141,6 +143,10 @@ class ClockSampler:
 
 
 def _time(fn, torch, steps=10, warmup=3):
+    # a short idle first: the previous workload may have left the GPU at its power limit, and a kernel that is
+    # timed right behind it would be measured at the reduced clock of its predecessor
+    torch.cuda.synchronize()
+    time.sleep(0.5)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -175,7 +181,7 @@ def other_configs(fb, torch, dev):
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         nbytes = A.element_size() * (m * k + k * n + m * n * (2 if beta != 0 else 1))
         rec = {"tflops": tf, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9}
-        if name == "tf32gemm_skinny_tn":
+        if name in ("tf32gemm_skinny_tn", "bfgemm_decode64_nt"):
             rec.update(bound="hbm", frac=rec["gbs"] / hbm, peak=hbm)
         elif kind == "tf32":
             rec.update(bound="tensor", frac=tf / (peak / 2), peak=peak / 2)   # TF32 runs at half the 16-bit rate

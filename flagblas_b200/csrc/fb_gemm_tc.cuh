@@ -99,7 +99,7 @@ struct TcGemmParams {
   // that holds its first stages ("owner"); the others park their fp32 partial accumulators in
   // `sk_partials` (one slot per worker) and raise `sk_flags[worker]`.
   int sk_enabled, sk_dp, sk_rem;
-  float* sk_partials;  // [workers][tile rows][BLOCK_N]
+  float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
   // by different CTAs; each writes its raw fp32 sums to `splitk_out + part * m * n` (row pitch n) and a second
@@ -840,7 +840,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                              static_cast<uint32_t>(acc * BLOCK_N);
       // Stream-K: this thread's row inside a worker's partial slot, and for an owner the workers
       // (worker + 1 .. sk_last) that hold the rest of the tile's k range.
-      const size_t sk_row_off = static_cast<size_t>(static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane) * BLOCK_N;
+      // Layout of a slot: [16-byte unit of the row][row of the tile], so that the 32 rows of a warp sit side by
+      // side and every access of a warp covers 512 consecutive bytes.
+      const size_t sk_row = static_cast<size_t>(static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane);
       constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
       int sk_last = worker;
       if (item.kind == ITEM_OWNER) {
@@ -910,10 +912,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (item.kind == ITEM_OWNER && ok) {
           for (int v = worker + 1; v <= sk_last; ++v) {
-            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot + sk_row_off + c * 32);
+            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const float4 x = __ldcg(src + q);
+              const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
               r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
               r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
               r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
@@ -932,10 +934,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (item.kind == ITEM_PARTIAL) {
           // park the raw fp32 partial sums in this worker's slot
-          float4* dst = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot + sk_row_off + c * 32);
+          float4* dst = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot) + sk_row;
 #pragma unroll
           for (int q = 0; q < 8; ++q)
-            __stcg(dst + q, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
+            __stcg(dst + static_cast<size_t>(c * 8 + q) * Cfg::kTileM, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
                                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
         } else if (!(p.debug & 4) && ok) {
           epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
