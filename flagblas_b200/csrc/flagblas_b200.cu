@@ -1064,6 +1064,8 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   if (p.group_m < 1) p.group_m = 1;
   p.alpha = alpha; p.beta = beta;
   p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n > 256 ? 256 : block_n);
+  if (!pair && env_int("FLAGBLAS_B200_DEBUG_M64", 0) != 0)  // EXPERIMENT (timing only, results are wrong)
+    p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, 64, block_n);
   p.block_k = span * ks;
   p.ks = ks;
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
