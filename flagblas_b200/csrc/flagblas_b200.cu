@@ -1008,10 +1008,11 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   // They need the one-copy-per-stage 3-D views of both operands.
   // Chosen by itself for large beta = 0 calls: with random data the GPU is power-limited, the smaller operand stream
   // leaves more of the budget to the tensor pipe (8192^3, 300 launches back to back: 0.955 -> 0.884 ms, SM clock
-  // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower).  It needs at least four
+  // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower; k = 4096 is break-even, k = 2048
+  loses 3 %).  It needs at least four
   // waves of tiles, and a wave count that wastes no more than the 256-wide tiling does.
   bool wide = false;
-  if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && k >= 4096 &&
+  if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && k > 4096 &&
       env_int("FLAGBLAS_B200_BLOCK_N", 0) == 0 && env_int("FLAGBLAS_B200_WIDE_TILES", 1) != 0) {
     const long long pairs = di->sm_count / 2;
     const long long rows = (m + 2 * kBlockM - 1) / (2 * kBlockM);
@@ -1064,8 +1065,6 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   if (p.group_m < 1) p.group_m = 1;
   p.alpha = alpha; p.beta = beta;
   p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n > 256 ? 256 : block_n);
-  if (!pair && env_int("FLAGBLAS_B200_DEBUG_M64", 0) != 0)  // EXPERIMENT (timing only, results are wrong)
-    p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, 64, block_n);
   p.block_k = span * ks;
   p.ks = ks;
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
