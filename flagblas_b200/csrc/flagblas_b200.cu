@@ -1009,7 +1009,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   // Chosen by itself for large beta = 0 calls: with random data the GPU is power-limited, the smaller operand stream
   // leaves more of the budget to the tensor pipe (8192^3, 300 launches back to back: 0.955 -> 0.884 ms, SM clock
   // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower; k = 4096 is break-even, k = 2048
-  loses 3 %).  It needs at least four
+  // loses 3 %).  It needs at least four
   // waves of tiles, and a wave count that wastes no more than the 256-wide tiling does.
   bool wide = false;
   if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && k > 4096 &&
