@@ -486,7 +486,7 @@ struct DensePlan {
 };
 
 // CTAs of 128-row tiles that can run at once when launched in clusters of `size` (a cluster needs `size` free SMs
-// in one GPC, so the larger the cluster the more SMs stay empty).
+// in one GPC, so the larger the cluster the more SMs stay empty).  0: clusters of that size cannot run here.
 static int cluster_capacity(int size, int sm_count) {
   static int cached[64][9];
   static std::mutex mu;
@@ -510,9 +510,9 @@ static int cluster_capacity(int size, int sm_count) {
       if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) n = 0;
     }
     cudaGetLastError();
-    cached[dev][size] = n > 0 ? n * size : sm_count / size * size * 3 / 4;
+    cached[dev][size] = n > 0 ? n * size : -1;  // -1: this cluster size cannot be launched here
   }
-  return cached[dev][size];
+  return cached[dev][size] > 0 ? cached[dev][size] : 0;
 }
 
 static DensePlan plan_dense(long long m, long long n, long long k, int esz, int sm_count) {
@@ -557,6 +557,7 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
           if (!in_cluster && sp > 1 && (force_split == 0 || stages / sp < 4)) continue;
           if (sp == 1 && in_cluster) continue;
           const long long at_once = in_cluster ? cluster_capacity(sp, sm_count) : sm_count;
+          if (at_once <= 0) continue;
           const long long ctas = tl * sp;
           const long long waves = (ctas + at_once - 1) / at_once;
           const double per_cta = static_cast<double>((stages + sp - 1) / sp + 4);
@@ -607,7 +608,8 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
     if (sp >= 2) pl.splitk = static_cast<int>(sp);
   }
   if (force_split > 1 && stages >= 2LL * force_split) { pl.splitk = force_split; pl.cluster_k = 1; }
-  if ((force_cluster == 2 || force_cluster == 4 || force_cluster == 8) && !pl.pair && stages >= force_cluster) {
+  if ((force_cluster == 2 || force_cluster == 4 || force_cluster == 8) && !pl.pair && stages >= force_cluster &&
+      cluster_capacity(force_cluster, sm_count) > 0) {
     pl.cluster_k = force_cluster;
     pl.splitk = 1;
   }

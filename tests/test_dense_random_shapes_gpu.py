@@ -1,0 +1,57 @@
+"""Randomised shapes for the dense operators: the plan of a call (CTA-pair or 128-row tiles, tile width, cluster
+split-K, split through scratch, wide tiles, packed copies of unaligned operands) depends on m, n, k, the leading
+dimensions and beta, so a seeded draw over those checks the planner's whole decision space against an fp64 product
+of the same (for TF32: truncated) operands.  Padding columns of C must come back untouched."""
+import random
+
+import pytest
+import torch
+
+import flagblas_b200 as fb
+from tests.helpers import KINDS, assert_parity
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+M_CHOICES = [1, 7, 16, 33, 64, 100, 128, 129, 200, 256, 300, 511, 1024, 1500]
+N_CHOICES = [8, 64, 120, 256, 264, 512, 1000, 1536, 2048, 4096, 5000]
+K_CHOICES = [64, 128, 192, 520, 1024, 2048, 4096, 6144, 8200, 16384]
+
+
+@pytest.mark.parametrize("chunk", range(6))
+def test_random_shapes_match_fp64_product(chunk):
+    rnd = random.Random(1000 + chunk)
+    for case in range(25):
+        kind = rnd.choice(["bf16", "fp16", "tf32"])
+        dt, opname, rtol = KINDS[kind][0], KINDS[kind][1], KINDS[kind][2]
+        ta, tb = rnd.randint(0, 1), rnd.randint(0, 1)
+        m, n, k = rnd.choice(M_CHOICES), rnd.choice(N_CHOICES), rnd.choice(K_CHOICES)
+        if kind == "tf32":
+            k = max(32, k // 2)
+        per16 = 16 // (4 if kind == "tf32" else 2)
+        pad = rnd.choice([0, 0, per16, 3])                      # 3: pitch not 16-byte aligned -> packed copy
+        cols_a, cols_b = (m if ta else k), (k if tb else n)
+        lda, ldb, ldc = cols_a + pad, cols_b + pad, n + rnd.choice([0, 0, per16, 1])
+        g = torch.Generator(device="cpu").manual_seed(chunk * 100 + case)
+        A = (torch.randn((k if ta else m), lda, generator=g) * 0.25).to(dt).to(DEV)
+        B = (torch.randn((n if tb else k), ldb, generator=g) * 0.25).to(dt).to(DEV)
+        C0 = (torch.randn(m, ldc, generator=g) * 0.5).to(dt).to(DEV)
+        alpha, beta = rnd.choice([1.0, 1.5, -0.5]), rnd.choice([0.0, 0.0, 1.0, 0.5])
+        C = C0.clone()
+        if beta == 0:
+            C[:, :n] = float("nan")                              # beta == 0 must not read C
+        getattr(fb, opname)(ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
+        torch.cuda.synchronize()
+        what = "%s ta=%d tb=%d %dx%dx%d ld=%d/%d/%d alpha=%g beta=%g" % (kind, ta, tb, m, n, k, lda, ldb, ldc, alpha, beta)
+        assert fb.device_status() == 0, what
+        op_a = (A[:, :cols_a].t() if ta else A[:, :cols_a]).double()
+        op_b = (B[:, :cols_b].t() if tb else B[:, :cols_b]).double()
+        if kind == "tf32":
+            trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+            op_a, op_b = trunc(op_a), trunc(op_b)
+        ref = alpha * (op_a @ op_b)
+        if beta != 0:
+            ref = ref + beta * C0[:, :n].double()
+        scale = abs(alpha) * (k ** 0.5) * 0.25 * 0.25 + abs(beta) * 0.5
+        assert_parity(C[:, :n].float().cpu(), ref.float().cpu(), rtol, scale, what)
+        assert torch.equal(C[:, n:], C0[:, n:]), what + ": padding columns of C were written"
