@@ -523,6 +523,10 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const int force_pair = env_int("FLAGBLAS_B200_PAIR", -1);
   if (force_pair == 0) pl.pair = false;
   if (force_pair == 1) pl.pair = true;
+  // Very short k (at most 512 bytes per row: 256 16-bit elements): a tile's epilogue is longer than its k loop, and
+  // the two CTAs of a pair share their TPC's path to L2 when both store (8192 x 8192 x 256: 493 -> 535 TFLOP/s with
+  // 128-row tiles; from k = 512 on the pair tiles are level or ahead).
+  if (pl.pair && force_pair != 1 && k * esz <= 512) pl.pair = false;
   pl.tile_m = pl.pair ? 2 * kBlockM : kBlockM;
   const int workers = pl.pair ? sm_count / 2 : sm_count;
   pl.block_n = choose_block_n(m, n, pl.tile_m, workers, !pl.pair);
@@ -543,7 +547,9 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const int force_cluster = env_int("FLAGBLAS_B200_CLUSTER_K", -1);
   const long long row_blocks = (m + kBlockM - 1) / kBlockM;
   const bool gpu_is_full = row_blocks * ((n + 255) / 256) >= 2LL * sm_count;  // whole-k tiles already fill it
-  if (force_bn == 0 && force_pair != 1 && stages >= 8 && !gpu_is_full && (force_split != 0 || force_cluster != 0)) {
+  // (FLAGBLAS_B200_PLAN_MIN_STAGES: shortest k, in two-slab stages, for which the search runs; profiling sweeps)
+  const int min_stages = env_int("FLAGBLAS_B200_PLAN_MIN_STAGES", 1);
+  if (force_bn == 0 && force_pair != 1 && stages >= min_stages && !gpu_is_full && (force_split != 0 || force_cluster != 0)) {
     const int cand[3] = {256, 128, 64};
     const double eff[3] = {1.0, 0.6, 0.35};
     double best = 1e300;
