@@ -107,6 +107,9 @@ struct TcGemmParams {
   // output tiles to occupy the GPU (a handful of tokens against a large weight matrix).
   int splitk;
   float* splitk_out;
+  // Dense call whose operands were packed by a kernel queued just before this one: this kernel is launched as its
+  // programmatic dependent and must wait for it before the first copy.
+  int wait_prior;
   // Cluster split-K (dense mode, 128-row tiles, `cluster_k` = 2, 4 or 8 = the launch's cluster size): the CTAs of a
   // cluster share one output tile and take consecutive parts of its k range.  Each leaves its fp32 sums in its own
   // shared memory; after a cluster barrier every CTA adds, over distributed shared memory and in rank order, the
@@ -557,7 +560,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // Grouped calls are launched as programmatic dependents of the table builder: everything above ran
   // while it was still working; its table and tensor maps may be read only from here on.
-  if (grouped) grid_dependency_wait();
+  if (grouped || p.wait_prior) grid_dependency_wait();
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
   const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
 

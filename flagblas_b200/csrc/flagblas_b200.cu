@@ -189,15 +189,27 @@ __global__ void scale_kernel(T* c, long long ldc, int m, int n, float beta) {
   }
 }
 
-// Copy a [rows, cols] view with row pitch ld_src into a dense-pitched buffer (ld_dst).
+// Both operands of a dense call in one launch: blocks [0, blocks_a) copy A, the rest copy B (either may be empty).
+// The GEMM that follows is launched as a programmatic dependent: it may start its prologue right away and waits
+// for this grid before its first copy.
+struct PackJob {
+  const void* src;
+  void* dst;
+  long long ld_src, ld_dst, rows, cols;
+};
 template <class T>
-__global__ void pack_kernel(const T* __restrict__ src, long long ld_src, T* __restrict__ dst, long long ld_dst,
-                            long long rows, long long cols) {
-  const long long total = rows * cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols, c = i - r * cols;
-    dst[r * ld_dst + c] = src[r * ld_src + c];
+__global__ void pack2_kernel(PackJob a, PackJob b, int blocks_a) {
+  grid_launch_dependents();
+  const bool is_a = static_cast<int>(blockIdx.x) < blocks_a;
+  const PackJob& j = is_a ? a : b;
+  const long long first = is_a ? blockIdx.x : blockIdx.x - blocks_a;
+  const long long nblocks = is_a ? blocks_a : gridDim.x - blocks_a;
+  const T* src = static_cast<const T*>(j.src);
+  T* dst = static_cast<T*>(j.dst);
+  const long long total = j.rows * j.cols;
+  for (long long i = first * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
+    const long long r = i / j.cols, c = i - r * j.cols;
+    dst[r * j.ld_dst + c] = src[r * j.ld_src + c];
   }
 }
 
@@ -309,7 +321,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
     ++n_attrs;
   }
-  if (p.num_groups > 0 && env_int("FLAGBLAS_B200_PDL", 1) != 0) {
+  if ((p.num_groups > 0 || p.wait_prior) && env_int("FLAGBLAS_B200_PDL", 1) != 0) {
     // grouped: overlap this kernel's launch and prologue with the table builder queued just before it
     attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
@@ -389,20 +401,6 @@ static PackPlan plan_pack(int dtype, int transa, int transb, long long m, long l
   pl.a_bytes = pl.pack_a ? round_up(static_cast<size_t>(pl.a_rows) * pl.a_ld * esz, 256) : 0;
   pl.b_bytes = pl.pack_b ? round_up(static_cast<size_t>(pl.b_rows) * pl.b_ld * esz, 256) : 0;
   return pl;
-}
-
-template <class T>
-static int run_pack(const void* src, long long ld_src, void* dst, long long ld_dst, long long rows, long long cols,
-                    cudaStream_t stream) {
-  const long long total = rows * cols;
-  if (total == 0) return FB_OK;
-  const int threads = 256;
-  long long blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  pack_kernel<T><<<static_cast<int>(blocks), threads, 0, stream>>>(static_cast<const T*>(src), ld_src,
-                                                                   static_cast<T*>(dst), ld_dst, rows, cols);
-  FB_CUDA_OK(cudaGetLastError());
-  return FB_OK;
 }
 
 template <class T>
@@ -973,6 +971,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
 
   const int esz = elem_size(dtype);
   size_t ws_used = 0;  // bytes of the workspace taken by packed operands
+  bool packed = false; // a packing kernel was queued just before the GEMM
   // Operands that TMA cannot address in place are packed to a 16-byte pitched copy first.
   const PackPlan pl = plan_pack(dtype, transa, transb, m, n, k, A, lda, B, ldb);
   if (pl.pack_a || pl.pack_b) {
@@ -980,17 +979,27 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
       return FB_ERR_WORKSPACE;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     ws_used = pl.a_bytes + pl.b_bytes;
+    PackJob ja{}, jb{};
+    int blocks_a = 0, blocks_b = 0;
+    auto blocks_for = [](long long total) {
+      long long b = (total + 255) / 256;
+      return static_cast<int>(b > 148 * 8 ? 148 * 8 : b);
+    };
     if (pl.pack_a) {
-      int rc = esz == 2 ? run_pack<uint16_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream)
-                        : run_pack<uint32_t>(A, lda, ws, pl.a_ld, pl.a_rows, pl.a_cols, stream);
-      if (rc) return rc;
+      ja = PackJob{A, ws, lda, pl.a_ld, pl.a_rows, pl.a_cols};
+      blocks_a = blocks_for(pl.a_rows * pl.a_cols);
       A = ws; lda = pl.a_ld; ws += pl.a_bytes;
     }
     if (pl.pack_b) {
-      int rc = esz == 2 ? run_pack<uint16_t>(B, ldb, ws, pl.b_ld, pl.b_rows, pl.b_cols, stream)
-                        : run_pack<uint32_t>(B, ldb, ws, pl.b_ld, pl.b_rows, pl.b_cols, stream);
-      if (rc) return rc;
+      jb = PackJob{B, ws, ldb, pl.b_ld, pl.b_rows, pl.b_cols};
+      blocks_b = blocks_for(pl.b_rows * pl.b_cols);
       B = ws; ldb = pl.b_ld;
+    }
+    if (blocks_a + blocks_b > 0) {
+      if (esz == 2) pack2_kernel<uint16_t><<<blocks_a + blocks_b, 256, 0, stream>>>(ja, jb, blocks_a);
+      else pack2_kernel<uint32_t><<<blocks_a + blocks_b, 256, 0, stream>>>(ja, jb, blocks_a);
+      FB_CUDA_OK(cudaGetLastError());
+      packed = true;
     }
   }
 
@@ -1080,6 +1089,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
+  p.wait_prior = packed ? 1 : 0;
   // Optional stream-K scratch behind the packed operands: used only when the caller provided it.
   if (dplan.want_streamk && block_n <= 256 && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
       workspace_bytes >= ws_used + streamk_bytes(di->sm_count, block_n)) {
