@@ -521,6 +521,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[3] = clock64();  // timeline: entry
+  if (p.splitk > 1) grid_launch_dependents();  // the kernel that adds the parts may start its prologue now
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -990,6 +991,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 template <class OutT>
 __global__ void splitk_finish_kernel(const float* __restrict__ parts, int splitk, int m, int n, float alpha, float beta,
                                      OutT* out, long long ldo) {
+  grid_dependency_wait();  // launched as a programmatic dependent of the kernel that writes the parts
   const long long total = static_cast<long long>(m) * n;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {

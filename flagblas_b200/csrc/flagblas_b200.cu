@@ -1126,18 +1126,30 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   if (rc || p.splitk <= 1) return rc;
   long long blocks = (m * n + 255) / 256;
   if (blocks > 4LL * di->sm_count) blocks = 4LL * di->sm_count;
+  cudaLaunchConfig_t fcfg{};
+  fcfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  fcfg.blockDim = dim3(256);
+  fcfg.stream = stream;
+  cudaLaunchAttribute fattr[1];
+  fattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  fattr[0].val.programmaticStreamSerializationAllowed = 1;
+  fcfg.attrs = fattr;
+  fcfg.numAttrs = 1;
+  const float* parts = p.splitk_out;
+  const int im = static_cast<int>(m), in = static_cast<int>(n);
+  const long long ldo = ldc;
   switch (dtype) {
     case FB_F16:
-      splitk_finish_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<__half*>(C), ldc);
+      FB_CUDA_OK(cudaLaunchKernelEx(&fcfg, splitk_finish_kernel<__half>, parts, p.splitk, im, in, alpha, beta,
+                                    static_cast<__half*>(C), ldo));
       break;
     case FB_BF16:
-      splitk_finish_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<__nv_bfloat16*>(C), ldc);
+      FB_CUDA_OK(cudaLaunchKernelEx(&fcfg, splitk_finish_kernel<__nv_bfloat16>, parts, p.splitk, im, in, alpha, beta,
+                                    static_cast<__nv_bfloat16*>(C), ldo));
       break;
     default:
-      splitk_finish_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-          p.splitk_out, p.splitk, static_cast<int>(m), static_cast<int>(n), alpha, beta, static_cast<float*>(C), ldc);
+      FB_CUDA_OK(cudaLaunchKernelEx(&fcfg, splitk_finish_kernel<float>, parts, p.splitk, im, in, alpha, beta,
+                                    static_cast<float*>(C), ldo));
       break;
   }
   FB_CUDA_OK(cudaGetLastError());
