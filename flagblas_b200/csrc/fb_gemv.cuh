@@ -130,6 +130,7 @@ constexpr int kGemvRows = 4;
 
 template <class T, int UNR, int MINB>
 __global__ void __launch_bounds__(256, MINB) gemv_n_kernel(const GemvParams p) {
+  if (p.partial) grid_launch_dependents();  // the kernel that adds the partial sums may start its prologue
   constexpr int E = 16 / sizeof(T);
   constexpr int R = kGemvRows;
   __shared__ float red[8][R];
@@ -237,6 +238,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_n_kernel(const GemvParams p) {
 // are combined through shared memory by a fixed-shape tree.
 template <class T, int U, int MINB, class TX = T, class TY = T>
 __global__ void __launch_bounds__(256, MINB) gemv_t_kernel(const GemvParams p) {
+  if (p.partial) grid_launch_dependents();  // the kernel that adds the partial sums may start its prologue
   constexpr int E = 16 / sizeof(T);
   __shared__ float red[256 * E];
   const int tx = threadIdx.x & (p.tx - 1);
@@ -319,6 +321,7 @@ template <class T>
 __global__ void __launch_bounds__(256) gemv_finish_kernel(const float* __restrict__ partial, int splits, long long len,
                                                           T* y, long long incy, float alpha, float beta) {
   __shared__ float red[kFinishSlices][33];
+  grid_dependency_wait();  // launched as a programmatic dependent of the kernel that writes the partial sums
   const int o = threadIdx.x & 31, sl = threadIdx.x >> 5;
   const long long i = static_cast<long long>(blockIdx.x) * 32 + o;
   float acc = 0.f;

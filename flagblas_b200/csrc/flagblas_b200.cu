@@ -623,6 +623,22 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   return pl;
 }
 
+// Launch `kern` as a programmatic dependent of the kernel queued before it on `stream`: it may become resident
+// while that kernel still runs and must call griddepcontrol.wait before touching its results.
+template <class... KArgs, class... Args>
+static cudaError_t launch_dependent(void (*kern)(KArgs...), unsigned grid, unsigned block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------- gemv
 // How a matrix-vector call is spread over the GPU (shared by fb_gemv and fb_gemv_workspace_bytes).
 struct GemvPlan {
@@ -739,9 +755,8 @@ static int run_gemv(int trans, long long m, long long n, float alpha, const void
   }
   FB_CUDA_OK(cudaGetLastError());
   if (pl.splits > 1) {
-    gemv_finish_kernel<T><<<static_cast<unsigned>((len_y + 31) / 32), 256, 0, stream>>>(
-        p.partial, pl.splits, len_y, static_cast<T*>(y), incy, alpha, beta);
-    FB_CUDA_OK(cudaGetLastError());
+    FB_CUDA_OK(launch_dependent(gemv_finish_kernel<T>, static_cast<unsigned>((len_y + 31) / 32), 256, stream, p.partial,
+                                pl.splits, len_y, static_cast<T*>(y), incy, alpha, beta));
   }
   return FB_OK;
 }
@@ -774,9 +789,8 @@ static int run_gemv_fp8(long long m, long long n, float alpha, const void* A, lo
   gemv_t_kernel<TA, 8, 4, TX, TY><<<grid, pl.threads, 0, stream>>>(p);
   FB_CUDA_OK(cudaGetLastError());
   if (pl.splits > 1) {
-    gemv_finish_kernel<TY><<<static_cast<unsigned>((n + 31) / 32), 256, 0, stream>>>(
-        p.partial, pl.splits, n, static_cast<TY*>(y), incy, alpha, beta);
-    FB_CUDA_OK(cudaGetLastError());
+    FB_CUDA_OK(launch_dependent(gemv_finish_kernel<TY>, static_cast<unsigned>((n + 31) / 32), 256, stream, p.partial,
+                                pl.splits, n, static_cast<TY*>(y), incy, alpha, beta));
   }
   return FB_OK;
 }
