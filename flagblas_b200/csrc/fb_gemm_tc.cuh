@@ -93,12 +93,12 @@ struct TcGemmParams {
   const int* total_tiles;        // device scalar written by the table builder
   const CUtensorMap* group_maps;  // [2 * num_groups]: A_g, B_g
   // Stream-K tail (dense mode only).  When `sk_enabled`, every worker first takes `sk_dp` whole tiles
-  // (tile = worker + i * workers); the `sk_rem` tiles left over (fewer than there are workers) are
-  // cut into k-stage units and dealt out evenly, so that the last partial wave costs its share of a
-  // tile time instead of a whole one.  A tile split over several workers is finished by the worker
-  // that holds its first stages ("owner"); the others park their fp32 partial accumulators in
-  // `sk_partials` (one slot per worker) and raise `sk_flags[worker]`.
-  int sk_enabled, sk_dp, sk_rem;
+  // (tile = worker + i * workers); each of the `sk_rem` tiles left over (at most half as many as there are
+  // workers) goes to `sk_group` neighbouring workers: the first ("owner") takes the head of the k range and
+  // finishes the tile, each of the others takes `sk_share` stages, parks its fp32 partial accumulators in
+  // `sk_partials` (one slot per worker) and raises `sk_flags[worker]`.  The owner's part is the longer one, by
+  // about the time a contributor needs to park its sums, so that it does not have to wait for them.
+  int sk_enabled, sk_dp, sk_rem, sk_group, sk_share;
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
@@ -439,22 +439,17 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
     return true;
   }
-  const long long units = static_cast<long long>(p.sk_rem) * stages;
-  long long u = worker * units / workers;
-  const long long u1 = (worker + 1) * units / workers;
-  for (int q = 0; u < u1; ++q) {
-    const int tl = static_cast<int>(u / stages);
-    const int sb = static_cast<int>(u - static_cast<long long>(tl) * stages);
-    const long long len = min(static_cast<long long>(stages - sb), u1 - u);
-    if (q == idx - p.sk_dp) {
-      it.tile = p.sk_dp * workers + tl;
-      it.sb = sb; it.se = sb + static_cast<int>(len);
-      it.kind = sb > 0 ? ITEM_PARTIAL : (it.se < stages ? ITEM_OWNER : ITEM_FULL);
-      return true;
-    }
-    u += len;
+  if (idx > p.sk_dp) return false;
+  const int tl = worker / p.sk_group, j = worker % p.sk_group;
+  if (tl >= p.sk_rem) return false;  // more workers than tail parts: this one is done
+  const int owner_len = stages - (p.sk_group - 1) * p.sk_share;
+  it.tile = p.sk_dp * workers + tl;
+  if (j == 0) {
+    it.sb = 0; it.se = owner_len; it.kind = ITEM_OWNER;
+  } else {
+    it.sb = owner_len + (j - 1) * p.sk_share; it.se = it.sb + p.sk_share; it.kind = ITEM_PARTIAL;
   }
-  return false;
+  return true;
 }
 
 // PAIR = true: two CTAs of a cluster work on one 256 x BLOCK_N tile with
@@ -850,9 +845,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
       int sk_last = worker;
       if (item.kind == ITEM_OWNER) {
-        const long long units = static_cast<long long>(p.sk_rem) * dense_stages;
-        const long long tile_end = static_cast<long long>(t - p.sk_dp * num_workers + 1) * dense_stages;
-        while (sk_last + 1 < num_workers && (sk_last + 1) * units / num_workers < tile_end) ++sk_last;
+        sk_last = worker + p.sk_group - 1;
         // wait (bounded) until every contributor has parked its partial sums
         uint32_t good = 1;
         if (lane == 0) {

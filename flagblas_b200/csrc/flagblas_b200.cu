@@ -330,16 +330,21 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
   if (n_attrs) { cfg.attrs = attrs; cfg.numAttrs = n_attrs; }
   TcGemmParams pp = p;
   pp.sk_enabled = 0;
-  if (p.num_groups == 0 && p.sk_partials && env_int("FLAGBLAS_B200_STREAMK", 0) != 0) {
-    // Stream-K tail (opt-in, FLAGBLAS_B200_STREAMK=1): for a partial last wave with few waves.  Measured
-    // slower than whole tiles on every shape tried so far (the owner's reduction of the parked partial
-    // sums is a chain of L2 round trips at the very end of the kernel), hence off by default.
+  if (p.num_groups == 0 && p.sk_partials && env_int("FLAGBLAS_B200_STREAMK", 1) != 0) {
+    // Stream-K tail (FLAGBLAS_B200_STREAMK=0 switches it off): for a last wave that is at most half full.
     const long long stages = (p.k + static_cast<long long>(p.block_k) - 1) / p.block_k;
     const long long dp = tiles / workers, rem = tiles - dp * workers;
-    if (rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4 * workers) {
+    long long group = rem > 0 ? workers / rem : 0;  // workers per tail tile
+    if (group > 4) group = 4;
+    // head start of the owner: about 12 k cycles (parking a 128 x 256 fp32 tile per CTA and reading it back), in stages
+    const long long head = (20 + p.ks - 1) / p.ks;
+    const long long share = group >= 2 ? (stages - head) / group : 0;
+    if (group >= 2 && share >= 2 && dp < 9) {
       pp.sk_enabled = 1;
       pp.sk_dp = static_cast<int>(dp);
       pp.sk_rem = static_cast<int>(rem);
+      pp.sk_group = static_cast<int>(group);
+      pp.sk_share = static_cast<int>(share);
       FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     }
   }
@@ -618,8 +623,8 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
     pl.splitk = 1;
   }
   const long long dp = pl.tiles / split_workers, rem = pl.tiles - dp * split_workers;
-  pl.want_streamk = rem > 0 && dp < 9 && stages >= 2 && rem * stages >= 4LL * split_workers && pl.cluster_k == 1 &&
-                    env_int("FLAGBLAS_B200_STREAMK", 0) != 0;
+  pl.want_streamk = rem > 0 && dp < 9 && 2 * rem <= split_workers && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
+                    stages >= 32 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
   return pl;
 }
 

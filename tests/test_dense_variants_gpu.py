@@ -36,11 +36,15 @@ def test_dense_plan_variants(env, kind, monkeypatch):
     ("tf32", 1, 0, 64, 8192, 8192),      # skinny: 64 single-CTA tiles spread over all SMs
     ("tf32", 0, 1, 1000, 1536, 2000),    # edge tiles inside a split tile
     ("bf16", 0, 0, 130, 4100, 6144),     # single-CTA tiles (m <= 128 ... two row blocks), ragged n
+    ("bf16", 0, 1, 4096, 4096, 4096),    # 3 whole waves + 34 tail tiles, two workers per tail tile
+    ("fp16", 0, 0, 2560, 4096, 4096),    # 2 whole waves + 12 tail tiles, four workers per tail tile
+    ("tf32", 1, 0, 4096, 4096, 2048),    # the same tail in TF32
+    ("bf16", 1, 1, 4000, 4000, 4160),    # ragged edge tiles, last k stage half full
 ])
 def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
-    """The opt-in stream-K schedule (FLAGBLAS_B200_STREAMK=1): shapes whose last wave is partial are
-    finished with k-split tiles (partial sums parked in the workspace, reduced by the tile's owner).
-    Same tolerance as every other dense test, and close agreement with the default whole-tile schedule."""
+    """The stream-K tail (FLAGBLAS_B200_STREAMK=0 switches it off): when the last wave of tiles is at most half
+    full and k is long, each tail tile is shared by 2-4 workers (partial sums parked in the workspace, added by
+    the tile's owner).  Same tolerance as every other dense test, and close agreement with whole tiles."""
     A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=31, scale=0.25)
     Ad, Bd = A.to(DEV), B.to(DEV)
     op = getattr(fb, KINDS[kind][1])
