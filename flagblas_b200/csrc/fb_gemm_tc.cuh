@@ -99,6 +99,9 @@ struct TcGemmParams {
   // `sk_partials` (one slot per worker) and raises `sk_flags[worker]`.  The owner's part is the longer one, by
   // about the time a contributor needs to park its sums, so that it does not have to wait for them.
   int sk_enabled, sk_dp, sk_rem, sk_group, sk_share;
+  // Grouped mode takes the same tail (`sk_grouped`): the tile count is only known on the device, so the workers
+  // derive the split themselves; `sk_head` = the owner's head start in stages.
+  int sk_grouped, sk_head;
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
@@ -452,6 +455,48 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
   return true;
 }
 
+// Grouped mode: the idx-th tile of `worker`, and in the stream-K tail its role (0 = owner, > 0 = contributor,
+// -1 = a whole tile) and the number of workers that share the tile.  False when the worker has no idx-th tile.
+__device__ __forceinline__ bool grouped_tile(const TcGemmParams& p, int worker, int workers, int num_tiles, int idx,
+                                             int& t, int& role, int& sharers) {
+  role = -1;
+  sharers = 1;
+  if (p.sk_grouped) {
+    const int dp = num_tiles / workers, rem = num_tiles - dp * workers;
+    int grp = rem > 0 ? workers / rem : 1;
+    if (grp > 4) grp = 4;
+    if (grp >= 2 && idx >= dp) {
+      if (idx > dp) return false;
+      const int tl = worker / grp;
+      if (tl >= rem) return false;
+      t = dp * workers + tl;
+      role = worker % grp;
+      sharers = grp;
+      return true;
+    }
+  }
+  t = worker + idx * workers;
+  return t < num_tiles;
+}
+
+// Stage range and kind of a grouped work item whose tile has `stages` k-stages.  A tail tile too short to be worth
+// splitting is done whole by its owner; false tells a contributor that it has nothing to do.
+__device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it) {
+  it.part = 0;
+  const int share = sharers > 1 ? (stages - p.sk_head) / sharers : 0;
+  if (role < 0 || share < 2) {
+    it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
+    return role <= 0;
+  }
+  const int owner_len = stages - (sharers - 1) * share;
+  if (role == 0) {
+    it.sb = 0; it.se = owner_len; it.kind = ITEM_OWNER;
+  } else {
+    it.sb = owner_len + (role - 1) * share; it.se = it.sb + share; it.kind = ITEM_PARTIAL;
+  }
+  return true;
+}
+
 // PAIR = true: two CTAs of a cluster work on one 256 x BLOCK_N tile with
 // tcgen05 cta_group::2.  Each CTA fetches its own 128 rows of A and its own half
 // of the B tile into its own shared memory, the leader CTA (cluster rank 0)
@@ -574,10 +619,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       long long prof_wait = 0, prof_issue = 0;
       for (int idx = 0; ok; ++idx) {
         WorkItem item;
-        int t;
+        int t, role = -1, sharers = 1;
         if (grouped) {
-          t = worker + idx * num_workers;
-          if (t >= num_tiles) break;
+          if (!grouped_tile(p, worker, num_workers, num_tiles, idx, t, role, sharers)) break;
         } else {
           if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
           t = item.tile;
@@ -605,7 +649,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * (Cfg::kBRows / Cfg::kHalves);
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        const int kb_begin = grouped ? 0 : item.sb, kb_end = grouped ? k_blocks : item.se;
+        if (grouped && !grouped_range(p, k_blocks, role, sharers, item)) break;
+        const int kb_begin = item.sb, kb_end = item.se;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
@@ -700,21 +745,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint64_t a_desc = 0, b_desc = 0;  // descriptors of the current stage
       for (int idx = 0; ok; ++idx) {
         WorkItem item;
-        int t;
+        int t, role = -1, sharers = 1;
         if (grouped) {
-          t = worker + idx * num_workers;
-          if (t >= num_tiles) break;
+          if (!grouped_tile(p, worker, num_workers, num_tiles, idx, t, role, sharers)) break;
         } else {
           if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
           t = item.tile;
         }
-        int kk_total = p.k;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
-          kk_total = p.groups[g].k;
+          const int stages_g = (p.groups[g].k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+          if (!grouped_range(p, stages_g, role, sharers, item)) break;
         }
-        const int k_blocks = grouped ? (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k)
-                                     : item.se - item.sb;  // stages of this work item
+        const int k_blocks = item.se - item.sb;  // stages of this work item
         // PAIR: the peer's epilogue warps arrive remotely -> cluster-scope acquire
         if (!mbar_test_wait(&tmem_empty_bar[acc], acc_phase ^ 1u) || PAIR) {
           const long long ct0 = p.prof ? clock64() : 0;
@@ -798,10 +841,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int idx = 0; ok; ++idx) {
       WorkItem item;
       item.kind = ITEM_FULL;
-      int t;
+      int t, role = -1, sharers = p.sk_group;
       if (grouped) {
-        t = worker + idx * num_workers;
-        if (t >= num_tiles) break;
+        if (!grouped_tile(p, worker, num_workers, num_tiles, idx, t, role, sharers)) break;
       } else {
         if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
         t = item.tile;
@@ -820,6 +862,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pr.vec_ok = gr.vec_ok;
         k_is_zero = gr.k == 0;
         row_base = gr.row_base;
+        const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+        if (!grouped_range(p, stages_g, role, sharers, item)) break;
       } else {
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         pr = p.prob;
@@ -845,7 +889,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
       int sk_last = worker;
       if (item.kind == ITEM_OWNER) {
-        sk_last = worker + p.sk_group - 1;
+        sk_last = worker + sharers - 1;
         // wait (bounded) until every contributor has parked its partial sums
         uint32_t good = 1;
         if (lane == 0) {

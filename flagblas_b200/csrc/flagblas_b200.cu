@@ -1181,9 +1181,16 @@ static constexpr size_t group_pass_bytes(size_t groups) {
 }
 static constexpr size_t group_ws_bytes(size_t groups) { return 2 * group_pass_bytes(groups); }
 
+// Behind the two passes' tables: flags and partial-sum slots of the stream-K tail (optional: a caller that passes
+// only the tables' bytes gets whole tiles).
+static size_t group_tail_offset(size_t groups) { return round_up(group_ws_bytes(groups), 256); }
+
 size_t fb_group_workspace_bytes(int group_count) {
   if (group_count <= 0) return 0;
-  return group_ws_bytes(static_cast<size_t>(group_count));
+  const size_t base = group_ws_bytes(static_cast<size_t>(group_count));
+  const DeviceInfo* di = device_info();
+  if (!di || env_int("FLAGBLAS_B200_GROUP_STREAMK", 1) == 0) return base;
+  return group_tail_offset(static_cast<size_t>(group_count)) + streamk_bytes(di->sm_count, 256);
 }
 
 static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long n_hint,
@@ -1192,7 +1199,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   if (!di) return FB_ERR_LAUNCH;
   if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
   const int G = ga.num_groups;
-  if (!workspace || workspace_bytes < fb_group_workspace_bytes(G) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+  if (!workspace || workspace_bytes < group_ws_bytes(static_cast<size_t>(G)) || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return FB_ERR_WORKSPACE;
   const int esz = elem_size(dtype);
   const uint32_t span = kSwizzleBytes / esz;
@@ -1261,6 +1268,16 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     }
   }
 
+  // Stream-K tail of the (single) pass: when the last wave of tiles is at most half full, each of its tiles is
+  // shared by 2-4 neighbouring workers (the split is derived on the device, where the tile count is known).  Needs
+  // the scratch behind the tables; FLAGBLAS_B200_GROUP_STREAMK=0 switches it off.
+  uint8_t* tail = nullptr;
+  if (!split && env_int("FLAGBLAS_B200_GROUP_STREAMK", 1) != 0 &&
+      workspace_bytes >= group_tail_offset(static_cast<size_t>(G)) + streamk_bytes(di->sm_count, block_n)) {
+    tail = ws + group_tail_offset(static_cast<size_t>(G));
+    FB_CUDA_OK(cudaMemsetAsync(tail, 0, kStreamKFlagBytes, stream));  // before the table builder: the GEMM stays its dependent
+  }
+
   group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
   FB_CUDA_OK(cudaGetLastError());
 
@@ -1280,6 +1297,12 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.groups = ps.recs;
     p.total_tiles = ps.total_tiles;
     p.group_maps = ps.maps;
+    if (tail) {
+      p.sk_grouped = 1;
+      p.sk_head = (20 + ks - 1) / ks;
+      p.sk_flags = reinterpret_cast<int*>(tail);
+      p.sk_partials = reinterpret_cast<float*>(tail + kStreamKFlagBytes);
+    }
     const int rc = dispatch_tc(dtype, block_n, pass_pair[i], ps.tmpl_a, ps.tmpl_b, p, /*tiles=*/-1, di->sm_count, stream);
     if (rc) return rc;
   }

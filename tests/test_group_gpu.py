@@ -107,6 +107,18 @@ def test_grouped_tile_plan_variants(env, monkeypatch):
     _run_group("tf32", [40, 200, 64, 513], 200, 136, 1.5, 0.5, seed=12, var_nk=True)
 
 
+@pytest.mark.parametrize("kind", ["bf16", "tf32"])
+def test_grouped_stream_k_tail(kind, monkeypatch):
+    """A grouped call whose last wave of tiles is at most half full shares each tail tile between 2-4 workers (the
+    split is derived on the device).  Long k so that the split is worth it; FLAGBLAS_B200_GROUP_STREAMK=0 (whole
+    tiles) must agree to the output type's rounding."""
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("FLAGBLAS_B200_GROUP_STREAMK", mode)
+        outs[mode] = _run_group(kind, [300, 100, 0, 520, 77], 4096 if kind == "tf32" else 8192, 512, 1.5, 0.5, seed=21)
+    assert_parity(outs["1"], outs["0"], KINDS[kind][2], 2.0, "grouped stream-k tail vs whole tiles")
+
+
 def test_grouped_many_groups():
     _run_group("bf16", [((7 * i) % 90) for i in range(600)], 128, 256, 1.0, 0.0, seed=7)
     # more groups than the table builder keeps in shared memory (its tile counts then go through global memory)
