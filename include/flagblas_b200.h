@@ -73,7 +73,9 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
             int64_t lda, const void* B, int64_t ldb, float beta, void* C, int64_t ldc, void* workspace,
             size_t workspace_bytes, void* stream);
 
-/* Bytes of workspace fb_gemm needs for these arguments (0 when none). */
+/* Bytes of workspace fb_gemm asks for with these arguments (0 when none): packed copies of operands that cannot be
+ * fetched in place (required), plus optional scratch for fp32 partial sums (a split of a long k range, the
+ * stream-K tail of a half-empty last wave of tiles); without the optional part the call runs unsplit. */
 size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
                                int64_t lda, const void* B, int64_t ldb);
 
@@ -193,6 +195,8 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
                 int64_t b_group_stride, void* C, int64_t ldc, const int32_t* d_offs, int group_count, int64_t n,
                 int64_t k, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Bytes the grouped entry points ask for: the two tile tables with their tensor maps (required) plus the
+ * partial-sum slots of the stream-K tail (optional: with only the tables' bytes the call runs whole tiles). */
 size_t fb_group_workspace_bytes(int group_count);
 
 /*
