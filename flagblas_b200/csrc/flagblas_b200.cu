@@ -336,8 +336,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     const long long dp = tiles / workers, rem = tiles - dp * workers;
     long long group = rem > 0 ? workers / rem : 0;  // workers per tail tile
     if (group > 4) group = 4;
-    // head start of the owner: about 12 k cycles (parking a 128 x 256 fp32 tile per CTA and reading it back), in stages
-    const long long head = (20 + p.ks - 1) / p.ks;
+    // head start of the owner over a contributor, which still has to park a 128 x 256 fp32 tile per CTA: in 64-deep
+    // stages; measured flat between 8 and 16 (4096 x 4096 x 8192: 1358 / 1361 / 1355 / 1350 TFLOP/s at 4 / 12 / 20 / 28)
+    const long long head = (env_int("FLAGBLAS_B200_SK_HEAD", 12) + p.ks - 1) / p.ks;
     const long long share = group >= 2 ? (stages - head) / group : 0;
     if (group >= 2 && share >= 2 && dp < 9) {
       pp.sk_enabled = 1;
@@ -1299,7 +1300,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.group_maps = ps.maps;
     if (tail) {
       p.sk_grouped = 1;
-      p.sk_head = (20 + ks - 1) / ks;
+      p.sk_head = (env_int("FLAGBLAS_B200_SK_HEAD", 12) + ks - 1) / ks;
       p.sk_flags = reinterpret_cast<int*>(tail);
       p.sk_partials = reinterpret_cast<float*>(tail + kStreamKFlagBytes);
     }
