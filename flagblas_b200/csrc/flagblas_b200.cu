@@ -625,7 +625,7 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   }
   const long long dp = pl.tiles / split_workers, rem = pl.tiles - dp * split_workers;
   pl.want_streamk = rem > 0 && dp < 9 && 2 * rem <= split_workers && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
-                    stages >= 32 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
+                    stages >= env_int("FLAGBLAS_B200_SK_MIN_STAGES", 32) && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
   return pl;
 }
 
