@@ -561,7 +561,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int num_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[3] = clock64();  // timeline: entry
-  if (p.splitk > 1) grid_launch_dependents();  // the kernel that adds the parts may start its prologue now
+  // Whatever is queued behind this kernel as a programmatic dependent (the next GEMM of the caller, the kernel
+  // that adds split-K parts) may take SMs as this grid's CTAs leave them and run its prologue; it waits for the
+  // whole grid before it touches global memory.
+  grid_launch_dependents();
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -601,7 +604,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // Grouped calls are launched as programmatic dependents of the table builder: everything above ran
   // while it was still working; its table and tensor maps may be read only from here on.
-  if (grouped || p.wait_prior) grid_dependency_wait();
+  // Every launch is a programmatic dependent of whatever precedes it on the stream (the table builder, a packing
+  // kernel, the caller's previous kernel): all of the above overlapped with its tail; global memory only from here.
+  grid_dependency_wait();
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
   const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
 

@@ -321,7 +321,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     attrs[n_attrs].val.clusterDim.x = 2; attrs[n_attrs].val.clusterDim.y = 1; attrs[n_attrs].val.clusterDim.z = 1;
     ++n_attrs;
   }
-  if ((p.num_groups > 0 || p.wait_prior) && env_int("FLAGBLAS_B200_PDL", 1) != 0) {
+  if (env_int("FLAGBLAS_B200_PDL", 1) != 0) {
     // grouped: overlap this kernel's launch and prologue with the table builder queued just before it
     attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
