@@ -31,6 +31,7 @@ struct GroupPass {
   int rows_mod;   // 0: the pass covers every row; else: pass covers the first floor(m / rows_mod) * rows_mod
                   // rows (`leading` = 1) or the rows after them (`leading` = 0)
   int leading;
+  int keep_over;  // > 0: a trailing remainder of more than `keep_over` rows stays with the leading pass
   int block_n;
   GroupRec* recs;       // [num_groups]
   int* total_tiles;     // device scalar
@@ -234,7 +235,8 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       // rows of the group this pass is responsible for: [row_base, row_base + rows)
       long long row_base = 0, rows = m;
       if (ps.rows_mod > 0) {
-        const long long lead = m / ps.rows_mod * ps.rows_mod;
+        long long lead = m / ps.rows_mod * ps.rows_mod;
+        if (ps.keep_over > 0 && m - lead > ps.keep_over) lead = m;  // a long remainder is one more (padded) tile of the leading pass
         if (ps.leading) rows = lead;
         else { row_base = lead; rows = m - lead; }
       }

@@ -1238,6 +1238,8 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     if (split) {
       pass[0].rows_mod = 2 * kBlockM; pass[0].leading = 1;
       pass[1].enabled = 1; pass[1].tile_m = kBlockM; pass[1].rows_mod = 2 * kBlockM; pass[1].leading = 0;
+      // FLAGBLAS_B200_GROUP_SPLIT=2: only remainders of at most 128 rows go to the single-CTA pass
+      if (env_int("FLAGBLAS_B200_GROUP_SPLIT", 0) == 2) pass[0].keep_over = pass[1].keep_over = kBlockM;
     }
   } else {
     pass[0].enabled = 1; pass[0].tile_m = kBlockM;

@@ -96,11 +96,12 @@ def test_grouped_alpha_zero_and_beta_zero(kind):
     assert not torch.isnan(got).any()
 
 
-@pytest.mark.parametrize("env", [{"FLAGBLAS_B200_GROUP_SPLIT": "1"}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_TMA3D": "0"},
+@pytest.mark.parametrize("env", [{"FLAGBLAS_B200_GROUP_SPLIT": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"}, {"FLAGBLAS_B200_PAIR": "0"},
+                                 {"FLAGBLAS_B200_TMA3D": "0"},
                                  {"FLAGBLAS_B200_KS": "1"}])
 def test_grouped_tile_plan_variants(env, monkeypatch):
-    """The alternative tile plans (two-pass split, single-CTA tiles, 2-D copies, one k-slab per stage)
-    compute the same thing."""
+    """The alternative tile plans (two-pass split of every remainder or only of remainders up to 128 rows,
+    single-CTA tiles, 2-D copies, one k-slab per stage) compute the same thing."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     _run_group("bf16", [5, 0, 70, 33, 300, 128, 129, 1, 700, 256], 512, 384, 1.5, 0.5, seed=11)
