@@ -363,6 +363,11 @@ __device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_addr) {
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
   return v;
 }
+// 16-byte store into the shared memory of any CTA of the cluster (address from mapa_shared).
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, const float4& v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ void cluster_arrive_release() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }

@@ -30,6 +30,9 @@ struct SimtParams {
   int b_mn_contig;  // 1: B stored [k, ldb] (transb = N); 0: stored [n, ldb]
   int a_vec, b_vec, c_vec;  // 16-byte aligned base and leading dimension
   int tiles_n;
+  // 2: the launch uses clusters of two CTAs that share an output tile, each taking half of k; the second hands its
+  // sums to the first through distributed shared memory (pipelined kernel only; small problems with few tiles).
+  int ksplit;
 };
 
 // Fetch this thread's 4 elements of a (TILE_MN x BK) operand slice.
@@ -232,8 +235,13 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
 
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int tile_m = blockIdx.x / p.tiles_n, tile_n = blockIdx.x % p.tiles_n;
+  const int parts = p.ksplit == 2 ? 2 : 1;
+  const int tile = static_cast<int>(blockIdx.x) / parts, part = static_cast<int>(blockIdx.x) % parts;
+  const int tile_m = tile / p.tiles_n, tile_n = tile % p.tiles_n;
   const int m0 = tile_m * BM, n0 = tile_n * BN;
+  // this CTA's k range (whole slices)
+  const int k_per = ((p.k + parts - 1) / parts + kPipeK - 1) / kPipeK * kPipeK;
+  const int k_begin = part * k_per, k_end = min(p.k, k_begin + k_per);
 
   float acc[TM][TN];
 #pragma unroll
@@ -245,12 +253,12 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
   auto row_of = [&](int i) { return (i / 4) * (BM / RG) + ty * 4 + (i % 4); };
   auto col_of = [&](int j) { return BKM ? tx + 16 * j : (j / 4) * (BN / CG) + tx * 4 + (j % 4); };
 
-  const int k_iters = (p.k + kPipeK - 1) / kPipeK;
+  const int k_iters = k_end > k_begin ? (k_end - k_begin + kPipeK - 1) / kPipeK : 0;
 #pragma unroll
   for (int s = 0; s < kPipeStages - 1; ++s) {
     if (s < k_iters) {
-      pipe_load<BM, AK>(As + s * kAFloats, p.A, p.lda, m0, s * kPipeK, p.m, p.k, tid);
-      pipe_load<BN, BKM>(Bs + s * kBFloats, p.B, p.ldb, n0, s * kPipeK, p.n, p.k, tid);
+      pipe_load<BM, AK>(As + s * kAFloats, p.A, p.lda, m0, k_begin + s * kPipeK, p.m, k_end, tid);
+      pipe_load<BN, BKM>(Bs + s * kBFloats, p.B, p.ldb, n0, k_begin + s * kPipeK, p.n, k_end, tid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
@@ -262,8 +270,8 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
       const int nx = it + kPipeStages - 1;
       if (nx < k_iters) {
         const int slot = nx % kPipeStages;
-        pipe_load<BM, AK>(As + slot * kAFloats, p.A, p.lda, m0, nx * kPipeK, p.m, p.k, tid);
-        pipe_load<BN, BKM>(Bs + slot * kBFloats, p.B, p.ldb, n0, nx * kPipeK, p.n, p.k, tid);
+        pipe_load<BM, AK>(As + slot * kAFloats, p.A, p.lda, m0, k_begin + nx * kPipeK, p.m, k_end, tid);
+        pipe_load<BN, BKM>(Bs + slot * kBFloats, p.B, p.ldb, n0, k_begin + nx * kPipeK, p.n, k_end, tid);
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -337,6 +345,31 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  if (parts == 2) {
+    // The mailbox sits behind the ring: [16-byte unit][thread], so a warp's accesses cover 512 consecutive bytes.
+    float* mailbox = pipe_smem + kPipeStages * (kAFloats + kBFloats);
+    const uint32_t mine = smem_u32(mailbox) + static_cast<uint32_t>(tid) * 16u;
+    if (part == 1) {
+      const uint32_t theirs = mapa_shared(mine, 0);
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; j += 4)
+          st_cluster_v4(theirs + static_cast<uint32_t>((i * TN + j) / 4) * 4096u,
+                        make_float4(acc[i][j], acc[i][j + 1], acc[i][j + 2], acc[i][j + 3]));
+    }
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (part == 1) return;
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; j += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(mailbox + ((i * TN + j) / 4) * 1024 + tid * 4);
+        acc[i][j] += v.x; acc[i][j + 1] += v.y; acc[i][j + 2] += v.z; acc[i][j + 3] += v.w;
+      }
+  }
 
   // epilogue: alpha * acc + beta * C, C never read when beta == 0
 #pragma unroll

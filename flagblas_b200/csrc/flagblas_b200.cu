@@ -432,6 +432,27 @@ static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t 
     FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     attr_set[dev] = true;
   }
+  if (p.ksplit == 2) {
+    // clusters of two CTAs per tile; the first CTA's mailbox for the second's sums sits behind the ring
+    constexpr int kMailbox = BM * BN * 4;
+    static bool attr2_set[64] = {};
+    if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
+      FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes + kMailbox));
+      attr2_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * tiles));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = kBytes + kMailbox;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+    return FB_OK;
+  }
   kern<<<static_cast<unsigned>(tiles), 256, kBytes, stream>>>(p);
   FB_CUDA_OK(cudaGetLastError());
   return FB_OK;
@@ -471,6 +492,8 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   const long long tiles = big ? big_tiles : ((m + 63) / 64) * p.tiles_n;
   // 16-byte aligned operands take the cp.async pipeline; FLAGBLAS_B200_SGEMM_PIPE=0 forces the
   // register-staged kernel (profiling sweeps), which also serves everything unaligned.
+  // Few tiles and a k worth halving: two CTAs per tile (FLAGBLAS_B200_SGEMM_KSPLIT=0 switches it off).
+  p.ksplit = (!big && 2 * tiles <= sms && k >= 256 && env_int("FLAGBLAS_B200_SGEMM_KSPLIT", 1) != 0) ? 2 : 1;
   if (p.a_vec && p.b_vec && env_int("FLAGBLAS_B200_SGEMM_PIPE", 1) != 0)
     return big ? dispatch_sgemm_pipe<128, 128>(p, tiles, stream) : dispatch_sgemm_pipe<64, 64>(p, tiles, stream);
   if (big) sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
