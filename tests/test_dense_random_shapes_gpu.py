@@ -55,3 +55,38 @@ def test_random_shapes_match_fp64_product(chunk):
         scale = abs(alpha) * (k ** 0.5) * 0.25 * 0.25 + abs(beta) * 0.5
         assert_parity(C[:, :n].float().cpu(), ref.float().cpu(), rtol, scale, what)
         assert torch.equal(C[:, n:], C0[:, n:]), what + ": padding columns of C were written"
+
+
+@pytest.mark.parametrize("chunk", range(2))
+def test_random_shapes_sgemm(chunk):
+    """The same draw for IEEE fp32 sgemm: 64 x 64 and 128 x 128 tiles, the two-CTA split of k for small problems, the
+    register-staged kernel for operands that are not 16-byte aligned."""
+    rnd = random.Random(2000 + chunk)
+    for case in range(20):
+        ta, tb = rnd.randint(0, 1), rnd.randint(0, 1)
+        m = rnd.choice([1, 7, 33, 64, 100, 129, 256, 300, 512, 1024])
+        n = rnd.choice([8, 64, 120, 256, 264, 512, 1000, 1536])
+        k = rnd.choice([16, 100, 256, 260, 512, 1000, 2048, 4100])
+        pad = rnd.choice([0, 0, 4, 3])
+        cols_a, cols_b = (m if ta else k), (k if tb else n)
+        lda, ldb, ldc = cols_a + pad, cols_b + pad, n + rnd.choice([0, 0, 4, 1])
+        g = torch.Generator(device="cpu").manual_seed(5000 + chunk * 100 + case)
+        A = (torch.randn((k if ta else m), lda, generator=g) * 0.25).to(DEV)
+        B = (torch.randn((n if tb else k), ldb, generator=g) * 0.25).to(DEV)
+        C0 = (torch.randn(m, ldc, generator=g) * 0.5).to(DEV)
+        alpha, beta = rnd.choice([1.0, 1.5, -0.5]), rnd.choice([0.0, 0.0, 1.0, 0.5])
+        C = C0.clone()
+        if beta == 0:
+            C[:, :n] = float("nan")
+        fb.sgemm(ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
+        torch.cuda.synchronize()
+        what = "fp32 ta=%d tb=%d %dx%dx%d ld=%d/%d/%d alpha=%g beta=%g" % (ta, tb, m, n, k, lda, ldb, ldc, alpha, beta)
+        assert fb.device_status() == 0, what
+        op_a = (A[:, :cols_a].t() if ta else A[:, :cols_a]).double()
+        op_b = (B[:, :cols_b].t() if tb else B[:, :cols_b]).double()
+        ref = alpha * (op_a @ op_b)
+        if beta != 0:
+            ref = ref + beta * C0[:, :n].double()
+        scale = abs(alpha) * (k ** 0.5) * 0.25 * 0.25 + abs(beta) * 0.5
+        assert_parity(C[:, :n].cpu(), ref.float().cpu(), KINDS["fp32"][2], scale, what)
+        assert torch.equal(C[:, n:], C0[:, n:]), what + ": padding columns of C were written"
