@@ -487,7 +487,10 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   p.b_mn_contig = transb ? 0 : 1;
   p.a_vec = aligned16(A, lda, 4); p.b_vec = aligned16(B, ldb, 4); p.c_vec = aligned16(C, ldc, 4);
   const long long big_tiles = ((m + 127) / 128) * ((n + 127) / 128);
-  const bool big = big_tiles >= 2LL * sms;
+  // 128 x 128 tiles once they nearly fill the GPU (measured: 144 tiles, 1536^3, 34.5 -> 41.9 TFLOP/s; 256 tiles, 2048^3,
+  // 36.1 -> 41.1; but 100 tiles, 1280 x 1280 x 4096, 31.9 -> 29.7 and 64 tiles, 1024^3, 28.7 -> 18.2): below that
+  // 64 x 64 tiles, two CTAs per SM.
+  const bool big = big_tiles >= env_int("FLAGBLAS_B200_SGEMM_BIG_TILES", sms * 7 / 8);
   p.tiles_n = static_cast<int>(big ? (n + 127) / 128 : (n + 63) / 64);
   const long long tiles = big ? big_tiles : ((m + 63) / 64) * p.tiles_n;
   // 16-byte aligned operands take the cp.async pipeline; FLAGBLAS_B200_SGEMM_PIPE=0 forces the
