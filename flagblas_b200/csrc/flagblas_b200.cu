@@ -495,8 +495,10 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   const long long tiles = big ? big_tiles : ((m + 63) / 64) * p.tiles_n;
   // 16-byte aligned operands take the cp.async pipeline; FLAGBLAS_B200_SGEMM_PIPE=0 forces the
   // register-staged kernel (profiling sweeps), which also serves everything unaligned.
-  // Few tiles and a k worth halving: two CTAs per tile (FLAGBLAS_B200_SGEMM_KSPLIT=0 switches it off).
-  p.ksplit = (!big && 2 * tiles <= sms && k >= 256 && env_int("FLAGBLAS_B200_SGEMM_KSPLIT", 1) != 0) ? 2 : 1;
+  // 64 x 64 tiles that do not fill two CTAs per SM, and a k worth halving: two CTAs per tile (768^3 25.1 -> 28.5 TFLOP/s,
+  // 896^3 21.8 -> 27.8, 640 x 640 x 2048 19.4 -> 22.6; FLAGBLAS_B200_SGEMM_KSPLIT=0 switches it off).
+  p.ksplit = (!big && tiles <= env_int("FLAGBLAS_B200_SGEMM_KSPLIT_TILES", 2 * sms) && k >= 256 &&
+              env_int("FLAGBLAS_B200_SGEMM_KSPLIT", 1) != 0) ? 2 : 1;
   if (p.a_vec && p.b_vec && env_int("FLAGBLAS_B200_SGEMM_PIPE", 1) != 0)
     return big ? dispatch_sgemm_pipe<128, 128>(p, tiles, stream) : dispatch_sgemm_pipe<64, 64>(p, tiles, stream);
   if (big) sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
