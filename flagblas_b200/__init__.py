@@ -12,7 +12,7 @@ from . import runtime, testing  # noqa: F401
 from . import _lib
 from .ops import *  # noqa: F401,F403
 from .ops import __all__ as _ops_all
-from ._lib import FlagBlasError, device_status  # noqa: F401
+from ._lib import FlagBlasError, device_status, reload_env  # noqa: F401
 
 # ``flag_blas.c_operators`` is the name the reference reserves for a compiled extension
 # (src/flag_blas/config.py:35-41); here it is the pybind11 module over the C ABI.
@@ -25,5 +25,5 @@ vendor_name = runtime.device.vendor_name
 __version__ = "0.1.0"
 
 __all__ = list(_ops_all) + ["runtime", "testing", "device", "vendor_name", "c_operators", "FlagBlasError",
-                            "device_status", "host", "enable", "only_enable", "use_blas", "all_registered_ops",
+                            "device_status", "reload_env", "host", "enable", "only_enable", "use_blas", "all_registered_ops",
                             "all_registered_keys"]

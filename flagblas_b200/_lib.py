@@ -32,10 +32,16 @@ class FlagBlasError(RuntimeError):
 
 def _load():
     path = _build.LIB_PATH
-    if not os.path.exists(path) or not os.path.exists(_build.EXT_PATH):
-        # Source checkout without built native code: build it once (needs nvcc and g++, not a GPU).
+    if not _build.up_to_date():
+        # No built native code, or one built from other sources than the ones beside it (the binaries are not
+        # version controlled): build it now (needs nvcc and g++, not a GPU).
         _build.build()
     handle = ctypes.CDLL(path)
+    handle.fb_build_id.restype = ctypes.c_char_p
+    handle.fb_build_id.argtypes = []
+    if handle.fb_build_id().decode() != _build.source_id():
+        raise ImportError("libflagblas_b200.so was built from other sources (build id %s, sources %s); "
+                          "run python -m flagblas_b200.build" % (handle.fb_build_id().decode(), _build.source_id()))
     c = ctypes
     i64, f32, vp, sz, i32 = c.c_int64, c.c_float, c.c_void_p, c.c_size_t, c.c_int
     handle.fb_gemm.restype = i32
@@ -73,6 +79,8 @@ def _load():
     handle.fb_last_cuda_error.argtypes = []
     handle.fb_sm_count.restype = i32
     handle.fb_sm_count.argtypes = []
+    handle.fb_reload_env.restype = None
+    handle.fb_reload_env.argtypes = []
     handle.fb_debug_set_profile_buffer.restype = None
     handle.fb_debug_set_profile_buffer.argtypes = [vp]
     handle.fb_selftest_bounded_wait.restype = i32
@@ -103,6 +111,8 @@ EXPORTED_SYMBOLS = (
     "fb_device_status",
     "fb_last_cuda_error",
     "fb_sm_count",
+    "fb_reload_env",
+    "fb_build_id",
     "fb_selftest_bounded_wait",
     "fb_debug_set_profile_buffer",
 )
@@ -163,3 +173,8 @@ def check(status, where=""):
 def device_status(reset=True):
     """Synchronise and return the device status word (0 = healthy)."""
     return cop.device_status(1 if reset else 0)
+
+
+def reload_env():
+    """Have the library read its ``FLAGBLAS_B200_*`` switches again (it reads the environment once per process)."""
+    cop.reload_env()

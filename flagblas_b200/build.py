@@ -16,6 +16,21 @@ _DEPS = sorted(
     os.path.join(_HERE, "csrc", f) for f in os.listdir(os.path.join(_HERE, "csrc")) if f.endswith((".cu", ".cuh"))
 ) + [os.path.join(os.path.dirname(_HERE), "include", "flagblas_b200.h")]
 
+ID_PATH = LIB_PATH + ".buildid"
+
+
+def source_id():
+    """Hash of every source the library is compiled from (and of the flags): the library carries it
+    (``fb_build_id()``) so that a binary built from other sources is never loaded silently."""
+    import hashlib
+
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for path in _DEPS + [_EXT_SRC]:
+        with open(path, "rb") as f:
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
+    return h.hexdigest()[:32]
+
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -57,26 +72,33 @@ def build_extension(force=False):
 
 
 def up_to_date():
-    if not os.path.exists(LIB_PATH):
+    """True when the built library and extension were made from the sources as they are now."""
+    if not (os.path.exists(LIB_PATH) and os.path.exists(EXT_PATH) and os.path.exists(ID_PATH)):
         return False
-    t = os.path.getmtime(LIB_PATH)
-    return all(not os.path.exists(d) or os.path.getmtime(d) <= t for d in _DEPS)
+    with open(ID_PATH) as f:
+        return f.read().strip() == source_id()
 
 
 def build(force=False, verbose=False):
     """Compile ``csrc/flagblas_b200.cu`` into ``libflagblas_b200.so`` (no GPU needed)."""
     if not force and up_to_date():
-        build_extension()
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH, _SRC]
+    sid = source_id()
+    if os.path.exists(ID_PATH):
+        os.remove(ID_PATH)
+    cmd = ([_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) +
+           ['-DFB_BUILD_ID="%s"' % sid, "-o", LIB_PATH, _SRC])
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose:
         sys.stderr.write(res.stderr)
     build_extension(force=True)
+    with open(ID_PATH, "w") as f:
+        f.write(sid + "\n")
     return LIB_PATH
 
 
 if __name__ == "__main__":
-    print(build(force=True, verbose="-v" in sys.argv))
+    # (importing the package has already rebuilt a stale binary; -f compiles again regardless)
+    print(build(force="-f" in sys.argv or "-v" in sys.argv, verbose="-v" in sys.argv))

@@ -68,6 +68,7 @@ PYBIND11_MODULE(c_operators, m) {
   m.def("device_status", &fb_device_status);
   m.def("last_cuda_error", &fb_last_cuda_error);
   m.def("sm_count", &fb_sm_count);
+  m.def("reload_env", &fb_reload_env);
   m.def("selftest_bounded_wait", [](int64_t limit, addr stream) { return fb_selftest_bounded_wait(limit, p(stream)); });
   m.def("debug_set_profile_buffer", [](addr buf) { fb_debug_set_profile_buffer(p(buf)); });
   m.attr("FB_F32") = static_cast<int>(FB_F32);

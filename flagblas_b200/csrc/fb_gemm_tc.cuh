@@ -22,6 +22,18 @@
 
 #include "fb_ptx.cuh"
 
+// Profiling switches that skip the MMAs, the copies or the stores of a launch (its results are then meaningless)
+// exist only in builds made with -DFB_PROFILING_SWITCHES; the shipped library contains none of those branches.
+#ifdef FB_PROFILING_SWITCHES
+#define FB_AND_COPIES_ON(p) && !((p).debug & 2)
+#define FB_MMA_ON(p) (!((p).debug & 1))
+#define FB_STORES_ON(p) (!((p).debug & 4))
+#else
+#define FB_AND_COPIES_ON(p)
+#define FB_MMA_ON(p) true
+#define FB_STORES_ON(p) true
+#endif
+
 namespace fb {
 
 constexpr int kBlockM = 128;        // rows of C per tile == TMEM lanes
@@ -68,13 +80,21 @@ struct GroupRec {
   int tile_start;  // first linear tile index of this group
   int tiles_n;
   int vec_ok;
-  int a3d, b3d;  // this group's A / B tensor map is a 3-D view (one copy per stage)
+  // How the producers fetch this group's A / B: kFetch2d / kFetch3d = through the group's tensor map (2-D boxes, or
+  // a 3-D view with one copy per stage); 2, 4, 8 or 16 = by hand with loads of that many bytes, for an operand
+  // whose base or row pitch is not 16-byte aligned (TMA cannot address it).
+  int a_fetch, b_fetch;
   int row_base;  // first row of the group this pass covers (rows before it belong to the other pass)
   void* out;
   long long ldo;
   const void* cin;
   long long ldcin;
+  // raw operands, for the hand-filled path
+  const void* a;
+  const void* b;
+  long long lda, ldb;  // elements
 };
+enum : int { kFetch2d = 0, kFetch3d = 1 };  // >= 2: hand-filled, the value is the load width in bytes
 
 struct TcGemmParams {
   // dense: the single problem.  grouped: unused (see `groups`).
@@ -90,7 +110,7 @@ struct TcGemmParams {
   // grouped mode (num_groups > 0): table + per-group tensor maps in global memory
   int num_groups;
   const GroupRec* groups;
-  const int* total_tiles;        // device scalar written by the table builder
+  const int* total_tiles;        // written by the table builder: [0] tile count, [1] some operand is fetched by hand
   const CUtensorMap* group_maps;  // [2 * num_groups]: A_g, B_g
   // Stream-K tail (dense mode only).  When `sk_enabled`, every worker first takes `sk_dp` whole tiles
   // (tile = worker + i * workers); each of the `sk_rem` tiles left over (at most half as many as there are
@@ -118,7 +138,8 @@ struct TcGemmParams {
   // shared memory; after a cluster barrier every CTA adds, over distributed shared memory and in rank order, the
   // 128 / cluster_k rows it is responsible for and writes them out.  No scratch memory, no second kernel.
   int cluster_k;
-  // Profiling switches (results are meaningless when set): bit 0 = issue no MMA, bit 1 = issue no TMA copy.
+  // Profiling switches, honoured only by builds with -DFB_PROFILING_SWITCHES (results are meaningless when set):
+  // bit 0 = issue no MMA, bit 1 = issue no TMA copy, bit 2 = store nothing.
   int debug;
   int stages;  // pipeline stages actually used (<= the compiled maximum)
   // Optional cycle accounting (profiling builds of a call): 16 counters written by CTA 0, or null.
@@ -497,6 +518,95 @@ __device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages,
   return true;
 }
 
+// ---- operand stages filled by hand (grouped calls: an operand whose base or row pitch is not 16-byte aligned
+// cannot be described by a tensor map, and the host never sees the addresses)
+//
+// One 16-byte unit of a stage holds 16 / ESZ consecutive elements of the operand's contiguous dimension; `valid` of
+// them exist (the rest lies beyond the matrix and reads as zero, like a TMA box that crosses the edge).  VEC = bytes
+// per load = the alignment that base and pitch guarantee for every unit.
+template <int ESZ, int VEC>
+__device__ __forceinline__ uint4 load_unit(const uint8_t* src, int valid) {
+  constexpr int kPer = 16 / ESZ;
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
+  if (valid >= kPer) {
+    if constexpr (VEC == 16) {
+      return __ldg(reinterpret_cast<const uint4*>(src));
+    } else if constexpr (VEC == 8) {
+      const uint2 lo = __ldg(reinterpret_cast<const uint2*>(src)), hi = __ldg(reinterpret_cast<const uint2*>(src) + 1);
+      return make_uint4(lo.x, lo.y, hi.x, hi.y);
+    } else if constexpr (VEC == 4) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
+      return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if constexpr (ESZ == 4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j < valid) w[j] = __ldg(reinterpret_cast<const uint32_t*>(src) + j);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < valid) w[j >> 1] |= static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(src) + j)) << ((j & 1) * 16);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Whole warp: writes this CTA's part of one pipeline stage of one operand (`ks` k-slabs of a `tile_mn`-row tile
+// starting at row / column `mn0`, k offset `k0`) in exactly the swizzled layout the TMA copies produce, then
+// credits the bytes to the stage's barrier (`bar_addr`, a shared::cluster address), each lane for what it wrote.
+//   K-major operand (stored [mn, ld], K contiguous):  [slab][tile row][128 B], 16-byte units XORed with row % 8.
+//   MN-major operand (stored [k, ld], MN contiguous): [128-byte chunk of MN][k row of the stage][128 B]; units XORed
+//     with k row % 8, or for 32-bit elements 32-byte atoms XORed with k row % 4.
+template <int ESZ, int VEC>
+__device__ __noinline__ void fill_stage_by_hand(uint8_t* dst, uint32_t bar_addr, int mn_major, int ks, int tile_mn,
+                                                const uint8_t* base, long long ld, int mn0, int mn_limit, int k0,
+                                                int k_limit) {
+  constexpr int kPer = 16 / ESZ, kSpan = 128 / ESZ;
+  const int lane = threadIdx.x & 31;
+  const int total = ks * tile_mn * 8;  // 16-byte units
+  const int k_rows = kSpan * ks;
+  const uint32_t dst_addr = smem_u32(dst);
+#pragma unroll 4
+  for (int u = lane; u < total; u += 32) {
+    const int unit = u & 7, rr = u >> 3;
+    long long r_src, c_src;  // row and first column of the unit in the stored matrix
+    int valid;
+    uint32_t off;
+    if (!mn_major) {
+      const int slab = rr / tile_mn, row = rr - slab * tile_mn;
+      const int r = mn0 + row, kk = k0 + slab * kSpan + unit * kPer;
+      valid = r < mn_limit ? k_limit - kk : 0;
+      off = static_cast<uint32_t>(rr * 128 + ((unit ^ (row & 7)) << 4));
+      r_src = r; c_src = kk;
+    } else {
+      const int krow = rr % k_rows;
+      const int kk = k0 + krow, mn = mn0 + (rr / k_rows) * kSpan + unit * kPer;
+      valid = kk < k_limit ? mn_limit - mn : 0;
+      const int su = ESZ == 4 ? ((((unit >> 1) ^ (krow & 3)) << 1) | (unit & 1)) : (unit ^ (krow & 7));
+      off = static_cast<uint32_t>(rr * 128 + (su << 4));
+      r_src = kk; c_src = mn;
+    }
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (valid > 0) v = load_unit<ESZ, VEC>(base + (r_src * ld + c_src) * ESZ, valid);
+    st_shared_v4(dst_addr + off, v);
+  }
+  fence_proxy_async_all();
+  fence_acq_rel_cluster();
+  mbar_complete_tx_cluster(bar_addr, static_cast<uint32_t>(total / 32) * 16u);
+}
+
+template <int ESZ>
+__device__ __forceinline__ void fill_stage_dispatch(int vec, uint8_t* dst, uint32_t bar_addr, int mn_major, int ks,
+                                                    int tile_mn, const void* base, long long ld, int mn0, int mn_limit,
+                                                    int k0, int k_limit) {
+  const uint8_t* b = static_cast<const uint8_t*>(base);
+  if (vec >= 16) fill_stage_by_hand<ESZ, 16>(dst, bar_addr, mn_major, ks, tile_mn, b, ld, mn0, mn_limit, k0, k_limit);
+  else if (vec == 8) fill_stage_by_hand<ESZ, 8>(dst, bar_addr, mn_major, ks, tile_mn, b, ld, mn0, mn_limit, k0, k_limit);
+  else if (vec == 4) fill_stage_by_hand<ESZ, 4>(dst, bar_addr, mn_major, ks, tile_mn, b, ld, mn0, mn_limit, k0, k_limit);
+  else if constexpr (ESZ == 2) fill_stage_by_hand<ESZ, 2>(dst, bar_addr, mn_major, ks, tile_mn, b, ld, mn0, mn_limit, k0, k_limit);
+}
+
 // PAIR = true: two CTAs of a cluster work on one 256 x BLOCK_N tile with
 // tcgen05 cta_group::2.  Each CTA fetches its own 128 rows of A and its own half
 // of the B tile into its own shared memory, the leader CTA (cluster rank 0)
@@ -611,10 +721,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
 
   if (warp == 0 || warp == 3) {
-    // ----------------------------------------------------------- TMA producers
+    // ----------------------------------------------------------- producers
     // Two issuing threads so that the copies of one stage are not serialised behind each
     // other: warp 0 arms the stage's barrier and fetches A, warp 3 fetches B.
-    if (lane == 0) {
+    // A grouped call in which some operand cannot be addressed by TMA (`by_hand`, found by the table builder) runs
+    // the loop with all 32 lanes: lane 0 still issues the copies of the operands that have tensor maps, the whole
+    // warp fills the others with ordinary loads and stores and credits the stage's barrier with the same byte count.
+    const bool by_hand = grouped && p.total_tiles[1] != 0;
+    if (by_hand || lane == 0) {
       const bool load_a = warp == 0;
       const OperandGeom& og = load_a ? p.a : p.b;
       int stage = 0;
@@ -635,6 +749,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const CUtensorMap* map = load_a ? &tmA : &tmB;
         uint32_t use3d = og.use3d;
         int row_base = 0;
+        int fetch = kFetch2d;          // grouped: how this group's operand is fetched
+        const void* raw = nullptr;     // hand-filled operand: base, pitch and extent along M / N
+        long long raw_ld = 0;
+        int mn_limit = 0;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           const GroupRec& gr = p.groups[g];
@@ -643,9 +761,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tn = lt - tm * gr.tiles_n;
           kk_total = gr.k;
           map = &p.group_maps[2 * g + (load_a ? 0 : 1)];
-          use3d = load_a ? gr.a3d : gr.b3d;
+          fetch = load_a ? gr.a_fetch : gr.b_fetch;
+          use3d = fetch == kFetch3d;
           row_base = gr.row_base;
-          fence_tensormap_acquire(map);
+          if (fetch > kFetch3d) {
+            raw = load_a ? gr.a : gr.b;
+            raw_ld = load_a ? gr.lda : gr.ldb;
+            mn_limit = load_a ? gr.m : gr.n;
+          } else if (lane == 0) {
+            fence_tensormap_acquire(map);
+          }
         } else {
           swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
           kk_total = p.k;
@@ -658,7 +783,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int kb_begin = item.sb, kb_end = item.se;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
+          if (by_hand) {
+            if (!mbar_wait_warp<0>(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
+          } else if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wctl, DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
           const long long c1 = p.prof ? clock64() : 0;
           prof_wait += c1 - c0;
           const int k0 = kb * static_cast<int>(p.block_k);
@@ -667,11 +794,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t slab_bytes = load_a ? Cfg::kABytes : Cfg::kBBytes;
           uint32_t bar = smem_u32(&full_bar[stage]);
           if constexpr (PAIR) bar = mapa_shared(bar, 0);  // both CTAs' copies are credited to the leader's barrier
-          if (load_a && cta_rank == 0) {
+          if (load_a && cta_rank == 0 && lane == 0) {
+#ifdef FB_PROFILING_SWITCHES
             if (p.debug & 2) mbar_arrive(&full_bar[stage]);
-            else mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (a_stage_bytes + b_stage_bytes));
+            else
+#endif
+            mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (a_stage_bytes + b_stage_bytes));
           }
-          if (!(p.debug & 2)) {
+          if (fetch > kFetch3d) {
+            // no tensor map for this operand: the whole warp fills the stage
+            fill_stage_dispatch<kTf32 ? 4 : 2>(fetch, dst, bar, static_cast<int>(og.mn_major), static_cast<int>(p.ks),
+                                               load_a ? kBlockM : Cfg::kBRows, raw, raw_ld, mn0, mn_limit, k0, kk_total);
+          } else if (lane == 0 FB_AND_COPIES_ON(p)) {
             if (use3d) {
               // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row.
               // A 512-wide tile's B stage is two halves, each laid out like a 256-wide tile's B stage
@@ -707,7 +841,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
-      if (p.prof && blockIdx.x == 0) {
+      if (p.prof && blockIdx.x == 0 && lane == 0) {
         if (load_a) { p.prof[0] = prof_wait; p.prof[1] = prof_issue; }
         else p.prof[10] = prof_wait + prof_issue;
       }
@@ -789,7 +923,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < kMaxMma; ++j) {
             if (j < n_mma) {
-              if (!(p.debug & 1)) {
+              if (FB_MMA_ON(p)) {
                 const uint32_t accum = (kb | (j / kH)) != 0 ? 1u : 0u;  // first k-step of the tile overwrites
                 const uint32_t d_half = d_tmem + static_cast<uint32_t>((j % kH) * Cfg::kMmaN);
                 if constexpr (PAIR) umma_pair<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
@@ -938,7 +1072,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           part.ldo = pr.n; part.cin = nullptr; part.ldcin = 0;
           part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
           epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back);
-        } else if (!(p.debug & 4) && ok) {
+        } else if (FB_STORES_ON(p) && ok) {
           epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back);
         } else {
           hand_back();
@@ -985,7 +1119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < 8; ++q)
             __stcg(dst + static_cast<size_t>(c * 8 + q) * Cfg::kTileM, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
                                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
-        } else if (!(p.debug & 4) && ok) {
+        } else if (FB_STORES_ON(p) && ok) {
           epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
         }
       }

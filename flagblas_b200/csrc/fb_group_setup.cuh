@@ -18,7 +18,7 @@
 namespace fb {
 
 enum : int {
-  DEV_GROUP_MISALIGNED = 201,  // a group's A/B base or leading dimension is not 16-byte aligned
+  DEV_GROUP_MISALIGNED = 201,  // a group's A / B address or pitch is not even a multiple of the element size
 };
 
 // One pass over the groups = one launch of the GEMM kernel with one tile shape.  The grouped
@@ -34,7 +34,7 @@ struct GroupPass {
   int keep_over;  // > 0: a trailing remainder of more than `keep_over` rows stays with the leading pass
   int block_n;
   GroupRec* recs;       // [num_groups]
-  int* total_tiles;     // device scalar
+  int* total_tiles;     // device: [0] = tile count of the pass, [1] = 1 when some operand has no tensor map
   CUtensorMap* maps;    // [2 * num_groups]: A_g, B_g
   CUtensorMap tmpl_a, tmpl_b, tmpl_a3, tmpl_b3;  // templates: 2-D A, 2-D B, 3-D A, 3-D B
 };
@@ -64,6 +64,7 @@ struct GroupSetupArgs {
   int esz;         // bytes per element
   int span;        // elements per 128 bytes
   int allow3d;     // build 3-D views where a group's extents allow it
+  int force_by_hand;  // 1: fetch every operand with ordinary loads, aligned or not (tests, comparisons)
   int publish_each;  // 1: publish every map with its own copy-and-fence instruction (profiling comparison)
 };
 
@@ -213,6 +214,7 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       const CUtensorMap* t = warp == 0 ? &ps.tmpl_a : (warp == 1 ? &ps.tmpl_b : (warp == 2 ? &ps.tmpl_a3 : &ps.tmpl_b3));
       reinterpret_cast<uint32_t*>(tmpl[warp])[lane] = reinterpret_cast<const uint32_t*>(t)[lane];
     }
+    if (tid == 0) ps.total_tiles[1] = 0;  // set below when some operand has to be fetched by hand
     __syncthreads();
 
     // ---- per-group records + tensor maps (one warp per group, strided)
@@ -225,13 +227,18 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       const void* cin = in.cin;
       void* out = in.out;
       const bool empty = (m == 0 || n == 0);
-      const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0 &&
-                           ((lda * ga.esz) & 15) == 0 && ((ldb * ga.esz) & 15) == 0;
-      const bool usable = !empty && (aligned || k == 0);
+      // What base and pitch guarantee for every 16-byte unit of the operand: 16 = TMA can address it; less = the
+      // GEMM's producer warps fetch it with loads of that width; less than an element = not a matrix of this type.
+      const uintptr_t a_bits = reinterpret_cast<uintptr_t>(a) | static_cast<uintptr_t>(lda * ga.esz) | 16u;
+      const uintptr_t b_bits = reinterpret_cast<uintptr_t>(b) | static_cast<uintptr_t>(ldb * ga.esz) | 16u;
+      const int a_align = static_cast<int>(a_bits & (~a_bits + 1)), b_align = static_cast<int>(b_bits & (~b_bits + 1));
+      const bool usable = !empty && (k == 0 || (a_align >= ga.esz && b_align >= ga.esz));
       if (!empty && !usable && lane == 0) atomicCAS(&g_fb_status, 0, DEV_GROUP_MISALIGNED);
+      const bool a_tma = a_align == 16 && !ga.force_by_hand, b_tma = b_align == 16 && !ga.force_by_hand;
       // a 3-D view tiles its third dimension in whole 128-byte rows: that extent must divide evenly
-      const bool a3d = ga.allow3d && usable && k > 0 && (k % ga.span) == 0;
-      const bool b3d = ga.allow3d && usable && k > 0 && ((ga.b_k_contig ? k : n) % ga.span) == 0;
+      const bool a3d = ga.allow3d && usable && a_tma && k > 0 && (k % ga.span) == 0;
+      const bool b3d = ga.allow3d && usable && b_tma && k > 0 && ((ga.b_k_contig ? k : n) % ga.span) == 0;
+      if (usable && k > 0 && (!a_tma || !b_tma) && lane == 0) ps.total_tiles[1] = 1;  // the GEMM's producers run as whole warps
       // rows of the group this pass is responsible for: [row_base, row_base + rows)
       long long row_base = 0, rows = m;
       if (ps.rows_mod > 0) {
@@ -247,10 +254,11 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
         r.tiles_n = static_cast<int>((n + ps.block_n - 1) / ps.block_n);
         // tile_start temporarily holds this group's tile count
         r.tile_start = usable ? static_cast<int>((rows + ps.tile_m - 1) / ps.tile_m) * r.tiles_n : 0;
-        r.a3d = a3d ? 1 : 0;
-        r.b3d = b3d ? 1 : 0;
+        r.a_fetch = a_tma ? (a3d ? kFetch3d : kFetch2d) : a_align;
+        r.b_fetch = b_tma ? (b3d ? kFetch3d : kFetch2d) : b_align;
         r.row_base = static_cast<int>(row_base);
         r.out = out; r.ldo = ldo; r.cin = cin; r.ldcin = ldcin;
+        r.a = a; r.b = b; r.lda = lda; r.ldb = ldb;
         r.vec_ok = (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(cin)) & 15) == 0 &&
                     ((ldo * ga.esz) & 15) == 0) ? 1 : 0;
         ps.recs[g] = r;
@@ -263,12 +271,12 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       reinterpret_cast<uint32_t*>(map_slot[warp][0])[lane] = reinterpret_cast<const uint32_t*>(tmpl[a3d ? 2 : 0])[lane];
       reinterpret_cast<uint32_t*>(map_slot[warp][1])[lane] = reinterpret_cast<const uint32_t*>(tmpl[b3d ? 3 : 1])[lane];
       __syncwarp();
-      if (lane == 0 && usable && k > 0) {
+      if (lane == 0 && usable && a_tma && k > 0) {
         if (a3d) tensormap_patch3(slot_a, a, static_cast<uint32_t>(m), static_cast<uint32_t>(k / ga.span),
                                   static_cast<uint64_t>(lda * ga.esz));
         else tensormap_patch(slot_a, a, static_cast<uint32_t>(k), static_cast<uint32_t>(m), static_cast<uint64_t>(lda * ga.esz));
       }
-      if (lane == 1 && usable && k > 0) {  // a second lane patches B's map at the same time
+      if (lane == 1 && usable && b_tma && k > 0) {  // a second lane patches B's map at the same time
         const uint64_t pitch = static_cast<uint64_t>(ldb * ga.esz);
         if (ga.b_k_contig) {  // stored [n, ldb]: K contiguous
           if (b3d) tensormap_patch3(slot_b, b, static_cast<uint32_t>(n), static_cast<uint32_t>(k / ga.span), pitch);

@@ -73,6 +73,18 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, ui
                "r"(bytes)
                : "memory");
 }
+// Credit `bytes` to the transaction count of a barrier (this CTA's, or another CTA's of the cluster through a
+// mapa address) without any asynchronous copy behind it: what a warp that filled a stage with ordinary loads
+// and stores does in place of the copy engine.  Relaxed; the caller orders its stores before it with
+// fence_proxy_async_all() + fence_acq_rel_cluster().
+__device__ __forceinline__ void mbar_complete_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.complete_tx.relaxed.cluster.shared::cluster.b64 [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+               : "memory");
+}
+// Orders this thread's generic-proxy accesses (st.shared) before later async-proxy accesses (tensor-core operand reads).
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <cstdio>
@@ -75,11 +76,27 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Integer environment switch (profiling sweeps and opt-in variants), `dflt` when unset or empty.
-static int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : dflt;
+// Integer environment switches (profiling sweeps and opt-in variants), `dflt` when unset or empty.  The
+// environment is read once per process and switch: every call site keeps what it read and looks again only
+// after fb_reload_env() (tests and sweeps that flip a switch in a running process call it).
+static std::atomic<unsigned> g_env_generation{1};
+struct EnvSlot {
+  std::atomic<unsigned> generation{0};
+  std::atomic<int> is_set{0};
+  std::atomic<int> value{0};
+};
+static int env_lookup(EnvSlot& slot, const char* name, int dflt) {
+  const unsigned now = g_env_generation.load(std::memory_order_acquire);
+  if (slot.generation.load(std::memory_order_acquire) != now) {
+    const char* v = getenv(name);
+    const bool set = v && *v;
+    slot.value.store(set ? atoi(v) : 0, std::memory_order_relaxed);
+    slot.is_set.store(set ? 1 : 0, std::memory_order_relaxed);
+    slot.generation.store(now, std::memory_order_release);
+  }
+  return slot.is_set.load(std::memory_order_relaxed) ? slot.value.load(std::memory_order_relaxed) : dflt;
 }
+#define env_int(name, dflt) ([&]() -> int { static EnvSlot slot_; return env_lookup(slot_, name, (dflt)); }())
 
 // L2 sector promotion of the tensor maps; FLAGBLAS_B200_L2PROMO = 0 (none), 1 (64 B), 2 (128 B), 3 (256 B,
 // the default) for profiling sweeps.
@@ -350,7 +367,11 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
     }
   }
   if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
+#ifdef FB_PROFILING_SWITCHES
   pp.debug = env_int("FLAGBLAS_B200_DEBUG_SKIP", 0);
+#else
+  pp.debug = 0;
+#endif
   const int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
   pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
   if (pp.stages < 1 || pp.stages > max_stages) pp.stages = max_stages;
@@ -1246,6 +1267,9 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   ga.allow3d = env_int("FLAGBLAS_B200_TMA3D", 1) != 0 ? 1 : 0;
   ga.b_k_contig = b_k_contig;
   ga.publish_each = env_int("FLAGBLAS_B200_GROUP_PUBLISH", 1);
+  // FLAGBLAS_B200_GROUP_BY_HAND=1: no tensor maps at all, every operand goes through the producers' load / store
+  // path that otherwise serves only operands TMA cannot address (tests and comparisons)
+  ga.force_by_hand = env_int("FLAGBLAS_B200_GROUP_BY_HAND", 0) != 0 ? 1 : 0;
   ga.esz = esz;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -1579,7 +1603,7 @@ const char* fb_status_string(int status) {
     case DEV_TIMEOUT_EPI_TMEM_FULL: return "device: epilogue timed out waiting for an accumulator";
     case DEV_TIMEOUT_TEST_FLAG: return "device: self-test wait timed out (expected)";
     case DEV_TIMEOUT_PEER: return "device: CTA-pair handshake timed out";
-    case DEV_GROUP_MISALIGNED: return "device: a group's A/B is not 16-byte aligned; group skipped";
+    case DEV_GROUP_MISALIGNED: return "device: a group's A / B address or pitch is not a multiple of the element size; group skipped";
     default: return "unknown status";
   }
 }
@@ -1596,6 +1620,13 @@ int fb_device_status(int reset) {
 }
 
 int fb_last_cuda_error(void) { return t_last_cuda_error; }
+
+#ifndef FB_BUILD_ID
+#define FB_BUILD_ID "unversioned"
+#endif
+const char* fb_build_id(void) { return FB_BUILD_ID; }
+
+void fb_reload_env(void) { g_env_generation.fetch_add(1, std::memory_order_acq_rel); }
 
 void fb_debug_set_profile_buffer(void* device_buffer_16_int64) {
   g_prof_buffer = static_cast<long long*>(device_buffer_16_int64);

@@ -163,8 +163,12 @@ size_t fb_gemv_fp8_workspace_bytes(int64_t m, int64_t n);
  *   (out_g and C_g share d_ldc, as in the reference).
  *   b_k_contiguous = 0: B_g stored [k_g, ldb>=n_g]  (group_bfgemm / group_hgemm)
  *   b_k_contiguous = 1: B_g stored [n_g, ldb>=k_g]  (group_tf32gemm)
- * A_g, B_g need 16-byte aligned base and row pitch; a group that violates
- * this is skipped and reported through fb_device_status().
+ * Any base address and any row pitch work, as in the reference (block pointers with
+ * boundary checks, src/flag_blas/ops/level3/group_gemm.py:162-185): an A_g / B_g whose base
+ * and pitch are 16-byte aligned is fetched by TMA, any other by the kernel's producer warps
+ * with ordinary loads (slower, same results).  Only an address or pitch that is not even a
+ * multiple of the element size is refused: that group is skipped and fb_device_status()
+ * reports 201 (the arrays live on the device, so the host cannot check them at the call).
  * Groups with m_g == 0 or n_g == 0 produce no work.
  *
  * Replaces group_bfgemm / group_hgemm / group_tf32gemm,
@@ -211,14 +215,23 @@ size_t fb_group_workspace_bytes(int group_count);
  *
  * Limits and rules:
  *   - at most fb_no_alloc_max_groups() (= 256) groups per call; more returns FB_ERR_TOO_LARGE;
- *   - the array costs about 160 KB of device memory on every GPU that loads the library, for
+ *   - the array costs about 185 KB of device memory on every GPU that loads the library, for
  *     the life of the process;
  *   - the first call on each device looks the array's address up (cudaGetSymbolAddress); make
- *     that first call before starting any stream capture on that device;
+ *     that first call before starting any stream capture on that device.  If it is also the
+ *     process's first use of this library on that device, the CUDA runtime loads the library's
+ *     module at that moment, which is when the array and the kernels are placed in device
+ *     memory: a service that hands all of HBM to its own pool must make this first call (a
+ *     group_count of 1 with m = 0 is enough) BEFORE it does so;
  *   - all calls share the one array per device: two calls whose GPU work can overlap (different
  *     streams, different threads) race on it -- order them on one stream or with events;
- *   - no cudaMalloc / cudaFree / allocating library routine is called, on any call.
- * Results are those of fb_group_gemm for the same arguments, bit for bit.
+ *   - the library itself calls no cudaMalloc / cudaFree / allocating library routine, on any call.
+ * Results: bit for bit those of fb_group_gemm called with a workspace of exactly the tables' size
+ * (the required part of fb_group_workspace_bytes; this entry point's array holds nothing else).
+ * A call of fb_group_gemm that also received the optional partial-sum scratch may split the k
+ * range of the tiles of a half-empty last wave between CTAs when k is long; it then adds the
+ * same products in another order, and the two results agree within fp32 summation rounding
+ * (well inside the operator's tolerance), not bit for bit.
  */
 int fb_group_gemm_no_alloc(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
                            const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
@@ -235,13 +248,20 @@ const char* fb_status_string(int status);
 
 /*
  * Device-side status word of the current device: 0, or the code left by a
- * kernel that gave up on a bounded wait (1xx) or skipped a misaligned group
- * (2xx).  Synchronises the device.  `reset` != 0 clears the word.
+ * kernel that gave up on a bounded wait (1xx) or skipped a group whose operand
+ * addresses are not element-aligned (2xx).  Synchronises the device.  `reset` != 0 clears the word.
  */
 int fb_device_status(int reset);
 
 /* cudaError_t (as int) of the last failed CUDA call made by this library on this thread. */
 int fb_last_cuda_error(void);
+
+/*
+ * The library's FLAGBLAS_B200_* environment switches (plan overrides for tests and profiling
+ * sweeps; INTEGRATION.md lists them) are read once per process.  A program that changes one
+ * with setenv() while running calls this to have every switch read again on its next use.
+ */
+void fb_reload_env(void);
 
 /*
  * Profiling aid: when set to a device buffer of 16 int64, CTA 0 of every tensor-core GEMM launched
@@ -251,6 +271,10 @@ int fb_last_cuda_error(void);
  * them there.  NULL (the default) switches the accounting off.  Not thread safe.
  */
 void fb_debug_set_profile_buffer(void* device_buffer_16_int64);
+
+/* Hash of the sources this binary was compiled from (set by the build recipe); the Python loader refuses a
+ * binary whose id differs from the sources next to it. */
+const char* fb_build_id(void);
 
 /* Number of SMs the persistent kernels size their grids with on the current device. */
 int fb_sm_count(void);

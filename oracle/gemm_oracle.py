@@ -153,14 +153,18 @@ def group_gemm(kind, a_list, b_list, c_list, alpha, beta, b_stored_nk=False, tf3
     return outs
 
 
-def group_mm(kind, A, B, offs):
-    """``C[o_{g-1}:o_g] = A[o_{g-1}:o_g] @ B[g]`` (group_gemm.py:614-686); rows past offs[-1] stay 0."""
+def group_mm(kind, A, B, offs, tf32_mode="trunc"):
+    """``C[o_{g-1}:o_g] = A[o_{g-1}:o_g] @ B[g]`` (group_gemm.py:614-686); rows past offs[-1] stay 0.
+    The reference's kernel forms the products in the storage precision (``tl.dot(..., allow_tf32=False)``,
+    ``group_gemm.py:656``): kinds "fp16" / "bf16" / "fp32" model that.  ``kind == "tf32"`` models what the CUDA
+    library does with fp32 tensors -- TF32 tensor-core products, operands truncated as in ``group_tf32gemm`` --
+    an extension the reference does not have."""
     M, N = A.shape[0], B.shape[2]
     C = np.zeros((M, N), dtype=np.float32)
     start = 0
     for g, end in enumerate(int(e) for e in offs):
         if end > start:
-            acc = A[start:end].astype(np.float64) @ B[g].astype(np.float64)
+            acc = _inputs(A[start:end], kind, tf32_mode) @ _inputs(B[g], kind, tf32_mode)
             C[start:end] = _epilogue(acc, 1.0, 0.0, None, kind)
         start = end
     return C

@@ -18,6 +18,7 @@ DEV = "cuda"
 def test_dense_plan_variants(env, kind, monkeypatch):
     for k, v in env.items():
         monkeypatch.setenv(k, v)
+        fb.reload_env()
     for ta, tb in ((0, 0), (0, 1), (1, 0), (1, 1)):
         m, n, k = 640, 896, 448
         A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=21)
@@ -51,6 +52,7 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
     outs = {}
     for sk in ("1", "0"):
         monkeypatch.setenv("FLAGBLAS_B200_STREAMK", sk)
+        fb.reload_env()
         Cd = C.to(DEV)
         op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
         torch.cuda.synchronize()
@@ -107,6 +109,7 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
                 monkeypatch.delenv(name, raising=False)
             else:
                 monkeypatch.setenv(name, val)
+        fb.reload_env()
         Cd = C.to(DEV) if beta != 0 else torch.full_like(C, float("nan")).to(DEV)
         op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, beta, Cd, ldc)
         torch.cuda.synchronize()
@@ -115,6 +118,7 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
     monkeypatch.setenv("FLAGBLAS_B200_CLUSTER_K", "0")
     monkeypatch.delenv("FLAGBLAS_B200_SPLITK", raising=False)
     monkeypatch.delenv("FLAGBLAS_B200_PAIR", raising=False)
+    fb.reload_env()
     need = fb.c_operators.gemm_workspace_bytes(fb._lib.FB_BF16, 0, 1, 16, 4096, 4096, 256, 4096, 512, 4096)
     assert need >= 2 * 16 * 4096 * 4          # without clusters the first shape's plan asks for scratch for >= 2 parts
 
@@ -131,6 +135,7 @@ def test_one_row_or_column_goes_through_gemv(kind, monkeypatch):
                 ref = oracle_dense(kind, ta, tb, m, n, k, 1.5, A, lda, B, ldb, 0.5, C, ldc)
                 for mode in ("1", "0"):
                     monkeypatch.setenv("FLAGBLAS_B200_GEMM_AS_GEMV", mode)
+                    fb.reload_env()
                     Cd = C.to(DEV)
                     op(ta, tb, m, n, k, 1.5, A.to(DEV), lda, B.to(DEV), ldb, 0.5, Cd, ldc)
                     torch.cuda.synchronize()

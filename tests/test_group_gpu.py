@@ -104,6 +104,7 @@ def test_grouped_tile_plan_variants(env, monkeypatch):
     single-CTA tiles, 2-D copies, one k-slab per stage) compute the same thing."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
+        fb.reload_env()
     _run_group("bf16", [5, 0, 70, 33, 300, 128, 129, 1, 700, 256], 512, 384, 1.5, 0.5, seed=11)
     _run_group("tf32", [40, 200, 64, 513], 200, 136, 1.5, 0.5, seed=12, var_nk=True)
 
@@ -116,8 +117,114 @@ def test_grouped_stream_k_tail(kind, monkeypatch):
     outs = {}
     for mode in ("1", "0"):
         monkeypatch.setenv("FLAGBLAS_B200_GROUP_STREAMK", mode)
+        fb.reload_env()
         outs[mode] = _run_group(kind, [300, 100, 0, 520, 77], 4096 if kind == "tf32" else 8192, 512, 1.5, 0.5, seed=21)
     assert_parity(outs["1"], outs["0"], KINDS[kind][2], 2.0, "grouped stream-k tail vs whole tiles")
+
+
+def _run_group_general(kind, specs, alpha, beta, seed=0):
+    """Grouped call in which every group has its own buffers, pitches and base offsets.
+    spec = (m, n, k, lda_pad, ldb_pad, a_off, b_off): pads in elements on top of the tight pitch, offsets = elements
+    by which the group's A / B start is shifted from its (256-byte aligned) allocation."""
+    dt = KINDS[kind][0]
+    nk = kind == "tf32"                      # group_tf32gemm stores B_g as [n, k]
+    g = torch.Generator().manual_seed(seed)
+    es = torch.empty(0, dtype=dt).element_size()
+    keep, ptr, size, host = [], {c: [] for c in "abco"}, {c: [] for c in ("m", "n", "k", "lda", "ldb", "ldc")}, []
+    for (m, n, k, lda_pad, ldb_pad, a_off, b_off) in specs:
+        lda, ldb, ldc = k + lda_pad, (k if nk else n) + ldb_pad, n + 3
+        A = torch.randn(m, lda, generator=g).to(dt)
+        B = (torch.randn(n if nk else k, ldb, generator=g) * max(k, 1) ** -0.5).to(dt)
+        C = torch.randn(m, ldc, generator=g).to(dt)
+        bufs = []
+        for t, off in ((A, a_off), (B, b_off), (C, 0), (torch.full_like(C, float("nan")), 0)):
+            flat = torch.zeros(t.numel() + off + 64, dtype=dt, device=DEV)
+            flat[off:off + t.numel()] = t.reshape(-1).to(DEV)
+            bufs.append((flat, off))
+        keep.append(bufs)
+        for c, (flat, off) in zip("abco", bufs):
+            ptr[c].append(flat.data_ptr() + off * es)
+        for name, v in zip(("m", "n", "k", "lda", "ldb", "ldc"), (m, n, k, lda, ldb, ldc)):
+            size[name].append(v)
+        host.append((A, B, C))
+    E = len(specs)
+    outd = keep[0][3][0]
+    getattr(fb, FN[kind])(outd, _i64(ptr["a"]), _i64(ptr["b"]), _i64(ptr["c"]), _i64(ptr["o"]), _i32(size["m"]), _i32(size["n"]),
+                          _i32(size["k"]), _i32(size["lda"]), _i32(size["ldb"]), _i32(size["ldc"]), E, sum(size["m"]),
+                          max(size["n"]), max(size["k"]), alpha, beta)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    for i, (m, n, k, *_rest) in enumerate(specs):
+        if m == 0 or n == 0:
+            continue
+        A, B, C = host[i]
+        a = A[:, :k].float().numpy()
+        b = (B[:, :k].t() if nk else B[:, :n]).float().numpy()
+        c = C[:, :n].float().numpy()
+        ref = go.group_gemm(kind, [a], [b], [c], alpha, beta, tf32_mode="trunc")[0]
+        flat, off = keep[i][3]
+        got = flat[off:off + m * (n + 3)].reshape(m, n + 3).float().cpu()
+        assert_parity(got[:, :n], torch.from_numpy(ref), KINDS[kind][2], abs(alpha) + abs(beta),
+                      "%s general group %d (m=%d n=%d k=%d)" % (kind, i, m, n, k))
+        assert torch.isnan(got[:, n:]).all(), "padding columns of the output were written"
+
+
+# (m, n, k, lda_pad, ldb_pad, a_off, b_off)
+_UNALIGNED_SPECS = [
+    (70, 136, 100, 0, 0, 0, 0),      # k = 100: 16-bit rows of A are only 8-byte aligned
+    (300, 200, 101, 0, 0, 0, 0),     # odd k: element-aligned rows of A (and of an [n, k] B)
+    (129, 256, 256, 0, 0, 1, 1),     # aligned pitches, both bases shifted by one element
+    (64, 128, 128, 0, 0, 0, 0),      # fully aligned group in the same call (stays on TMA)
+    (260, 130, 192, 0, 1, 0, 0),     # odd ldb
+    (0, 64, 64, 1, 1, 1, 1),         # empty group
+    (33, 72, 40, 3, 5, 2, 3),        # everything odd, k shorter than a stage
+    (513, 264, 520, 2, 0, 0, 0),     # several row tiles; A by hand, B by TMA
+]
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_unaligned_operands(kind):
+    """Groups whose A / B base or pitch is not 16-byte aligned (the reference takes any: block pointers with
+    boundary checks, ops/level3/group_gemm.py:162-185) are computed by the producers' load / store path, mixed in
+    one call with groups that stay on TMA."""
+    _run_group_general(kind, _UNALIGNED_SPECS, 1.5, 0.5, seed=31)
+    _run_group_general(kind, _UNALIGNED_SPECS[:3], 1.0, 0.0, seed=32)
+
+
+@pytest.mark.parametrize("env", [{}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"}])
+def test_grouped_by_hand_matches_tma(env, monkeypatch):
+    """Every operand through the load / store path (FLAGBLAS_B200_GROUP_BY_HAND=1), aligned or not, in each tile plan:
+    bit for bit what the TMA path gives."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("FLAGBLAS_B200_GROUP_BY_HAND", mode)
+        fb.reload_env()
+        outs[mode] = [_run_group("bf16", [5, 0, 70, 33, 300, 128, 129, 1, 700, 256], 512, 384, 1.5, 0.5, seed=11),
+                      _run_group("tf32", [40, 200, 64, 513], 200, 136, 1.5, 0.5, seed=12, var_nk=True),
+                      _run_group("fp16", [100, 260], 1024, 128, 1.0, 0.0, seed=13)]
+    for a, b in zip(outs["0"], outs["1"]):
+        assert torch.equal(torch.nan_to_num(a, nan=-7.0), torch.nan_to_num(b, nan=-7.0))
+
+
+def test_group_mm_unaligned_and_fp32(monkeypatch):
+    """group_mm with pitches TMA cannot address, including fp32 (TF32 products) with B stored [k, n]: the by-hand
+    producer then writes the 32-byte-atom swizzle of N-contiguous 32-bit operands."""
+    g = torch.Generator().manual_seed(41)
+    offs = torch.tensor([20, 20, 300, 433], dtype=torch.int32)
+    for dt, kind, K, N in ((torch.float32, "tf32", 102, 66), (torch.float32, "tf32", 128, 136), (torch.bfloat16, "bf16", 100, 129),
+                           (torch.float16, "fp16", 264, 320)):
+        A = torch.randn(433, K, generator=g).to(dt)
+        B = (torch.randn(4, K, N, generator=g) * K ** -0.5).to(dt)
+        ref = torch.from_numpy(go.group_mm(kind, A.float().numpy(), B.float().numpy(), offs.numpy()))
+        for mode in ("0", "1"):
+            monkeypatch.setenv("FLAGBLAS_B200_GROUP_BY_HAND", mode)
+            fb.reload_env()
+            C = fb.group_mm(A.to(DEV), B.to(DEV), offs.to(DEV))
+            torch.cuda.synchronize()
+            assert fb.device_status() == 0
+            assert_parity(C.float().cpu(), ref, KINDS[kind][2], 1.0, "group_mm %s K=%d N=%d by_hand=%s" % (kind, K, N, mode))
 
 
 def test_grouped_many_groups():

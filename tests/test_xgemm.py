@@ -222,6 +222,7 @@ def test_dgemm_tensor_path_and_cuda_core_path_agree(monkeypatch):
                 outs = []
                 for mma in ("1", "0"):
                     monkeypatch.setenv("FLAGBLAS_B200_DGEMM_MMA", mma)
+                    fb.reload_env()
                     Cd = C.to(DEV)
                     fb.dgemm(ta, tb, m, n, k, 2.5, A.to(DEV), lda, B.to(DEV), ldb, 0.5, Cd, ldc)
                     torch.cuda.synchronize()
@@ -251,6 +252,7 @@ def test_zgemm_tensor_path_and_cuda_core_path_agree(monkeypatch):
                 scale = abs(alpha) * k ** 0.5 * _rms(A) * _rms(B) + abs(beta) * _rms(C)
                 for mma in ("1", "0"):
                     monkeypatch.setenv("FLAGBLAS_B200_DGEMM_MMA", mma)
+                    fb.reload_env()
                     Cd = C.to(DEV)
                     fb.zgemm(ta, tb, m, n, k, alpha, A.to(DEV), lda, B.to(DEV), ldb, beta, Cd, ldc)
                     torch.cuda.synchronize()
