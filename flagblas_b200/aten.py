@@ -9,8 +9,8 @@ The functions take whatever strides ``torch`` hands them: a matrix that is row-m
 of a row-major matrix, is passed in place with ``trans = N / T`` and its pitch as the leading dimension;
 anything else is made contiguous first.  fp16 and bf16 run on the tensor cores with fp32 accumulation;
 fp32 runs the IEEE kernel unless ``torch.backends.cuda.matmul.allow_tf32`` is set, then the TF32 kernel.
-Other dtypes are not provided: leave them out with ``use_blas(exclude=...)`` / ``only_enable(include=...)``
-or keep such calls outside the ``with`` block.
+float64, complex64 and complex128 go to the library's ``dgemm`` / ``cgemm`` / ``zgemm`` kernels (``fb_gemm_ex``).
+Any other dtype raises ``NotImplementedError`` (torch's own CUDA ``mm`` has no integer or fp8 kernels either).
 """
 import warnings
 
@@ -31,7 +31,35 @@ def _code(dtype):
         return _lib.FB_BF16
     if dtype == torch.float32:
         return _lib.FB_TF32 if torch.backends.cuda.matmul.allow_tf32 else _lib.FB_F32
-    raise NotImplementedError("flag_blas aten overrides cover float16, bfloat16 and float32, not %s" % dtype)
+    raise NotImplementedError("flag_blas aten overrides cover float16, bfloat16, float32, float64, complex64 and "
+                              "complex128, not %s" % dtype)
+
+
+_EX_CODES = {torch.float64: _lib.FB_F64, torch.complex64: _lib.FB_C64, torch.complex128: _lib.FB_C128}
+
+
+def _parts(v):
+    v = complex(v.item() if isinstance(v, torch.Tensor) else v)
+    return float(v.real), float(v.imag)
+
+
+def _mm_into_ex(out, a, b, alpha, beta):
+    """float64 / complex: out[m, n] (contiguous) <- alpha * a @ b + beta * out through ``fb_gemm_ex``."""
+    m, k = a.shape
+    n = b.shape[1]
+    # a lazily conjugated view (x.mH, x.conj()) is materialised: the kernel sees plain memory
+    a, ta, lda = as_operand(a.resolve_conj())
+    b, tb, ldb = as_operand(b.resolve_conj())
+    ar, ai = _parts(alpha)
+    br, bi = _parts(beta)
+    stream, prev = _lib.enter(out.device)
+    try:
+        status = _cop.gemm_ex(_EX_CODES[out.dtype], ta, tb, m, n, k, ar, ai, a.data_ptr(), lda, b.data_ptr(), ldb, br, bi,
+                              out.data_ptr(), n, stream)
+    finally:
+        _lib.leave(prev)
+    _lib.check(status, "aten::mm")
+    return out
 
 
 def as_operand(t):
@@ -54,6 +82,8 @@ def _mm_into(out, a, b, alpha, beta):
         return out
     if k == 0:
         return out.zero_() if beta == 0 else out.mul_(beta)
+    if out.dtype in _EX_CODES:
+        return _mm_into_ex(out, a, b, alpha, beta)
     a, ta, lda = as_operand(a)
     b, tb, ldb = as_operand(b)
     _gemm._launch(_code(a.dtype), "aten::mm", ta, tb, m, n, k, float(alpha), a.data_ptr(), lda, b.data_ptr(), ldb,
@@ -104,7 +134,7 @@ def bmm(self, mat2):
     assert self.dtype == mat2.dtype
     batch, m, k = self.shape
     n = mat2.shape[2]
-    code = _code(self.dtype)
+    code = _lib.FB_F32 if self.dtype in _EX_CODES else _code(self.dtype)  # (double / complex: one GEMM per entry)
     esz = self.element_size()
     if (batch >= 3 and code != _lib.FB_F32 and m > 0 and n > 0 and k > 0 and (k * esz) % 16 == 0 and (n * esz) % 16 == 0):
         from .ops.level3.group_gemm import group_mm
@@ -141,6 +171,9 @@ def _mv_into(out, a, x, alpha, beta):
         return out
     if n == 0:
         return out.zero_() if beta == 0 else out.mul_(beta)
+    if out.dtype in _EX_CODES:
+        _mm_into_ex(out.view(m, 1), a, x.contiguous().view(n, 1), alpha, beta)
+        return out
     a, trans, lda = as_operand(a)
     if x.stride(0) < 1:
         x = x.contiguous()

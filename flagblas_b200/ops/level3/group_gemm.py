@@ -49,7 +49,8 @@ def group_bfgemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_siz
                  d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
     """bf16 grouped GEMM (reference: ops/level3/group_gemm.py:221-262).
 
-    ``use_small_m`` is accepted for compatibility; one kernel serves every m_g.
+    ``use_small_m`` is the caller's promise that no group has more than 64 rows (the reference routes such calls
+    to dedicated kernels, runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721); here it steers the tile plan.
     """
     return _group(_lib.FB_BF16, 0, "group_bfgemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
                   d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
@@ -116,7 +117,8 @@ def group_mm(A: torch.Tensor, B: torch.Tensor, offs: torch.Tensor) -> torch.Tens
 
 
 def group_gemm(group_A, group_B, group_C, offs_table, alpha=1.0, beta=0.0):
-    """``out_g = alpha * A_g @ B_g + beta * C_g`` over row segments (bf16 / fp16).
+    """``out_g = alpha * A_g @ B_g + beta * C_g`` over row segments (bf16 / fp16; fp32 tensors run with TF32
+    products, ``B_g`` stored ``[k, n]`` like the 16-bit types).
 
     ``offs_table[g] = [m_g, n, k, start_M, start_K, start_C]`` (a host list, as in
     the reference's ``tests/test_group_gemm.py:60-69``): ``A_g`` = ``m_g`` rows of
@@ -142,7 +144,6 @@ def group_gemm(group_A, group_B, group_C, offs_table, alpha=1.0, beta=0.0):
     sizes = torch.tensor(
         [[r[0] for r in rows], [r[1] for r in rows], [r[2] for r in rows],
          [lda] * G, [ldb] * G, [ldc] * G], dtype=torch.int32).to(dev)
-    fn = group_bfgemm if group_A.dtype == torch.bfloat16 else group_hgemm
-    fn(out, ptrs[0], ptrs[1], ptrs[2], ptrs[3], sizes[0], sizes[1], sizes[2], sizes[3], sizes[4], sizes[5], G,
-       sum(r[0] for r in rows), rows[0][1], rows[0][2], alpha, beta)
+    _group(_CODES[group_A.dtype], 0, "group_gemm", out, ptrs[0], ptrs[1], ptrs[2], ptrs[3], sizes[0], sizes[1], sizes[2],
+           sizes[3], sizes[4], sizes[5], G, sum(r[0] for r in rows), rows[0][1], rows[0][2], alpha, beta)
     return out

@@ -134,6 +134,63 @@ def trmm_cases(name):
         yield "%s_c%d" % (name, ci), (side, uplo, trans, diag, m, n, lda, ldb, ldc, alpha), A, B, C
 
 
+# ---------------------------------------------------------------- the benchmark workloads at full size
+# name: (kind, transa, transb, m, n, k, alpha, beta, seed); inputs as the benchmark states them.
+FULL_SIZE = {
+    "hgemm_8192_nn": ("fp16", 0, 0, 8192, 8192, 8192, 1.0, 0.0, 1),
+    "bfgemm_mlp_nt": ("bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 2),
+    "tf32gemm_16384_tn": ("tf32", 1, 0, 16384, 16384, 16384, 1.5, 0.5, 4),
+    "tf32gemm_skinny_tn": ("tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 4),
+}
+MOE = {"experts": 64, "k": 4096, "n": 1536, "tokens": 32768, "zipf": 1.2, "seed": 3}
+
+
+def full_size_dense(name):
+    """(kind, ta, tb, m, n, k, alpha, beta, A, B, C) of a full-size dense workload, CPU tensors in storage layout:
+    fp16 8192^3 with N(0,1)*0.05 operands; the bf16 MLP shape with A ~ N(0,1), B and C ~ N(0,0.02); the TF32 shapes
+    with U(-1,1) operands and C."""
+    kind, ta, tb, m, n, k, alpha, beta, seed = FULL_SIZE[name]
+    dt = DTYPES[kind]
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    a_shape, b_shape = ((k, m) if ta else (m, k)), ((n, k) if tb else (k, n))
+    if kind == "fp16":
+        A = (torch.randn(a_shape, generator=gen) * 0.05).to(dt)
+        B = (torch.randn(b_shape, generator=gen) * 0.05).to(dt)
+        C = torch.zeros(m, n, dtype=dt)
+    elif kind == "bf16":
+        A = torch.randn(a_shape, generator=gen).to(dt)
+        B = (torch.randn(b_shape, generator=gen) * 0.02).to(dt)
+        C = (torch.randn(m, n, generator=gen) * 0.02).to(dt)
+    else:
+        A = torch.rand(a_shape, generator=gen) * 2 - 1
+        B = torch.rand(b_shape, generator=gen) * 2 - 1
+        C = torch.rand(m, n, generator=gen) * 2 - 1
+    return kind, ta, tb, m, n, k, alpha, beta, A, B, C
+
+
+def sample_rows_cols(m, n, count=8):
+    """Rows and columns of a full-size result that the fixture keeps: both edges, tile seams and a spread."""
+    def pick(size):
+        want = [0, 127, 128, 256, size // 3 + 5, size // 2 + 3, (2 * size) // 3 + 7, size - 1]
+        return sorted({v for v in want if 0 <= v < size})[:count]
+    return pick(m), pick(n)
+
+
+def moe_case():
+    """(ms, K, N, A [tokens, K], B [E * K, N]) of the grouped MoE workload: token counts drawn from
+    Multinomial(tokens, Zipf(1.2) weights over the experts), zeros allowed; A ~ N(0,1), B ~ N(0,0.02), bf16."""
+    E, K, N, T = MOE["experts"], MOE["k"], MOE["n"], MOE["tokens"]
+    gen = torch.Generator(device="cpu").manual_seed(MOE["seed"])
+    w = torch.arange(1, E + 1, dtype=torch.float64) ** -MOE["zipf"]
+    ms = torch.multinomial(w / w.sum(), T, replacement=True, generator=gen).bincount(minlength=E).tolist()
+    A = torch.randn(T, K, generator=gen).bfloat16()
+    B = (torch.randn(E * K, N, generator=gen) * 0.02).bfloat16()
+    return ms, K, N, A, B
+
+
+MOE_COLS = [0, 255, 256, 1535]
+
+
 def pack(t):
     """Storage-exact numpy form: 16-bit types as their bit patterns, fp32 as is."""
     if t.dtype in (torch.bfloat16, torch.float16):

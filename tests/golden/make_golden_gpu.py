@@ -10,6 +10,7 @@ Needs an installed copy of the reference (it is not shipped with this repo), e.g
     FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py          # gpu_reference.npz
     FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py gemv     # gpu_reference_gemv.npz
     FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py xgemm    # gpu_reference_xgemm.npz
+    FLAGBLAS_REFERENCE_SITE=baseline/_ref python tests/golden/make_golden_gpu.py full_size  # gpu_reference_full_size.npz
 
 and a CUDA device.  The same import shims as ``make_golden.py`` apply (stub ``sqlalchemy``,
 ``BLAS_VENDOR`` / ``ARCH`` / ``FLAGGEMS_DB_URL``, pass-through ``libentry`` that launches every kernel
@@ -242,8 +243,76 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_full_size():
+    """``gpu_reference_full_size.npz``: samples (whole rows and whole columns) of what the reference's generic
+    kernels give on the benchmark workloads at full size: fp16 8192^3, the bf16 MLP shape with beta = 1, the 64-expert
+    MoE, and the two TF32 contractions (the reference has TF32 only in grouped form, so those run as a single group
+    of ``group_tf32gemm`` on operands laid out the way it wants them: A as [m, k], B as [n, k])."""
+    torch, ref = _import_reference()
+    sys.path.insert(0, HERE)
+    import gpu_cases as gc
+
+    dev = "cuda"
+    out = {"device": np.array(torch.cuda.get_device_name(0)), "triton": np.array(__import__("triton").__version__)}
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
+    for name in gc.FULL_SIZE:
+        kind, ta, tb, m, n, k, alpha, beta, A, B, C = gc.full_size_dense(name)
+        rows, cols = gc.sample_rows_cols(m, n)
+        Ad, Bd, Cd = A.to(dev), B.to(dev), C.to(dev)
+        if kind == "tf32":
+            Am = Ad.t().contiguous() if ta else Ad           # [m, k]
+            Bn = Bd if tb else Bd.t().contiguous()           # [n, k]
+            o = torch.empty_like(Cd)
+            ref["group_tf32gemm"](o, i64([Am.data_ptr()]), i64([Bn.data_ptr()]), i64([Cd.data_ptr()]), i64([o.data_ptr()]),
+                                  i32([m]), i32([n]), i32([k]), i32([k]), i32([k]), i32([n]), 1, m, n, k, alpha=alpha, beta=beta)
+            res = o
+        else:
+            if beta == 0.0:
+                Cd.fill_(float("nan"))
+            fn = ref["hgemm"] if kind == "fp16" else ref["bfgemm"]
+            fn(ta, tb, m, n, k, alpha, Ad, A.shape[1], Bd, B.shape[1], beta, Cd, n)
+            res = Cd
+        torch.cuda.synchronize()
+        out[name + "_rows"] = np.array(rows)
+        out[name + "_cols"] = np.array(cols)
+        out[name + "_row_vals"] = gc.pack(res[rows].cpu())
+        out[name + "_col_vals"] = gc.pack(res[:, cols].cpu())
+        out[name + "_probe"] = np.concatenate([A.float().numpy().ravel()[:8], B.float().numpy().ravel()[:8]])
+        print("full size", name, "done", flush=True)
+        del Ad, Bd, Cd, res
+
+    ms, K, N, A, B = gc.moe_case()
+    E = len(ms)
+    Ad, Bd = A.to(dev), B.to(dev)
+    o = torch.full((sum(ms), N), float("nan"), dtype=torch.bfloat16, device=dev)
+    ap, bp, op, s = [], [], [], 0
+    for g, mg in enumerate(ms):
+        ap.append(Ad.data_ptr() + s * K * 2); op.append(o.data_ptr() + s * N * 2); bp.append(Bd.data_ptr() + g * K * N * 2)
+        s += mg
+    ref["group_bfgemm"](o, i64(ap), i64(bp), i64(op), i64(op), i32(ms), i32([N] * E), i32([K] * E), i32([K] * E),
+                        i32([N] * E), i32([N] * E), E, sum(ms), N, K, alpha=1.0, beta=0.0)
+    torch.cuda.synchronize()
+    rows, s = [], 0
+    for mg in ms:            # first and last token of every expert
+        if mg:
+            rows += sorted({s, s + mg - 1})
+        s += mg
+    out["moe_ms"] = np.array(ms)
+    out["moe_rows"] = np.array(rows)
+    out["moe_row_vals"] = gc.pack(o[rows].cpu())
+    out["moe_col_vals"] = gc.pack(o[:, gc.MOE_COLS].cpu())
+    out["moe_probe"] = np.concatenate([A.float().numpy().ravel()[:8], B.float().numpy().ravel()[:8]])
+    print("full size moe done", flush=True)
+    path = os.path.join(HERE, "gpu_reference_full_size.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["gemv"]:
+    if sys.argv[1:] == ["full_size"]:
+        main_full_size()
+    elif sys.argv[1:] == ["gemv"]:
         main_gemv()
     elif sys.argv[1:] == ["xgemm"]:
         main_xgemm()

@@ -94,9 +94,37 @@ def test_use_blas_autograd_and_include():
         (a @ b).sum().backward()
     torch.testing.assert_close(a.grad, ga, rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(b.grad, gb, rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_use_blas_double_and_complex():
+    """After enable() / inside use_blas() every CUDA mm is overridden, so float64 and complex matrices must keep
+    working: they run on the library's dgemm / cgemm / zgemm kernels."""
+    dev = "cuda"
+    g = torch.Generator(device="cpu").manual_seed(5)
+    for dt, tol in ((torch.float64, 1e-12), (torch.complex64, 1e-5), (torch.complex128, 1e-12)):
+        a = torch.randn(70, 96, generator=g, dtype=dt).to(dev)
+        b = torch.randn(96, 40, generator=g, dtype=dt).to(dev)
+        c = torch.randn(70, 40, generator=g, dtype=dt).to(dev)
+        v = torch.randn(96, generator=g, dtype=dt).to(dev)
+        bt = torch.randn(40, 96, generator=g, dtype=dt).to(dev)
+        want = [a @ b, torch.addmm(c, a, b, beta=0.5, alpha=2.0), a @ bt.t(), torch.mv(a, v),
+                torch.bmm(torch.stack([a, a]), torch.stack([b, b]))]
+        if dt.is_complex:
+            want.append(a @ bt.mH)
+        with fb.use_blas():
+            got = [a @ b, torch.addmm(c, a, b, beta=0.5, alpha=2.0), a @ bt.t(), torch.mv(a, v),
+                   torch.bmm(torch.stack([a, a]), torch.stack([b, b]))]
+            if dt.is_complex:
+                got.append(a @ bt.mH)
+            torch.cuda.synchronize()
+        for w, gv in zip(want, got):
+            assert w.shape == gv.shape and w.dtype == gv.dtype
+            assert float((w - gv).abs().max()) <= tol * 96 ** 0.5 * 4, dt
     with fb.use_blas():
-        with pytest.raises(NotImplementedError):
-            torch.mm(a.double().detach(), b.double().detach())
+        with pytest.raises((NotImplementedError, RuntimeError)):
+            torch.mm(torch.ones(4, 4, device=dev, dtype=torch.int32), torch.ones(4, 4, device=dev, dtype=torch.int32))
+    assert fb.device_status() == 0
 
 
 @pytest.mark.gpu

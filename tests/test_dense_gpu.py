@@ -180,25 +180,34 @@ def _cublas(kind, ta, tb, A, B):
     return (opA.float() @ opB.float()) if kind != "fp32" else opA @ opB
 
 
-@pytest.mark.parametrize("cfg", ["C2_hgemm_8192", "C3_bfgemm_mlp", "C5_tf32_skinny", "C5_tf32_4096_TN"])
+@pytest.mark.parametrize("cfg", ["hgemm_8192_nn", "bfgemm_mlp_nt", "tf32gemm_skinny_tn", "tf32gemm_4096_tn", "tf32gemm_16384_tn"])
 def test_full_size_properties(cfg):
-    """At sizes the CPU oracle cannot finish: (1) a row/column sample against the fp64 oracle,
-    (2) linearity in alpha, (3) NaN-C is never read when beta == 0."""
+    """The benchmark workloads at full size, where the CPU oracle cannot finish: (1) whole rows and columns against
+    an fp64 product of the same (for TF32: truncated) operands, (2) exact linearity in alpha, (3) NaN-filled C is
+    never read when beta == 0, (4) the whole result against cuBLAS through torch, block of rows by block of rows."""
     torch.backends.cuda.matmul.allow_tf32 = False
-    if cfg == "C2_hgemm_8192":
-        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "fp16", 0, 0, 8192, 8192, 8192, 1.0, 0.0, 0.05, 0.05, 1
-    elif cfg == "C3_bfgemm_mlp":
-        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 1.0, 0.02, 2
-    elif cfg == "C5_tf32_skinny":
-        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "tf32", 1, 0, 64, 16384, 16384, 1.5, 0.5, 0.577, 0.577, 4
+    uniform = False     # operands N(0, 1) * s, or U(-1, 1)
+    if cfg == "hgemm_8192_nn":
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, sc0, seed = "fp16", 0, 0, 8192, 8192, 8192, 1.0, 0.0, 0.05, 0.05, 0.02, 1
+    elif cfg == "bfgemm_mlp_nt":
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, sc0, seed = "bf16", 0, 1, 16384, 14336, 4096, 1.0, 1.0, 1.0, 0.02, 0.02, 2
     else:
-        kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = "tf32", 1, 0, 4096, 4096, 4096, 1.5, 0.5, 0.577, 0.577, 4
+        mm = {"tf32gemm_skinny_tn": 64, "tf32gemm_4096_tn": 4096, "tf32gemm_16384_tn": 16384}[cfg]
+        nk = 4096 if cfg == "tf32gemm_4096_tn" else 16384
+        kind, ta, tb, m, n, k, alpha, beta, sa, sb, sc0, seed = "tf32", 1, 0, mm, nk, nk, 1.5, 0.5, 0.577, 0.577, 0.577, 4
+        uniform = True
     dt, opname, rtol = KINDS[kind]
     op = getattr(fb, opname)
     g = torch.Generator(device=DEV).manual_seed(seed)
-    A = (torch.randn((k, m) if ta else (m, k), generator=g, device=DEV) * sa).to(dt)
-    B = (torch.randn((n, k) if tb else (k, n), generator=g, device=DEV) * sb).to(dt)
-    C0 = (torch.randn(m, n, generator=g, device=DEV) * 0.02).to(dt)
+
+    def draw(shape, s):
+        if uniform:
+            return torch.rand(shape, generator=g, device=DEV) * 2 - 1
+        return (torch.randn(shape, generator=g, device=DEV) * s).to(dt)
+
+    A = draw((k, m) if ta else (m, k), sa)
+    B = draw((n, k) if tb else (k, n), sb)
+    C0 = draw((m, n), sc0)
     if beta == 0.0:
         C0.fill_(float("nan"))
     C = C0.clone()
@@ -206,34 +215,45 @@ def test_full_size_properties(cfg):
     torch.cuda.synchronize()
     assert fb.device_status() == 0
     assert not torch.isnan(C).any()
-    # (1) sampled rows and columns against fp64 on the host
+    # (1) sampled rows and columns against fp64 (formed on the GPU by cuBLAS's dgemm: a checker, not the product)
     rows = torch.tensor(sorted(r for r in {0, 1, 127, 128, m // 2 + 3, m - 1} if r < m), device=DEV)
     cols = torch.tensor(sorted(c for c in {0, 255, 256, n // 2 + 5, n - 1} if c < n), device=DEV)
-    opA = (A.t() if ta else A)
-    opB = (B.t() if tb else B)
-    if kind == "tf32":
-        trunc = lambda x: (x.view(torch.int32) & ~0x1FFF).view(torch.float32)  # noqa: E731
-        opA, opB = trunc(opA.contiguous()), trunc(opB.contiguous())
-    sc = abs(alpha) * (k ** 0.5) * sa * sb + abs(beta) * 0.02
-    ref_rows = alpha * (opA[rows].double().cpu() @ opB.double().cpu())
-    ref_cols = alpha * (opA.double().cpu() @ opB[:, cols].double().cpu())
+    trunc = (lambda x: (x.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)) if kind == "tf32" else (lambda x: x)
+    a_rows = trunc(A[:, rows].t() if ta else A[rows]).double()            # [rows, k]
+    b_cols = trunc(B[cols].t() if tb else B[:, cols]).double()            # [k, cols]
+    sc = abs(alpha) * (k ** 0.5) * sa * sb + abs(beta) * sc0
+    ref_rows = torch.empty(len(rows), n, dtype=torch.float64, device=DEV)
+    ref_cols = torch.empty(m, len(cols), dtype=torch.float64, device=DEV)
+    step = 2048
+    for j in range(0, n, step):      # operand blocks are widened to fp64 piece by piece
+        bj = trunc(B[j:j + step].t() if tb else B[:, j:j + step]).double()
+        ref_rows[:, j:j + step] = alpha * (a_rows @ bj)
+    for i in range(0, m, step):
+        ai = trunc(A[:, i:i + step].t() if ta else A[i:i + step]).double()
+        ref_cols[i:i + step] = alpha * (ai @ b_cols)
     if beta != 0.0:
-        ref_rows += beta * C0[rows].double().cpu()
-        ref_cols += beta * C0[:, cols].double().cpu()
-    assert_parity(C[rows].float().cpu(), ref_rows.float(), rtol, sc, cfg + " rows")
-    assert_parity(C[:, cols].float().cpu(), ref_cols.float(), rtol, sc, cfg + " cols")
+        ref_rows += beta * C0[rows].double()
+        ref_cols += beta * C0[:, cols].double()
+    assert_parity(C[rows].float().cpu(), ref_rows.float().cpu(), rtol, sc, cfg + " rows")
+    assert_parity(C[:, cols].float().cpu(), ref_cols.float().cpu(), rtol, sc, cfg + " cols")
+    del ref_rows, ref_cols, a_rows, b_cols
     # (2) linearity: doubling alpha (beta = 0) doubles the result -- exactly for normal numbers
     # (power-of-two scaling commutes with rounding); fp16 subnormals may differ by one step (2^-24)
     C1 = torch.empty_like(C)
-    C2 = torch.empty_like(C)
     op(ta, tb, m, n, k, 1.0, A, A.shape[1], B, B.shape[1], 0.0, C1, n)
-    op(ta, tb, m, n, k, 2.0, A, A.shape[1], B, B.shape[1], 0.0, C2, n)
-    assert float((C1.float() * 2.0 - C2.float()).abs().max()) <= (2.0 ** -23 if kind == "fp16" else 0.0)
-    # (3) independent cross-check of the whole result: cuBLAS through torch on the same data
-    if m * n <= 8192 * 8192:
-        refc = _cublas(kind, ta, tb, A, B)
-        d = (C1.float() - refc).abs().max().item()
-        assert d <= 2 * rtol * (k ** 0.5) * sa * sb + rtol * refc.abs().max().item(), d
+    op(ta, tb, m, n, k, 2.0, A, A.shape[1], B, B.shape[1], 0.0, C, n)
+    lin_tol = 2.0 ** -23 if kind == "fp16" else 0.0
+    for i in range(0, m, step):
+        assert float((C1[i:i + step].float() * 2.0 - C[i:i + step].float()).abs().max()) <= lin_tol
+    # (4) independent cross-check of the whole result: cuBLAS through torch on the same data, by row blocks
+    opB = (B.t() if tb else B)
+    opB = opB.float() if kind != "tf32" else opB
+    bound_abs = 2 * rtol * (k ** 0.5) * sa * sb
+    for i in range(0, m, step):
+        ai = (A[:, i:i + step].t() if ta else A[i:i + step])
+        refc = (ai.float() if kind != "tf32" else ai) @ opB
+        d = (C1[i:i + step].float() - refc).abs().max().item()
+        assert d <= bound_abs + rtol * refc.abs().max().item(), (cfg, i, d)
 
 
 @pytest.mark.parametrize("kind,ta,tb,beta", [("bf16", 0, 1, 0.5), ("fp16", 0, 0, 0.0), ("tf32", 1, 0, 0.5), ("fp32", 0, 0, 0.0)])

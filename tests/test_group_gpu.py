@@ -261,6 +261,26 @@ def test_group_mm_and_group_gemm():
         assert_parity(out.float().cpu(), torch.from_numpy(np.concatenate(refs, 0)), 1e-2, 2.0, "group_gemm " + kind)
 
 
+def test_group_gemm_fp32_runs_tf32():
+    """group_gemm on fp32 tensors: TF32 products with B_g stored [k, n] (not a 16-bit kernel over fp32 storage)."""
+    g = torch.Generator().manual_seed(9)
+    ms, K, N = [20, 0, 280, 132], 256, 320
+    A = torch.randn(sum(ms), K, generator=g)
+    B = torch.randn(4 * K, N, generator=g) / 16
+    Cin = torch.randn(sum(ms), N, generator=g)
+    table, s = [], 0
+    for i, mg in enumerate(ms):
+        table.append([mg, N, K, s, i * K, s])
+        s += mg
+    out = fb.group_gemm(A.to(DEV), B.to(DEV), Cin.to(DEV), table, alpha=1.5, beta=0.5)
+    a_list, c_list, s = [], [], 0
+    for mg in ms:
+        a_list.append(A[s:s + mg].numpy()); c_list.append(Cin[s:s + mg].numpy()); s += mg
+    refs = go.group_gemm("tf32", a_list, [B[i * K:(i + 1) * K].numpy() for i in range(4)], c_list, 1.5, 0.5)
+    assert_parity(out.float().cpu(), torch.from_numpy(np.concatenate(refs, 0)), 1e-3, 2.0, "group_gemm fp32")
+    assert fb.device_status() == 0
+
+
 def test_golden_grouped_on_gpu(golden_dir):
     z = np.load(os.path.join(golden_dir, "grouped.npz"))
     for name, kind in (("h", "fp16"), ("tf32", "tf32")):
