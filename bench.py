@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One JSON line on stdout (rank 0).  The headline workload is BASELINE config 2:
+One JSON line on stdout (rank 0).  The headline workload is the large square fp16 GEMM:
 ``hgemm`` fp16, M=N=K=8192, NN, alpha=1, beta=0, A,B ~ N(0,1)*0.05 (seed 1), fp32
 accumulate, fp16 output.  A "step" is one full GEMM.  With N > 1 GPUs the same GEMM is
 column-sharded (N-split) across the ranks, one process per GPU, with no collective on the
@@ -39,7 +39,7 @@ WORKLOADS = {
     "sgemm_512_nn": ("sgemm", "fp32", 0, 0, 512, 512, 512, 1.0, 0.0, 0.577, 0.577, 0),
     "sgemm_4096_nn": ("sgemm", "fp32", 0, 0, 4096, 4096, 4096, 1.0, 0.0, 0.577, 0.577, 0),
 }
-# BASELINE config 4: 64 experts sharing K and N, token counts ~ Multinomial(T, Zipf(1.2)), seed 3
+# grouped MoE workload: 64 experts sharing K and N, token counts ~ Multinomial(T, Zipf(1.2)), seed 3
 MOE = {"name": "group_bfgemm_moe64", "experts": 64, "k": 4096, "n": 1536, "tokens": 32768, "zipf": 1.2, "seed": 3}
 HEADLINE = "hgemm_8192_nn"
 
@@ -71,6 +71,14 @@ def measured_peak():
         return float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
     except (OSError, KeyError, ValueError):
         return FALLBACK_TENSOR_PEAK, "fallback"
+
+
+def measured(key, fallback):
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)[key]), "measured (MEASURED_PEAKS.json %s)" % key
+    except (OSError, KeyError, ValueError):
+        return fallback, "fallback"
 
 
 def ncu_traffic(workload):
@@ -159,14 +167,45 @@ def _time(fn, torch, steps=10, warmup=3):
     return e0.elapsed_time(e1) / steps
 
 
+def _time_cold(fn, torch, dev, steps=10, warmup=3):
+    """Mean time of single launches each of which finds L2 holding none of its operands: a buffer twice the size of
+    L2 is rewritten before every launch (outside the timed interval)."""
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(steps):
+        flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / steps
+
+
+def moe_setup(torch, dev, token_counts, K, N, seed):
+    """Device tensors and the operator's argument tuple for a grouped bf16 GEMM over stacked token rows."""
+    E, T = len(token_counts), sum(token_counts)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    A = torch.randn(T, K, generator=g, device=dev).bfloat16()
+    B = (torch.randn(E * K, N, generator=g, device=dev) * 0.02).bfloat16()
+    O = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+    ap, bp, op_, s = [], [], [], 0
+    for e, mg in enumerate(token_counts):
+        ap.append(A.data_ptr() + s * K * 2); bp.append(B.data_ptr() + e * K * N * 2); op_.append(O.data_ptr() + s * N * 2); s += mg
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    args = (O, i64(ap), i64(bp), i64(op_), i64(op_), i32(token_counts), i32([N] * E), i32([K] * E), i32([K] * E),
+            i32([N] * E), i32([N] * E), E, T, N, K, 1.0, 0.0)
+    return (A, B, O), args
+
+
 def other_configs(fb, torch, dev):
-    """Short device-resident timings of the remaining BASELINE configs (not the headline)."""
+    """Short device-resident timings of the other benchmark workloads (not the headline)."""
     peak, _ = measured_peak()
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            hbm = float(json.load(f)["hbm_gbs"])
-    except (OSError, KeyError, ValueError):
-        hbm = 6650.0
+    hbm, _ = measured("hbm_gbs", 6650.0)
     out = {}
     dts = {"fp16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32, "fp32": torch.float32}
     for name, (op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed) in WORKLOADS.items():
@@ -181,10 +220,25 @@ def other_configs(fb, torch, dev):
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         nbytes = A.element_size() * (m * k + k * n + m * n * (2 if beta != 0 else 1))
         rec = {"tflops": tf, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9}
-        if name in ("tf32gemm_skinny_tn", "bfgemm_decode64_nt"):
+        if name == "tf32gemm_skinny_tn":
             rec.update(bound="hbm", frac=rec["gbs"] / hbm, peak=hbm)
+        elif name == "bfgemm_decode64_nt":
+            # back to back its 32 MiB of weights stay in the 126 MB L2: the HBM roofline applies to launches that
+            # find L2 cold, timed one by one with L2 rewritten in between
+            cold = _time_cold(lambda: fn(ta, tb, m, n, k, alpha, A, A.shape[1], B, B.shape[1], beta, C, n), torch, dev)
+            rec.update(bound="latency (operands L2-resident between back-to-back launches)", ms_l2_cold=cold,
+                       gbs_l2_cold=nbytes / (cold * 1e-3) / 1e9, frac=nbytes / (cold * 1e-3) / 1e9 / hbm, peak=hbm,
+                       frac_is="HBM roofline of the L2-cold launches")
         elif kind == "tf32":
-            rec.update(bound="tensor", frac=tf / (peak / 2), peak=peak / 2)   # TF32 runs at half the 16-bit rate
+            # no measured TF32 figure exists: the denominator is assumed, half the measured 16-bit rate; cuBLAS's
+            # TF32 GEMM on the same operands is timed beside it as context
+            torch.backends.cuda.matmul.allow_tf32 = True
+            opA, opB = (A.t() if ta else A), (B.t() if tb else B)
+            cms = _time(lambda: torch.matmul(opA, opB), torch, steps=5)
+            torch.backends.cuda.matmul.allow_tf32 = False
+            rec.update(bound="tensor", frac=tf / (peak / 2), peak=peak / 2,
+                       peak_source="assumed: MEASURED_PEAKS.json bf16_tflops / 2 (no measured TF32 figure)",
+                       cublas_tf32_tflops=2.0 * m * n * k / (cms * 1e-3) / 1e12)
         elif kind == "fp32":
             ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12   # SMs x FP32 lanes x 2 FLOP x max SM clock
             rec.update(bound="fp32 FFMA" + (" (latency bound at this size)" if m <= 512 else ""), frac=tf / ffma_peak,
@@ -193,24 +247,25 @@ def other_configs(fb, torch, dev):
             rec.update(bound="tensor", frac=tf / peak, peak=peak)
         out[name] = rec
         del A, B, C
-    # grouped MoE config: 64 experts, K=4096, N=1536, Zipf(1.2) token counts, bf16
+    # grouped MoE workload: 64 experts, K=4096, N=1536, Zipf(1.2) token counts, bf16
     E, K, N, T = MOE["experts"], MOE["k"], MOE["n"], MOE["tokens"]
-    ms_ = moe_token_counts(torch)
-    g = torch.Generator(device=dev).manual_seed(3)
-    A = torch.randn(T, K, generator=g, device=dev).bfloat16()
-    B = (torch.randn(E * K, N, generator=g, device=dev) * 0.02).bfloat16()
-    O = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
-    ap, bp, op_, s = [], [], [], 0
-    for e, mg in enumerate(ms_):
-        ap.append(A.data_ptr() + s * K * 2); bp.append(B.data_ptr() + e * K * N * 2); op_.append(O.data_ptr() + s * N * 2); s += mg
-    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)  # noqa: E731
-    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
-    args = (O, i64(ap), i64(bp), i64(op_), i64(op_), i32(ms_), i32([N] * E), i32([K] * E), i32([K] * E), i32([N] * E),
-            i32([N] * E), E, T, N, K, 1.0, 0.0)
+    keep, args = moe_setup(torch, dev, moe_token_counts(torch), K, N, MOE["seed"])
     ms = _time(lambda: fb.group_bfgemm(*args), torch)
     tf = 2.0 * T * N * K / (ms * 1e-3) / 1e12
     out["group_bfgemm_moe64"] = {"tflops": tf, "ms": ms, "bound": "tensor", "frac": tf / peak, "peak": peak}
-    del A, B, O
+    del keep, args
+    # the same experts at decode time: at most 64 tokens each (the reference's small-M case).  Every expert's weights
+    # are read once for a handful of rows, so HBM bounds it; 805 MB of weights do not fit L2, no flush needed.
+    rnd = __import__("random").Random(MOE["seed"])
+    counts = [rnd.randint(1, 64) for _ in range(E)]
+    keep, args = moe_setup(torch, dev, counts, K, N, MOE["seed"])
+    ms = _time(lambda: fb.group_bfgemm(*args, use_small_m=True), torch)
+    Td = sum(counts)
+    nbytes = 2 * (Td * K + E * K * N + Td * N)
+    out["group_bfgemm_moe64_decode"] = {"tflops": 2.0 * Td * N * K / (ms * 1e-3) / 1e12, "ms": ms, "tokens": Td,
+                                        "gbs": nbytes / (ms * 1e-3) / 1e9, "bound": "hbm",
+                                        "frac": nbytes / (ms * 1e-3) / 1e9 / hbm, "peak": hbm}
+    del keep, args
     # matrix-vector products (the callers' decode-time shape): A read once, HBM bound
     for op, dt in (("bfgemv", torch.bfloat16), ("sgemv", torch.float32)):
         for trans in (0, 1):
@@ -234,7 +289,7 @@ def moe_token_counts(torch):
 
 
 def run_grouped(args, rank, world, local_rank):
-    """BASELINE config 4 as the benchmarked workload: ``group_bfgemm`` over 64 experts.  With N > 1 ranks
+    """The grouped MoE workload as the benchmarked one: ``group_bfgemm`` over 64 experts.  With N > 1 ranks
     the groups are dealt out by FLOPs (largest first, oversize groups cut into row slices); every rank
     holds the tokens and weights, runs its pieces, and nothing is exchanged."""
     import torch
@@ -423,6 +478,45 @@ def run_gemv(args, local_rank):
     emit(line)
 
 
+def dense_config(workload, world, gather=False):
+    """The ``config`` object of a dense workload's line: the same in this arm and in the reference arm."""
+    op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[workload]
+    esz = 4 if kind in ("tf32", "fp32") else 2
+    mib = (m * k + k * n + m * n) * esz / 2**20
+    return {"workload": workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb, "alpha": alpha,
+            "beta": beta, "accumulate": "f32",
+            "parallelism": "single GPU" if world == 1 else "N-split of C columns over %d GPUs, no collective%s" % (world, " + all-gather" if gather else ""),
+            "l2": "per-GPU inputs (%.0f MiB) %s L2; no flush between steps" % (mib, "larger than" if mib * 2**20 > 126e6 else "NOT larger than")}
+
+
+def moe_sharded(fb, fbdist, torch, dev, rank, world, timed):
+    """The grouped MoE workload on `world` ranks: groups dealt by FLOPs (row slices of oversize groups), every rank
+    holds tokens and weights, nothing is exchanged.  Whole-job TFLOP/s from the max-over-ranks time."""
+    E, K, N, T = MOE["experts"], MOE["k"], MOE["n"], MOE["tokens"]
+    ms_ = moe_token_counts(torch)
+    (A, B, O), _ = moe_setup(torch, dev, ms_, K, N, MOE["seed"])
+    starts = [sum(ms_[:e]) for e in range(E)]
+    a_ptrs = [A.data_ptr() + s * K * 2 for s in starts]
+    b_ptrs = [B.data_ptr() + e * K * N * 2 for e in range(E)]
+    o_ptrs = [O.data_ptr() + s * N * 2 for s in starts]
+    plan = fbdist.plan_group_shards(ms_, [N] * E, [K] * E, world, row_align=256)
+    arrays, pieces = fbdist.shard_group_arrays(plan[rank], a_ptrs, b_ptrs, o_ptrs, o_ptrs, ms_, [N] * E, [K] * E,
+                                               [K] * E, [N] * E, [N] * E, 2, dev)
+    rows_here = sum(r for _, _, r in plan[rank])
+
+    def step():
+        if pieces:
+            fb.group_bfgemm(O, *arrays, pieces, rows_here, N, K, 1.0, 0.0)
+
+    for _ in range(3):
+        step()
+    ms = timed(step, 10)
+    peak, _ = measured_peak()
+    tf = 2.0 * T * N * K / (ms * 1e-3) / 1e12
+    return {"tflops": tf, "ms": ms, "bound": "tensor", "frac": tf / world / peak, "peak": peak, "per_gpu": True,
+            "planned_imbalance": fbdist.plan_imbalance(plan, ms_, [N] * E, [K] * E)}
+
+
 def run_reference(args, rank, world):
     """Reference arm: the path on the host cores (torch.matmul fp32 over a bounded row sample)."""
     if rank != 0:
@@ -435,6 +529,10 @@ def run_reference(args, rank, world):
     if args.workload == MOE["name"]:
         WORKLOADS[MOE["name"]] = ("group_bfgemm", "bf16", 0, 0, MOE["tokens"], MOE["n"], MOE["k"], 1.0, 0.0, 1.0, 0.02, MOE["seed"])
 
+    # the same `config` object as this repo's arm prints for the workload
+    ref_config = (dense_config(args.workload, world, args.gather) if (args.workload in WORKLOADS and args.workload not in GEMV
+                                                                      and args.workload != MOE["name"])
+                  else {"workload": args.workload})
     op, kind, ta, tb, m, n, k, alpha, beta, sa, sb, seed = WORKLOADS[args.workload]
     per_step = max(0.5, min(20.0, 60.0 / max(1, args.steps + args.warmup)))  # the whole run stays near a minute
     vals, rows, threads = [], 0, 1
@@ -448,7 +546,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * 2.0 * rows * n * k / (tf * 1e12),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb},
+        "config": ref_config,
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -466,7 +564,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true", help="N>1: all-gather C over NCCL inside the timed step")
-    ap.add_argument("--no-other-configs", action="store_true", help="skip the brief runs of the other BASELINE configs")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the brief runs of the other workloads")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second back-to-back loop")
     args = ap.parse_args()
     claim_stdout()
 
@@ -505,83 +604,125 @@ def main():
     A = (torch.randn((k, m) if ta else (m, k), generator=g, device=dev) * sa).to(dt)
     B = (torch.randn((n, k) if tb else (k, n), generator=g, device=dev) * sb).to(dt)
     C = (torch.randn(m, n, generator=g, device=dev) * 0.02).to(dt) if beta != 0 else torch.full((m, n), float("nan"), device=dev, dtype=dt)
-    lda = A.shape[1]
+    lda, ldb, ldc = A.shape[1], B.shape[1], n
     n0, n1 = fbdist.column_ranges(n, world)[rank]
     nl = n1 - n0
-    if world > 1:
-        # Column-sharded layout: A replicated, every rank owns its columns of B and of C as local,
-        # densely pitched shards (what a tensor-parallel caller holds); nothing is exchanged.
-        B = (B[n0:n1] if tb else B[:, n0:n1]).contiguous()
-        C = C[:, n0:n1].contiguous()
-    ldb, ldc = B.shape[1], C.shape[1]
     opfn = getattr(fb, op)
-    gathered = torch.empty(world, m, max(nl, 1), dtype=dt, device=dev) if (use_dist and args.gather) else None
 
+    # Device-resident step.  N > 1: column-sharded in place -- every rank holds full-size A, B and C with their
+    # original leading dimensions and computes its column block of C (the shard of B / C is a strided view; nothing
+    # is copied or exchanged).  --gather adds the all-gather that completes C on every rank, overlapped by row blocks.
     def step():
-        if nl > 0:
-            opfn(ta, tb, m, nl, k, alpha, A, lda, B, ldb, beta, C, ldc)
-        if gathered is not None:
-            tdist.all_gather_into_tensor(gathered.view(world * m, -1), C)
+        if world == 1:
+            opfn(ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
+        elif args.gather:
+            fbdist.sharded_gemm_gather(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+        else:
+            fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
 
     def barrier():
         if use_dist:
             tdist.barrier()
         torch.cuda.synchronize()
 
+    def maxed(ms):
+        if use_dist:
+            t = torch.tensor([ms], device=dev)
+            tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def timed(fn, steps, sampler=None):
+        """ms per step of `steps` back-to-back calls, barrier + synchronize on both sides, max over ranks."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return maxed(e0.elapsed_time(e1)) / steps
+
     for _ in range(args.warmup):
         step()
     barrier()
     assert fb.device_status() == 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clk:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        barrier()
-    ms_total = e0.elapsed_time(e1)
-    if use_dist:
-        t = torch.tensor([ms_total], device=dev)
-        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+        ms_step = timed(step, args.steps)
     flops = 2.0 * m * n * k
     value = flops / (ms_step * 1e-3) / 1e12
     status = fb.device_status()
 
-    # ---- end to end: host buffers in, host buffer out, through the operator API
+    # ---- sustained: the same step back to back for at least two seconds (the clock sags under load), with the SM
+    # clock sampled over that window
+    sustained = None
+    if not args.no_sustained:
+        n_sus = max(args.steps, int(2200.0 / ms_step) + 1)
+        time.sleep(0.5)
+        with ClockSampler(local_rank, period=0.01) as sclk:
+            sus_ms = timed(step, n_sus)
+        sus_peak, sus_src = measured("bf16_tflops_sustained", 1400.0)
+        sus_val = flops / (sus_ms * 1e-3) / 1e12
+        sustained = {"value": sus_val, "unit": "TFLOP/s", "steps": n_sus, "seconds": sus_ms * n_sus * 1e-3,
+                     "ms_per_step": sus_ms, "clocks": sclk.summary(), "peak": sus_peak, "peak_source": sus_src,
+                     "frac": sus_val / world / sus_peak, "per_gpu": True}
+        time.sleep(0.5)
+
+    # ---- N > 1: what the optional all-gather of C costs, serial and overlapped by row blocks; and the same
+    # column block computed from densely pitched local shards of B and C (what a tensor-parallel caller holds)
+    gather = None
+    if use_dist and not args.gather:
+        try:
+            def serial():
+                fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+                fbdist.all_gather_columns(C, m, n, ldc, rank, world)
+
+            def overlapped():
+                fbdist.sharded_gemm_gather(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+
+            for fn in (serial, overlapped):
+                fn()
+            gather = {"ms_gemm_only": ms_step, "ms_gemm_then_all_gather": timed(serial, 5),
+                      "ms_all_gather_overlapped_by_row_blocks": timed(overlapped, 5),
+                      "bytes_per_rank": m * nl * A.element_size()}
+        except Exception as exc:  # the headline line must survive a failing side measurement
+            gather = {"error": repr(exc)[:200]}
+
+    # ---- end to end: host buffers in, host buffer out, through the library's host-memory entry.  N > 1: every rank
+    # owns the densely pitched column shards of B and C; of A it copies 1/N of every row block from the host and the
+    # ranks complete the block with an all-gather over NVLink.
     esz = A.element_size()
-    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
-    hC = torch.empty(C.shape, dtype=dt).pin_memory()
+    if world > 1:
+        Bl = (B[n0:n1] if tb else B[:, n0:n1]).contiguous()
+        Cl = C[:, n0:n1].contiguous()
+    else:
+        Bl, Cl = B, C
+    ldbl, ldcl = Bl.shape[1], Cl.shape[1]
+    hA, hB = A.cpu().pin_memory(), Bl.cpu().pin_memory()
+    hC = torch.empty(Cl.shape, dtype=dt).pin_memory()
 
     from flagblas_b200 import host as fbhost
 
     def e2e_step():
-        # the library's host-memory entry: copies in, kernels and copies out overlapped on streams
-        if nl > 0:
-            fbhost.gemm_from_host(op, ta, tb, m, nl, k, alpha, hA, lda, hB, ldb, beta, hC, ldc, A, B, C)
+        fbhost.gemm_from_host_sharded(op, ta, tb, m, nl, k, alpha, hA, lda, hB, ldbl, beta, hC, ldcl, A, Bl, Cl, rank, world)
         torch.cuda.synchronize()
 
     e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
-    if use_dist:
-        t = torch.tensor([e2e_ms], device=dev)
-        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    h2d = (A.numel() + B.numel() + (C.numel() if beta != 0 else 0)) * esz
-    d2h = C.numel() * esz
+    e2e_ms = timed(e2e_step, args.e2e_steps)
+    a_rows_from_host = (A.numel() // world) if (world > 1 and ta == 0 and m % world == 0) else A.numel()
+    h2d = world * a_rows_from_host * esz + (n * k + (m * n if beta != 0 else 0)) * esz   # whole job, all ranks
+    d2h = m * n * esz
 
-    # ---- the other BASELINE configs, briefly (single GPU only; informational)
+    # ---- the other workloads, briefly (informational)
     others = {}
-    if world == 1 and not args.no_other_configs:
-        others = other_configs(fb, torch, dev)
+    if not args.no_other_configs:
+        if world == 1:
+            others = other_configs(fb, torch, dev)
+        else:
+            try:
+                others = {MOE["name"]: moe_sharded(fb, fbdist, torch, dev, rank, world, timed)}
+            except Exception as exc:
+                others = {MOE["name"]: {"error": repr(exc)[:200]}}
 
     if rank == 0:
         peak, peak_src = measured_peak()
@@ -591,10 +732,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": {"fp16": "f16", "bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[kind],
             "data": "synthetic",
-            "config": {"workload": args.workload, "op": op, "m": m, "n": n, "k": k, "transa": ta, "transb": tb,
-                       "alpha": alpha, "beta": beta, "accumulate": "f32",
-                       "parallelism": "single GPU" if world == 1 else "N-split of C columns over %d GPUs, no collective%s" % (world, " + all-gather" if args.gather else ""),
-                       "l2": "per-GPU inputs (%.0f MiB) %s L2; no flush between steps" % ((A.numel() + B.numel() + C.numel()) * esz / 2**20, "larger than" if (A.numel() + B.numel() + C.numel()) * esz > 126e6 else "NOT larger than")},
+            "config": dense_config(args.workload, world, args.gather),
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                          "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
                          "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
@@ -605,6 +743,10 @@ def main():
             "clocks": clk.summary(),
             "device_status": status,
         }
+        if sustained is not None:
+            line["sustained"] = sustained
+        if gather is not None:
+            line["gather"] = gather
         if world == 1 and not args.no_cpu_baseline:
             from oracle import cpu_baseline
 

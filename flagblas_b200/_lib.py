@@ -71,6 +71,8 @@ def _load():
     handle.fb_group_mm.argtypes = [i32, i32, vp, i64, vp, i64, i64, vp, i64, vp, i32, i64, i64, vp, sz, vp]
     handle.fb_group_workspace_bytes.restype = sz
     handle.fb_group_workspace_bytes.argtypes = [i32]
+    handle.fb_group_min_workspace_bytes.restype = sz
+    handle.fb_group_min_workspace_bytes.argtypes = [i32]
     handle.fb_status_string.restype = c.c_char_p
     handle.fb_status_string.argtypes = [i32]
     handle.fb_device_status.restype = i32
@@ -107,6 +109,7 @@ EXPORTED_SYMBOLS = (
     "fb_group_gemm_no_alloc",
     "fb_no_alloc_max_groups",
     "fb_group_workspace_bytes",
+    "fb_group_min_workspace_bytes",
     "fb_status_string",
     "fb_device_status",
     "fb_last_cuda_error",

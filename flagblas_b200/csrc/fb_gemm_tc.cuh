@@ -85,6 +85,11 @@ struct GroupRec {
   // whose base or row pitch is not 16-byte aligned (TMA cannot address it).
   int a_fetch, b_fetch;
   int row_base;  // first row of the group this pass covers (rows before it belong to the other pass)
+  // > 0: the group's last row block is partial and is computed transposed by the CTA pair: the 256 columns of
+  // the tile sit in the MMA's M slot (B_g is its A operand, fetched exactly as for an ordinary tile), the block's
+  // rows, rounded up to this multiple of 16, in its N slot (each CTA fetches half of them), and the accumulator
+  // holds the tile transposed.  Tensor time and operand bytes then follow the rows that exist instead of 256.
+  int swap_rows;
   void* out;
   long long ldo;
   const void* cin;
@@ -111,17 +116,21 @@ struct TcGemmParams {
   int num_groups;
   const GroupRec* groups;
   const int* total_tiles;        // written by the table builder: [0] tile count, [1] some operand is fetched by hand
-  const CUtensorMap* group_maps;  // [2 * num_groups]: A_g, B_g
+  const CUtensorMap* group_maps;  // [3 * num_groups]: A_g, B_g, A_g boxed for the partial block
   // Stream-K tail (dense mode only).  When `sk_enabled`, every worker first takes `sk_dp` whole tiles
   // (tile = worker + i * workers); each of the `sk_rem` tiles left over (at most half as many as there are
   // workers) goes to `sk_group` neighbouring workers: the first ("owner") takes the head of the k range and
   // finishes the tile, each of the others takes `sk_share` stages, parks its fp32 partial accumulators in
   // `sk_partials` (one slot per worker) and raises `sk_flags[worker]`.  The owner's part is the longer one, by
   // about the time a contributor needs to park its sums, so that it does not have to wait for them.
+  // sk_enabled == 2: stream-K over the whole launch instead (see dense_work_item).
   int sk_enabled, sk_dp, sk_rem, sk_group, sk_share;
   // Grouped mode takes the same tail (`sk_grouped`): the tile count is only known on the device, so the workers
   // derive the split themselves; `sk_head` = the owner's head start in stages.
   int sk_grouped, sk_head;
+  // Grouped mode, CTA-pair tiles: compute every group's partial last row block transposed (GroupRec::swap_rows).
+  int swap_partial;
+  uint32_t idesc_swapped;  // instruction descriptor of such a block with N = 0 (the block's row count is added per tile)
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
@@ -142,6 +151,11 @@ struct TcGemmParams {
   // bit 0 = issue no MMA, bit 1 = issue no TMA copy, bit 2 = store nothing.
   int debug;
   int stages;  // pipeline stages actually used (<= the compiled maximum)
+  // 512-wide tiles: 1 = this CTA's B stage is ONE copy of 256 consecutive columns of the tile (CTA r of the pair owns
+  // tile columns [256 r, 256 r + 256); the MMA half h reads rows [128 h, +128) of it, so accumulator column
+  // 256 h + 128 q + c holds tile column 256 q + 128 h + c); 0 = two copies of 128 columns, one per MMA half
+  // (accumulator columns in tile order).  One copy instruction less per stage.
+  int wide_merged;
   // Optional cycle accounting (profiling builds of a call): 16 counters written by CTA 0, or null.
   long long* prof;
 };
@@ -242,7 +256,7 @@ constexpr int kEpiStageBytes = 32 * 128;
 template <class T, int BLOCK_N, class HandBack>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* stage, const Problem& pr, int row0,
                                                      int col_base, float alpha, float beta, int lane, bool zero_acc,
-                                                     HandBack hand_back) {
+                                                     HandBack hand_back, bool wide_merged = false) {
   constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
   constexpr int kLoads = kW / 32;
   constexpr int kSteps = BLOCK_N / kW;
@@ -253,7 +267,9 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
   const bool with_c = beta != 0.f;
 #pragma unroll 1
   for (int s = 0; s < kSteps; ++s) {
-    const int col0 = col_base + s * kW;
+    int acc_col = s * kW;  // accumulator column of this step -> column of the tile
+    if (BLOCK_N == 512 && wide_merged) acc_col = ((acc_col >> 7) & 1) * 256 + (acc_col >> 8) * 128 + (acc_col & 127);
+    const int col0 = col_base + acc_col;
     const bool fast = pr.vec_ok && col0 + kW <= pr.n;
     if (fast && with_c) {
       // the C rows of this step, whole row segments per instruction, into the staging block
@@ -458,6 +474,37 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
     return it.tile < tiles;
   }
+  if (p.sk_enabled == 2) {
+    // Stream-K over the whole launch (few waves, the last one more than half full): the tiles' k stages form one
+    // line of tiles x stages units that is cut into `workers` equal ranges.  A range that starts inside a tile
+    // begins with that tile's tail (a partial, parked for the worker before it, which holds the tile's first
+    // stages and finishes it); then come whole tiles; a range that ends inside a tile ends with that tile's head,
+    // whose worker owns the tile and adds the parts of the workers after it -- parts that were the first thing
+    // those workers did, so they are parked long before the owner's epilogue asks for them.
+    const long long line = static_cast<long long>(tiles) * stages;
+    long long lo = worker * line / workers;
+    const long long hi = (worker + 1) * line / workers;
+    for (int i = 0;; ++i) {
+      if (lo >= hi) return false;
+      const long long t = lo / stages;
+      const int sb = static_cast<int>(lo - t * stages);
+      const int se = static_cast<int>(min(static_cast<long long>(stages), sb + (hi - lo)));
+      if (i == idx) {
+        it.tile = static_cast<int>(t);
+        it.sb = sb; it.se = se;
+        it.kind = sb > 0 ? ITEM_PARTIAL : (se == stages ? ITEM_FULL : ITEM_OWNER);
+        if (it.kind == ITEM_OWNER) {
+          // workers worker + 1 .. v hold the rest of the tile: v = the one whose range contains its last stage
+          const long long last = (t + 1) * stages - 1;
+          int v = worker + 1;
+          while ((v + 1) * line / workers <= last) ++v;
+          it.part = v - worker + 1;  // workers that share the tile
+        }
+        return true;
+      }
+      lo += se - sb;
+    }
+  }
   if (idx < p.sk_dp) {
     it.tile = worker + idx * workers;
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
@@ -502,9 +549,10 @@ __device__ __forceinline__ bool grouped_tile(const TcGemmParams& p, int worker, 
 
 // Stage range and kind of a grouped work item whose tile has `stages` k-stages.  A tail tile too short to be worth
 // splitting is done whole by its owner; false tells a contributor that it has nothing to do.
-__device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it) {
+__device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it,
+                                              bool never_split = false) {
   it.part = 0;
-  const int share = sharers > 1 ? (stages - p.sk_head) / sharers : 0;
+  const int share = (sharers > 1 && !never_split) ? (stages - p.sk_head) / sharers : 0;
   if (role < 0 || share < 2) {
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
     return role <= 0;
@@ -749,6 +797,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const CUtensorMap* map = load_a ? &tmA : &tmB;
         uint32_t use3d = og.use3d;
         int row_base = 0;
+        int swap_half = 0;             // > 0: a transposed partial block; rows of A_g each CTA of the pair fetches
         int fetch = kFetch2d;          // grouped: how this group's operand is fetched
         const void* raw = nullptr;     // hand-filled operand: base, pitch and extent along M / N
         long long raw_ld = 0;
@@ -760,10 +809,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tm = lt / gr.tiles_n;
           tn = lt - tm * gr.tiles_n;
           kk_total = gr.k;
-          map = &p.group_maps[2 * g + (load_a ? 0 : 1)];
+          map = &p.group_maps[3 * g + (load_a ? 0 : 1)];
           fetch = load_a ? gr.a_fetch : gr.b_fetch;
           use3d = fetch == kFetch3d;
           row_base = gr.row_base;
+          if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) {
+            // partial last row block, computed transposed: B_g is fetched as ever; of A_g each CTA fetches its half
+            // of the block's rows through the group's third map (or by hand)
+            swap_half = gr.swap_rows >> 1;
+            if (load_a) map = &p.group_maps[3 * g + 2];
+          }
           if (fetch > kFetch3d) {
             raw = load_a ? gr.a : gr.b;
             raw_ld = load_a ? gr.lda : gr.ldb;
@@ -776,11 +831,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           kk_total = p.k;
         }
         // first row (A) / first column (B) of the operand slab this CTA fetches
-        const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM
-                               : tn * BLOCK_N + static_cast<int>(cta_rank) * (Cfg::kBRows / Cfg::kHalves);
+        const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * (swap_half ? swap_half : kBlockM)
+                               : tn * BLOCK_N + static_cast<int>(cta_rank) * (p.wide_merged ? Cfg::kBRows : Cfg::kBRows / Cfg::kHalves);
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        if (grouped && !grouped_range(p, k_blocks, role, sharers, item)) break;
+        if (grouped && !grouped_range(p, k_blocks, role, sharers, item, swap_half != 0)) break;
         const int kb_begin = item.sb, kb_end = item.se;
+        // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
+        const uint32_t a_slab_bytes = swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : Cfg::kABytes;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (by_hand) {
@@ -791,7 +848,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int k0 = kb * static_cast<int>(p.block_k);
           const uint32_t a_stage_bytes = p.ks * Cfg::kABytes, b_stage_bytes = p.ks * Cfg::kBBytes;
           uint8_t* dst = load_a ? smem_a + stage * a_stage_bytes : smem_b + stage * b_stage_bytes;
-          const uint32_t slab_bytes = load_a ? Cfg::kABytes : Cfg::kBBytes;
+          const uint32_t slab_bytes = load_a ? a_slab_bytes : Cfg::kBBytes;
           uint32_t bar = smem_u32(&full_bar[stage]);
           if constexpr (PAIR) bar = mapa_shared(bar, 0);  // both CTAs' copies are credited to the leader's barrier
           if (load_a && cta_rank == 0 && lane == 0) {
@@ -799,18 +856,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (p.debug & 2) mbar_arrive(&full_bar[stage]);
             else
 #endif
-            mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (a_stage_bytes + b_stage_bytes));
+            mbar_arrive_expect_tx(&full_bar[stage], (PAIR ? 2u : 1u) * (p.ks * a_slab_bytes + b_stage_bytes));
           }
           if (fetch > kFetch3d) {
             // no tensor map for this operand: the whole warp fills the stage
             fill_stage_dispatch<kTf32 ? 4 : 2>(fetch, dst, bar, static_cast<int>(og.mn_major), static_cast<int>(p.ks),
-                                               load_a ? kBlockM : Cfg::kBRows, raw, raw_ld, mn0, mn_limit, k0, kk_total);
+                                               load_a ? (swap_half ? swap_half : kBlockM) : Cfg::kBRows, raw, raw_ld, mn0,
+                                               mn_limit, k0, kk_total);
           } else if (lane == 0 FB_AND_COPIES_ON(p)) {
             if (use3d) {
               // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row.
               // A 512-wide tile's B stage is two halves, each laid out like a 256-wide tile's B stage
               // (this CTA's 128 columns of tile columns [256 h, 256 h + 256)), fetched by one copy each.
-              const int halves = load_a ? 1 : Cfg::kHalves;
+              const int halves = (load_a || p.wide_merged) ? 1 : Cfg::kHalves;
               for (int h = 0; h < halves; ++h) {
                 const int mn = mn0 + h * Cfg::kMmaN;
                 const int y = og.mn_major ? k0 : mn;
@@ -871,7 +929,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // j = (slab, k-step, half): both halves of a k-step follow each other and share the A operand
         const int half = j % kH, step = (j / kH) & 3, slab = j / (4 * kH);
         off_a[j] = (slab * p.a.slab_adv_bytes + step * p.a.k_adv_bytes) >> 4;
-        off_b[j] = (half * p.ks * Cfg::kHalfBBytes + slab * p.b.slab_adv_bytes + step * p.b.k_adv_bytes) >> 4;
+        // the second half of a 512-wide tile: a block of its own behind the first half's slabs, or (merged copy of a
+        // K-major operand) the next 128 rows of every slab
+        const uint32_t half_off = (p.wide_merged && !p.b.mn_major) ? Cfg::kHalfBBytes : p.ks * Cfg::kHalfBBytes;
+        off_b[j] = (half * half_off + slab * p.b.slab_adv_bytes + step * p.b.k_adv_bytes) >> 4;
       }
       const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a), p.a.lbo, p.a.sbo, p.a.layout);
       const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b), p.b.lbo, p.b.sbo, p.b.layout);
@@ -891,10 +952,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!dense_work_item(p, worker, num_workers, dense_stages, idx, item)) break;
           t = item.tile;
         }
+        // A transposed partial block (GroupRec::swap_rows): the MMA's A operand is the B stage, its B operand the
+        // A stage (`swap_half` rows per CTA, so its slabs lie closer together), and N is the block's row count.
+        int swap_half = 0;
+        uint32_t idesc = p.idesc;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
-          const int stages_g = (p.groups[g].k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-          if (!grouped_range(p, stages_g, role, sharers, item)) break;
+          const GroupRec& gr = p.groups[g];
+          const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+          if (PAIR && p.swap_partial && gr.swap_rows > 0 && (t - gr.tile_start) / gr.tiles_n == gr.m / Cfg::kTileM) {
+            swap_half = gr.swap_rows >> 1;
+            idesc = p.idesc_swapped | (static_cast<uint32_t>(gr.swap_rows >> 3) << 17);
+          }
+          if (!grouped_range(p, stages_g, role, sharers, item, swap_half != 0)) break;
         }
         const int k_blocks = item.se - item.sb;  // stages of this work item
         // PAIR: the peer's epilogue warps arrive remotely -> cluster-scope acquire
@@ -926,8 +996,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (FB_MMA_ON(p)) {
                 const uint32_t accum = (kb | (j / kH)) != 0 ? 1u : 0u;  // first k-step of the tile overwrites
                 const uint32_t d_half = d_tmem + static_cast<uint32_t>((j % kH) * Cfg::kMmaN);
-                if constexpr (PAIR) umma_pair<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
-                else umma<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], p.idesc, accum);
+                if constexpr (PAIR) {
+                  uint64_t da = a_desc + off_a[j], db = b_desc + off_b[j];
+                  if (kH == 1 && swap_half) {
+                    // slab j / 4 of the A stage starts swap_half rows of 128 bytes after the previous one
+                    da = b_desc + off_b[j];
+                    db = a_desc + static_cast<uint32_t>((j >> 2) * swap_half * (kSwizzleBytes >> 4)) + ((p.a.k_adv_bytes >> 4) * (j & 3));
+                  }
+                  umma_pair<kTf32>(d_half, da, db, idesc, accum);
+                } else {
+                  umma<kTf32>(d_half, a_desc + off_a[j], b_desc + off_b[j], idesc, accum);
+                }
               }
               if (j == n_mma - 2) {
                 // Slot before the last MMA: everything the next stage needs, so that its first MMA
@@ -991,6 +1070,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int row_base = 0;
       Problem pr;
       bool k_is_zero = false;  // a group with k == 0 contributes beta * C only
+      int swap_rows = 0;       // > 0: the accumulator holds a partial row block transposed (lanes = columns of the tile)
       if (grouped) {
         while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
         const GroupRec& gr = p.groups[g];
@@ -1002,7 +1082,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         k_is_zero = gr.k == 0;
         row_base = gr.row_base;
         const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        if (!grouped_range(p, stages_g, role, sharers, item)) break;
+        if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) swap_rows = gr.swap_rows;
+        if (!grouped_range(p, stages_g, role, sharers, item, swap_rows != 0)) break;
       } else {
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         pr = p.prob;
@@ -1028,6 +1109,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
       int sk_last = worker;
       if (item.kind == ITEM_OWNER) {
+        if (!grouped && p.sk_enabled == 2) sharers = item.part;
         sk_last = worker + sharers - 1;
         // wait (bounded) until every contributor has parked its partial sums
         uint32_t good = 1;
@@ -1053,6 +1135,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!good) ok = false;  // still drain TMEM below so that the MMA issuer is not left waiting
       }
       if (item.kind == ITEM_CLUSTER) break;  // the accumulator is complete; the whole CTA finishes the tile below
+      if constexpr (PAIR) if (swap_rows) {
+        // Transposed partial block: TMEM lane = column of the tile (this CTA's 128 of its 256), TMEM column = row of
+        // the block.  A thread holds 32 consecutive rows of one output column; for each of them the warp's 32 lanes
+        // write 32 neighbouring elements of one output row.
+        using T = OutT;
+        const int col = tn * BLOCK_N + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
+        const int block_row0 = row_base + tm * Cfg::kTileM;
+        const int rows_here = min(swap_rows, pr.m - block_row0);
+        const int chunks = (rows_here + 31) >> 5;
+        T* ocol = reinterpret_cast<T*>(pr.out) + col;
+        const T* ccol = reinterpret_cast<const T*>(pr.cin) + col;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_lane + static_cast<uint32_t>(c * 32), r);
+          tmem_ld_wait();
+          if (c == chunks - 1) {
+            // every row of this accumulator that exists is in registers: hand TMEM back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+          }
+          if (FB_STORES_ON(p) && ok && col < pr.n) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int lr = c * 32 + j;
+              if (lr < rows_here) {
+                const size_t row = static_cast<size_t>(block_row0 + lr);
+                float v = k_is_zero ? 0.f : p.alpha * __uint_as_float(r[j]);
+                if (p.beta != 0.f) v += p.beta * to_f32(ccol[row * pr.ldcin]);
+                ocol[row * pr.ldo] = from_f32<T>(v);
+              }
+            }
+          }
+        }
+        if (chunks == 0) {  // (cannot happen: a swapped block has at least one row) keep the barrier protocol whole
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+        }
+        if (p.prof) prof_ebody += clock64() - e1;
+        if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
+        continue;
+      }
       if (item.kind == ITEM_FULL || item.kind == ITEM_SPLIT) {
         // the usual case: this warp's 32 rows leave through its staging block as whole row segments
         uint8_t* stage = ctl + Cfg::kCtlBytes + (warp - kEpiWarp0) * kEpiStageBytes;
@@ -1073,7 +1199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
           epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back);
         } else if (FB_STORES_ON(p) && ok) {
-          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back);
+          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
+                                              p.wide_merged != 0);
         } else {
           hand_back();
         }

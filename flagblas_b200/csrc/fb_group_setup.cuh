@@ -32,10 +32,12 @@ struct GroupPass {
                   // rows (`leading` = 1) or the rows after them (`leading` = 0)
   int leading;
   int keep_over;  // > 0: a trailing remainder of more than `keep_over` rows stays with the leading pass
+  int swap_partial;  // 1 (CTA-pair tiles covering every row): a group's last, partial 256-row block is computed
+                     // transposed (see GroupRec::swap_rows); a third tensor map per group fetches its rows
   int block_n;
   GroupRec* recs;       // [num_groups]
   int* total_tiles;     // device: [0] = tile count of the pass, [1] = 1 when some operand has no tensor map
-  CUtensorMap* maps;    // [2 * num_groups]: A_g, B_g
+  CUtensorMap* maps;    // [3 * num_groups]: A_g, B_g, and A_g with the box of the partial block's rows
   CUtensorMap tmpl_a, tmpl_b, tmpl_a3, tmpl_b3;  // templates: 2-D A, 2-D B, 3-D A, 3-D B
 };
 
@@ -99,6 +101,11 @@ __device__ __forceinline__ void tensormap_patch3(uint32_t smem_map, const void* 
 
 // Whole-warp: copy the 128-byte map from shared to global memory (plain stores; tensormap_release_all()
 // orders them towards the tensormap proxy afterwards).
+// Rows per box (dimension 1 of both the 2-D and the 3-D view of a K-contiguous operand).
+__device__ __forceinline__ void tensormap_patch_box_rows(uint32_t smem_map, uint32_t rows) {
+  asm volatile("tensormap.replace.tile.box_dim.shared::cta.b1024.b32 [%0], 1, %1;" ::"r"(smem_map), "r"(rows) : "memory");
+}
+
 __device__ __forceinline__ void tensormap_store(CUtensorMap* gdst, const uint8_t* smem_map, int lane) {
   reinterpret_cast<uint32_t*>(gdst)[lane] = reinterpret_cast<const uint32_t*>(smem_map)[lane];
 }
@@ -191,7 +198,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
 __global__ void __launch_bounds__(kSetupThreads)
 group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constant__ GroupPass pass1,
                    const GroupSetupArgs ga) {
-  __shared__ __align__(128) uint8_t map_slot[kSetupThreads / 32][2][128];  // per warp: A and B map under construction
+  __shared__ __align__(128) uint8_t map_slot[kSetupThreads / 32][3][128];  // per warp: A, B and partial-block A map under construction
   __shared__ __align__(128) uint8_t tmpl[4][128];                           // 2-D A, 2-D B, 3-D A, 3-D B of the pass
   __shared__ int counts[kSetupSmemGroups];
   __shared__ int warp_tot[32];
@@ -248,8 +255,13 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
         else { row_base = lead; rows = m - lead; }
       }
 
+      // the last row block of the group, when it is not a whole one, runs transposed with its row count (rounded up
+      // to the MMA's granularity of 16) in the instruction's N slot
+      const int part_rows = ps.swap_partial ? static_cast<int>(m % ps.tile_m) : 0;
+      const int swap_rows = (part_rows + 15) / 16 * 16;
       if (lane == 0) {
         GroupRec r;
+        r.swap_rows = swap_rows;
         r.m = static_cast<int>(m); r.n = static_cast<int>(n); r.k = static_cast<int>(k);
         r.tiles_n = static_cast<int>((n + ps.block_n - 1) / ps.block_n);
         // tile_start temporarily holds this group's tile count
@@ -287,12 +299,20 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
         }
       }
       __syncwarp();
+      // third map: A_g again, with a box of the rows one CTA of the pair fetches of the partial block
+      const uint32_t slot_r = smem_u32(map_slot[warp][2]);
+      reinterpret_cast<uint32_t*>(map_slot[warp][2])[lane] = reinterpret_cast<const uint32_t*>(map_slot[warp][0])[lane];
+      __syncwarp();
+      if (lane == 0 && swap_rows > 0 && usable && a_tma && k > 0) tensormap_patch_box_rows(slot_r, static_cast<uint32_t>(swap_rows / 2));
+      __syncwarp();
       if (ga.publish_each) {
-        tensormap_publish(&ps.maps[2 * g], slot_a);
-        tensormap_publish(&ps.maps[2 * g + 1], slot_b);
+        tensormap_publish(&ps.maps[3 * g], slot_a);
+        tensormap_publish(&ps.maps[3 * g + 1], slot_b);
+        tensormap_publish(&ps.maps[3 * g + 2], slot_r);
       } else {
-        tensormap_store(&ps.maps[2 * g], map_slot[warp][0], lane);
-        tensormap_store(&ps.maps[2 * g + 1], map_slot[warp][1], lane);
+        tensormap_store(&ps.maps[3 * g], map_slot[warp][0], lane);
+        tensormap_store(&ps.maps[3 * g + 1], map_slot[warp][1], lane);
+        tensormap_store(&ps.maps[3 * g + 2], map_slot[warp][2], lane);
       }
     }
     if (!ga.publish_each) tensormap_release_all();

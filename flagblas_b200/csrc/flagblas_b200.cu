@@ -364,6 +364,13 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
       pp.sk_group = static_cast<int>(group);
       pp.sk_share = static_cast<int>(share);
       FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
+    } else if (rem > 0 && 2 * rem > workers && dp >= 1 && dp <= 2 && stages >= 16 && BLOCK_N <= 256 &&
+               env_int("FLAGBLAS_B200_STREAMK_FULL", 1) != 0) {
+      // Two or three waves of which the last is more than half full (one rank's share of a GEMM sharded over eight
+      // GPUs: 128 tiles on 74 CTA pairs): whole tiles would leave (workers - rem) workers idle for a whole tile time.
+      // All k stages of all tiles are dealt evenly instead (FLAGBLAS_B200_STREAMK_FULL=0: whole tiles).
+      pp.sk_enabled = 2;
+      FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     }
   }
   if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
@@ -675,6 +682,10 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const long long dp = pl.tiles / split_workers, rem = pl.tiles - dp * split_workers;
   pl.want_streamk = rem > 0 && dp < 9 && 2 * rem <= split_workers && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
                     stages >= env_int("FLAGBLAS_B200_SK_MIN_STAGES", 32) && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
+  // ... or stream-K over the whole launch: two or three waves, the last more than half full (see launch_tc)
+  if (rem > 0 && 2 * rem > split_workers && dp >= 1 && dp <= 2 && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
+      pl.block_n <= 256 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 && env_int("FLAGBLAS_B200_STREAMK_FULL", 1) != 0)
+    pl.want_streamk = true;
   return pl;
 }
 
@@ -1109,8 +1120,11 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     wide = t512 >= 4 * pairs && e512 >= e256 - 0.02 && n % 512 == 0;
   }
   if (pair && a3d && b3d && (wide || env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512)) block_n = 512;
-  const int halves = block_n > 256 ? 2 : 1;
-  const int b_rows = (pair ? block_n / 2 : block_n) / halves;  // rows of B per copy (per column half of the tile)
+  // 512-wide tiles fetch this CTA's 256 columns of B with one copy (FLAGBLAS_B200_WIDE_MERGED=0: one copy of 128
+  // columns per MMA half, the accumulator then holds the tile's columns in order)
+  const bool wide_merged = block_n > 256 && env_int("FLAGBLAS_B200_WIDE_MERGED", 1) != 0;
+  const int halves = (block_n > 256 && !wide_merged) ? 2 : 1;
+  const int b_rows = (pair ? block_n / 2 : block_n) / halves;  // rows of B per copy
 
   CUtensorMap ma, mb;
   const bool atom32 = esz == 4;  // MN-major fp32 operands use the 32-byte-atom swizzle
@@ -1159,6 +1173,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
+  p.wide_merged = wide_merged ? 1 : 0;
   p.wait_prior = packed ? 1 : 0;
   // Optional stream-K scratch behind the packed operands: used only when the caller provided it.
   if (dplan.want_streamk && block_n <= 256 && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
@@ -1228,13 +1243,17 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
 
 // Workspace of one pass: records, the tile count, tensor maps.
 static constexpr size_t group_pass_bytes(size_t groups) {
-  return (sizeof(GroupRec) * groups + 255) / 256 * 256 + 256 + sizeof(CUtensorMap) * 2 * groups;
+  return (sizeof(GroupRec) * groups + 255) / 256 * 256 + 256 + sizeof(CUtensorMap) * 3 * groups;
 }
 static constexpr size_t group_ws_bytes(size_t groups) { return 2 * group_pass_bytes(groups); }
 
 // Behind the two passes' tables: flags and partial-sum slots of the stream-K tail (optional: a caller that passes
 // only the tables' bytes gets whole tiles).
 static size_t group_tail_offset(size_t groups) { return round_up(group_ws_bytes(groups), 256); }
+
+size_t fb_group_min_workspace_bytes(int group_count) {
+  return group_count <= 0 ? 0 : group_ws_bytes(static_cast<size_t>(group_count));
+}
 
 size_t fb_group_workspace_bytes(int group_count) {
   if (group_count <= 0) return 0;
@@ -1284,8 +1303,12 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     ps.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ps.total_tiles) + 256);
     ps.block_n = block_n;
   }
+  // One pass of CTA-pair tiles: every whole 256-row block of a group is an ordinary tile, its last, partial block is
+  // computed transposed with its row count in the MMA's N slot (FLAGBLAS_B200_GROUP_SWAP=0: an ordinary, padded tile).
+  const bool swap_partial = pair && !split && block_n == 256 && env_int("FLAGBLAS_B200_GROUP_SWAP", 1) != 0;
   if (pair) {
     pass[0].enabled = 1; pass[0].tile_m = 2 * kBlockM; pass_pair[0] = true;
+    pass[0].swap_partial = swap_partial ? 1 : 0;
     pass_ks[0] = env_int("FLAGBLAS_B200_KS", 2) == 1 ? 1 : 2;
     if (split) {
       pass[0].rows_mod = 2 * kBlockM; pass[0].leading = 1;
@@ -1350,6 +1373,8 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.a = make_geom(esz, kBlockM, false, ks, false);
     p.b = make_geom(esz, b_rows, !b_k_contig, ks, false);
     p.num_groups = G;
+    p.swap_partial = ps.swap_partial;
+    p.idesc_swapped = make_idesc(idesc_fmt(dtype), b_k_contig ? 0 : 1, 0, block_n, 0);  // M slot = the tile's columns
     p.groups = ps.recs;
     p.total_tiles = ps.total_tiles;
     p.group_maps = ps.maps;

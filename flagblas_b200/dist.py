@@ -92,6 +92,45 @@ def all_gather_columns(C_local: torch.Tensor, m: int, n: int, ldc: int, rank: in
             c2d[:, s:e].copy_(gathered[r, :, : e - s])
 
 
+_gather_streams = {}
+
+
+def sharded_gemm_gather(name: str, transa: int, transb: int, m: int, n: int, k: int, alpha, A: torch.Tensor, lda: int,
+                        B: torch.Tensor, ldb: int, beta, C: torch.Tensor, ldc: int, rank: int, world: int,
+                        align: int = 256, chunks: int = 4, group=None) -> None:
+    """:func:`sharded_gemm` followed by :func:`all_gather_columns`, overlapped: the GEMM runs in row blocks of
+    ``A`` / ``C`` on the current stream and every finished block is exchanged on a side stream while the next one
+    computes, so only the last block's exchange is exposed.  ``A``, ``B``, ``C`` are full-size operands with their
+    original leading dimensions (the rank's shard of ``C`` is a strided column block of the full ``C``); afterwards
+    every rank holds the complete ``C``.  Needs ``transa = N`` to cut row blocks; other layouts run the two phases
+    one after the other."""
+    if world == 1 or transa != CUBLAS_OP_N or chunks <= 1 or m < 2 * chunks:
+        sharded_gemm(name, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world, align)
+        if world > 1:
+            all_gather_columns(C, m, n, ldc, rank, world, align, group)
+        return
+    dev = C.device
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _gather_streams:
+        _gather_streams[key] = torch.cuda.Stream(device=dev)
+    side = _gather_streams[key]
+    cur = torch.cuda.current_stream(dev)
+    side.wait_stream(cur)
+    a2 = A.view(-1)[: m * lda].view(m, lda)
+    c2 = C.view(-1)[: m * ldc].view(m, ldc)
+    step = -(-m // chunks)
+    step = -(-step // 256) * 256  # whole 256-row tiles per block
+    for r0 in range(0, m, step):
+        r1 = min(m, r0 + step)
+        sharded_gemm(name, transa, transb, r1 - r0, n, k, alpha, a2[r0:r1], lda, B, ldb, beta, c2[r0:r1], ldc, rank, world,
+                     align)
+        done = cur.record_event()
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            all_gather_columns(c2[r0:r1], r1 - r0, n, ldc, rank, world, align, group)
+    cur.wait_stream(side)
+
+
 def plan_group_shards(m_sizes: Sequence[int], n_sizes: Sequence[int], k_sizes: Sequence[int], world: int,
                       row_align: int = 128) -> List[List[Tuple[int, int, int]]]:
     """FLOP-balanced assignment of grouped-GEMM work to ranks.

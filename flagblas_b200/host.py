@@ -76,3 +76,63 @@ def gemm_from_host(name, transa, transb, m, n, k, alpha, hA, lda, hB, ldb, beta,
     cur.wait_stream(s_out)
     cur.wait_stream(s_in)
     cur.wait_stream(s_run)
+
+
+def gemm_from_host_sharded(name, transa, transb, m, n_local, k, alpha, hA, lda, hB, ldb, beta, hC, ldc, dA, dB, dC, rank,
+                           world, group=None, chunks=8):
+    """:func:`gemm_from_host` for one process per GPU with the columns of ``C`` (and of ``B``) sharded over ``world``
+    ranks: ``hB, hC, dB, dC`` are this rank's column shard (``n_local`` columns, densely pitched), ``hA`` / ``dA`` the
+    whole ``A``, which every rank needs.
+
+    Copying all of ``A`` from the host on every rank would move ``world`` times its size over the host's links each
+    step.  Instead every rank copies a ``1 / world`` slice of each row block of ``A`` from its host memory and the ranks
+    complete the block with one NCCL all-gather over NVLink (in place: a rank's slice is already where the gathered
+    block wants it); the GEMM of a block starts when its gather is done, copies out overlap as in the unsharded form.
+    Collective: every rank of ``group`` must make the call with the same ``m, k, chunks``.
+    """
+    import torch.distributed as tdist
+
+    if world == 1:
+        return gemm_from_host(name, transa, transb, m, n_local, k, alpha, hA, lda, hB, ldb, beta, hC, ldc, dA, dB, dC, chunks)
+    op = getattr(ops, name)
+    cur = torch.cuda.current_stream(dA.device)
+    step = -(-m // max(chunks, 1))
+    step = -(-step // (256 * world)) * (256 * world)  # whole tiles per block, whole rows per rank
+    if transa != CUBLAS_OP_N or lda != k or m % world != 0 or step > m:
+        # no contiguous row blocks to deal out: every rank fetches what it needs itself
+        if n_local > 0:
+            gemm_from_host(name, transa, transb, m, n_local, k, alpha, hA, lda, hB, ldb, beta, hC, ldc, dA, dB, dC, chunks)
+        return
+    s_in, s_run, s_out = _get_streams(dA.device)
+    for s in (s_in, s_run, s_out):
+        s.wait_stream(cur)
+    a2, ha2 = dA.view(-1)[: m * lda].view(m, lda), hA.view(-1)[: m * lda].view(m, lda)
+    if n_local > 0:
+        c2, hc2 = dC.view(-1)[: m * ldc].view(m, ldc), hC.view(-1)[: m * ldc].view(m, ldc)
+        with torch.cuda.stream(s_in):
+            dB.copy_(hB, non_blocking=True)
+    for r0 in range(0, m, step):
+        r1 = min(m, r0 + step)
+        rows = r1 - r0
+        with torch.cuda.stream(s_in):
+            if rows % world == 0:
+                sub = rows // world
+                mine = a2[r0 + rank * sub: r0 + (rank + 1) * sub]
+                mine.copy_(ha2[r0 + rank * sub: r0 + (rank + 1) * sub], non_blocking=True)
+                tdist.all_gather_into_tensor(a2[r0:r1], mine, group=group)
+            else:
+                a2[r0:r1].copy_(ha2[r0:r1], non_blocking=True)
+            if beta != 0 and n_local > 0:
+                c2[r0:r1].copy_(hc2[r0:r1], non_blocking=True)
+            ready = s_in.record_event()
+        if n_local > 0:
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ready)
+                op(transa, transb, rows, n_local, k, alpha, a2[r0:r1], lda, dB, ldb, beta, c2[r0:r1], ldc)
+                done = s_run.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                hc2[r0:r1].copy_(c2[r0:r1], non_blocking=True)
+    cur.wait_stream(s_out)
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_run)

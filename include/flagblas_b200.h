@@ -203,6 +203,9 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
  * partial-sum slots of the stream-K tail (optional: with only the tables' bytes the call runs whole tiles). */
 size_t fb_group_workspace_bytes(int group_count);
 
+/* The required part alone: tile tables and tensor maps.  A grouped call given exactly this much runs every tile whole. */
+size_t fb_group_min_workspace_bytes(int group_count);
+
 /*
  * fb_group_gemm without a workspace argument, for callers that are not allowed to allocate
  * device memory at all.  (This entry point has no counterpart in the reference.)

@@ -63,3 +63,30 @@ def assert_parity(got, ref, rtol, scale, what=""):
                              "max diff %g" % (what, int(bad.sum()), bad.numel(), i, float(got.reshape(-1)[i]),
                                               float(ref.reshape(-1)[i]), float(bound.reshape(-1)[i]),
                                               float(diff[~nan_r].max())))
+
+
+def check_samples_fp64(kind, ta, tb, m, n, k, alpha, beta, A, B, C0, C, scale, what, dev="cuda"):
+    """Whole rows and whole columns of a device-resident result ``C`` against an fp64 product of the same operands
+    (TF32: with the 13 low mantissa bits of the operands dropped, as the tensor core does), formed on the GPU block
+    by block so that sizes the numpy oracle cannot finish stay cheap.  ``A``, ``B`` in storage layout, ``C0`` = C
+    before the call (ignored when ``beta == 0``)."""
+    rtol = KINDS[kind][2]
+    rows = torch.tensor(sorted(r for r in {0, 1, 127, 128, 255, 256, m // 2 + 3, m - 2, m - 1} if 0 <= r < m), device=dev)
+    cols = torch.tensor(sorted(c for c in {0, 1, 255, 256, 511, 512, n // 2 + 5, n - 2, n - 1} if 0 <= c < n), device=dev)
+    trunc = (lambda x: (x.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)) if kind == "tf32" else (lambda x: x)
+    a_rows = trunc(A[:, rows].t() if ta else A[rows]).double()            # [rows, k]
+    b_cols = trunc(B[cols].t() if tb else B[:, cols]).double()            # [k, cols]
+    ref_rows = torch.empty(len(rows), n, dtype=torch.float64, device=dev)
+    ref_cols = torch.empty(m, len(cols), dtype=torch.float64, device=dev)
+    step = 2048
+    for j in range(0, n, step):
+        bj = trunc(B[j:j + step].t() if tb else B[:, j:j + step]).double()
+        ref_rows[:, j:j + step] = alpha * (a_rows @ bj)
+    for i in range(0, m, step):
+        ai = trunc(A[:, i:i + step].t() if ta else A[i:i + step]).double()
+        ref_cols[i:i + step] = alpha * (ai @ b_cols)
+    if beta != 0.0:
+        ref_rows += beta * C0[rows, :n].double()
+        ref_cols += beta * C0[:, cols].double()
+    assert_parity(C[rows, :n].float().cpu(), ref_rows.float().cpu(), rtol, scale, what + " rows")
+    assert_parity(C[:, cols].float().cpu(), ref_cols.float().cpu(), rtol, scale, what + " cols")

@@ -41,6 +41,11 @@ def test_dense_plan_variants(env, kind, monkeypatch):
     ("fp16", 0, 0, 2560, 4096, 4096),    # 2 whole waves + 12 tail tiles, four workers per tail tile
     ("tf32", 1, 0, 4096, 4096, 2048),    # the same tail in TF32
     ("bf16", 1, 1, 4000, 4000, 4160),    # ragged edge tiles, last k stage half full
+    ("fp16", 0, 0, 8192, 1024, 8192),    # 128 tiles on 74 CTA pairs (one rank's share of 8192^3 over eight GPUs):
+                                         # 1.73 waves -> stream-K over the whole launch
+    ("bf16", 0, 1, 2048, 4096, 2048),    # the same tile count, short k (16 stages), K-contiguous B
+    ("tf32", 1, 0, 2304, 4096, 4096),    # 144 tiles: 1.95 waves, ranges that end a few stages into a tile
+    ("bf16", 0, 0, 5000, 2500, 4096),    # 200 tiles = 2.7 waves with ragged edge tiles
 ])
 def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
     """The stream-K tail (FLAGBLAS_B200_STREAMK=0 switches it off): when the last wave of tiles is at most half

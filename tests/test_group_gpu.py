@@ -22,7 +22,7 @@ def _i32(v):
     return torch.tensor(v, dtype=torch.int32, device=DEV)
 
 
-def _run_group(kind, ms, K, N, alpha, beta, seed=0, var_nk=False):
+def _run_group(kind, ms, K, N, alpha, beta, seed=0, var_nk=False, use_small_m=False):
     """Mirror of the reference tests' set-up (tests/test_group_bfgemm.py:99-160): one A buffer of
     stacked rows, per-group B, raw device pointer / size arrays."""
     dt = KINDS[kind][0]
@@ -47,7 +47,7 @@ def _run_group(kind, ms, K, N, alpha, beta, seed=0, var_nk=False):
         s += mg
     ldb = [ks[i] if nk else ns[i] for i in range(E)]
     ret = getattr(fb, FN[kind])(outd, _i64(ap), _i64(bp), _i64(cp), _i64(op), _i32(ms), _i32(ns), _i32(ks), _i32([K] * E),
-                                _i32(ldb), _i32([N] * E), E, sum(ms), N, K, alpha, beta)
+                                _i32(ldb), _i32([N] * E), E, sum(ms), N, K, alpha, beta, use_small_m=use_small_m)
     assert ret is outd
     torch.cuda.synchronize()
     assert fb.device_status() == 0
@@ -98,7 +98,8 @@ def test_grouped_alpha_zero_and_beta_zero(kind):
 
 @pytest.mark.parametrize("env", [{"FLAGBLAS_B200_GROUP_SPLIT": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"}, {"FLAGBLAS_B200_PAIR": "0"},
                                  {"FLAGBLAS_B200_TMA3D": "0"},
-                                 {"FLAGBLAS_B200_KS": "1"}])
+                                 {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SWAP": "0"},
+                                 {"FLAGBLAS_B200_GROUP_SWAP": "0", "FLAGBLAS_B200_KS": "1"}])
 def test_grouped_tile_plan_variants(env, monkeypatch):
     """The alternative tile plans (two-pass split of every remainder or only of remainders up to 128 rows,
     single-CTA tiles, 2-D copies, one k-slab per stage) compute the same thing."""
@@ -191,7 +192,8 @@ def test_grouped_unaligned_operands(kind):
     _run_group_general(kind, _UNALIGNED_SPECS[:3], 1.0, 0.0, seed=32)
 
 
-@pytest.mark.parametrize("env", [{}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"}])
+@pytest.mark.parametrize("env", [{}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"},
+                                 {"FLAGBLAS_B200_GROUP_SWAP": "0"}])
 def test_grouped_by_hand_matches_tma(env, monkeypatch):
     """Every operand through the load / store path (FLAGBLAS_B200_GROUP_BY_HAND=1), aligned or not, in each tile plan:
     bit for bit what the TMA path gives."""
@@ -225,6 +227,25 @@ def test_group_mm_unaligned_and_fp32(monkeypatch):
             torch.cuda.synchronize()
             assert fb.device_status() == 0
             assert_parity(C.float().cpu(), ref, KINDS[kind][2], 1.0, "group_mm %s K=%d N=%d by_hand=%s" % (kind, K, N, mode))
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_partial_blocks_every_row_count(kind):
+    """A group's last, partial 256-row block is computed transposed with its row count (rounded up to 16) in the
+    MMA's N slot: every residue class of the row count, alone and behind whole blocks, ragged n and k."""
+    ms = [1, 15, 16, 17, 31, 32, 33, 64, 100, 127, 128, 129, 200, 240, 241, 255, 256, 257, 256 + 16, 512 + 250, 0, 3 * 256]
+    _run_group(kind, ms, 256, 520, 1.5, 0.5, seed=51)
+    _run_group(kind, ms[:12], 200, 136, 1.0, 0.0, seed=52, var_nk=True)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "tf32"])
+def test_grouped_decode_shape_small_m(kind):
+    """The reference's small-M case (every m_g <= 64, use_small_m=True routes to its dedicated kernels,
+    runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721): here every tile is a transposed partial block."""
+    import random
+    rnd = random.Random(7)
+    ms = [rnd.randint(0, 64) for _ in range(64)]
+    _run_group(kind, ms, 1024, 768, 1.5, 0.5, seed=53, use_small_m=True)
 
 
 def test_grouped_many_groups():

@@ -69,6 +69,41 @@ def test_no_alloc_matches_workspace_entry_point_twice():
         assert torch.equal(got, ref)  # same kernels, same arithmetic: identical bits (tolerance 0)
 
 
+def test_no_alloc_long_k_agrees_with_both_workspace_sizes():
+    """Long k and few tiles: given its optional partial-sum scratch, the ordinary entry point shares each tile of the
+    half-empty last wave between several CTAs (another summation order); the built-in array holds only the tables, so
+    the allocation-free entry point runs whole tiles.  Its result is bit for bit that of the ordinary entry point with
+    a tables-only workspace, and within the operator's tolerance of the one with the full workspace."""
+    from tests.helpers import assert_parity
+
+    L = _lib.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    ms, K, N, alpha, beta = [600, 100, 256], 8192, 512, 1.5, 0.5
+    A, B, C, ap, bp, cp, sizes, E = _problem(ms, K, N, 3)
+    outs = {}
+    for name, nbytes in (("full", L.fb_group_workspace_bytes(E)), ("tables", L.fb_group_min_workspace_bytes(E))):
+        assert nbytes > 0
+        out = torch.full_like(C, float("nan"))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+        rc = L.fb_group_gemm(_lib.FB_BF16, 0, ap.data_ptr(), bp.data_ptr(), cp.data_ptr(), _out_ptrs(out, ms, N).data_ptr(),
+                             *[t.data_ptr() for t in sizes], E, sum(ms), N, K, alpha, beta, ws.data_ptr(), nbytes, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        outs[name] = out
+    assert L.fb_group_workspace_bytes(E) > L.fb_group_min_workspace_bytes(E)
+    for _ in range(2):
+        got = torch.full_like(C, float("nan"))
+        rc = L.fb_group_gemm_no_alloc(_lib.FB_BF16, 0, ap.data_ptr(), bp.data_ptr(), cp.data_ptr(),
+                                      _out_ptrs(got, ms, N).data_ptr(), *[t.data_ptr() for t in sizes], E, sum(ms), N, K,
+                                      alpha, beta, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        assert not torch.isnan(got).any()
+        assert torch.equal(got, outs["tables"])
+        assert_parity(got.float().cpu(), outs["full"].float().cpu(), 1e-2, abs(alpha) + abs(beta), "no-alloc vs full workspace")
+
+
 def test_no_alloc_rejects_more_groups_than_it_can_hold():
     L = _lib.lib
     cap = L.fb_no_alloc_max_groups()
