@@ -475,22 +475,31 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
     return it.tile < tiles;
   }
   if (p.sk_enabled == 2) {
-    // Stream-K over the whole launch (few waves, the last one more than half full): the tiles' k stages form one
+    // Few waves, the last one more than half full: the first `sk_dp` waves run whole tiles, all workers sweeping k
+    // in step (which is what keeps the shared operand panels in L2: dealing out the stages of ALL tiles was measured
+    // 19 % slower than whole tiles on 8192 x 1024 x 8192, each panel then being fetched from HBM once per tile that
+    // uses it).  The k stages of the remaining tiles, whose operands fit L2 together, form one
     // line of tiles x stages units that is cut into `workers` equal ranges.  A range that starts inside a tile
     // begins with that tile's tail (a partial, parked for the worker before it, which holds the tile's first
     // stages and finishes it); then come whole tiles; a range that ends inside a tile ends with that tile's head,
     // whose worker owns the tile and adds the parts of the workers after it -- parts that were the first thing
     // those workers did, so they are parked long before the owner's epilogue asks for them.
-    const long long line = static_cast<long long>(tiles) * stages;
+    if (idx < p.sk_dp) {
+      it.tile = worker + idx * workers;
+      it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
+      return true;
+    }
+    const int first = p.sk_dp * workers;  // first tile of the line
+    const long long line = static_cast<long long>(tiles - first) * stages;
     long long lo = worker * line / workers;
     const long long hi = (worker + 1) * line / workers;
-    for (int i = 0;; ++i) {
+    for (int i = p.sk_dp;; ++i) {
       if (lo >= hi) return false;
       const long long t = lo / stages;
       const int sb = static_cast<int>(lo - t * stages);
       const int se = static_cast<int>(min(static_cast<long long>(stages), sb + (hi - lo)));
       if (i == idx) {
-        it.tile = static_cast<int>(t);
+        it.tile = first + static_cast<int>(t);
         it.sb = sb; it.se = se;
         it.kind = sb > 0 ? ITEM_PARTIAL : (se == stages ? ITEM_FULL : ITEM_OWNER);
         if (it.kind == ITEM_OWNER) {

@@ -368,8 +368,10 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
                env_int("FLAGBLAS_B200_STREAMK_FULL", 1) != 0) {
       // Two or three waves of which the last is more than half full (one rank's share of a GEMM sharded over eight
       // GPUs: 128 tiles on 74 CTA pairs): whole tiles would leave (workers - rem) workers idle for a whole tile time.
-      // All k stages of all tiles are dealt evenly instead (FLAGBLAS_B200_STREAMK_FULL=0: whole tiles).
+      // After the whole waves the k stages of the last wave's tiles are dealt evenly over all workers
+      // (FLAGBLAS_B200_STREAMK_FULL=0: whole tiles; =2: deal out the stages of every tile, no whole waves).
       pp.sk_enabled = 2;
+      pp.sk_dp = env_int("FLAGBLAS_B200_STREAMK_FULL", 1) == 2 ? 0 : static_cast<int>(dp);
       FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     }
   }
@@ -1120,6 +1122,11 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     wide = t512 >= 4 * pairs && e512 >= e256 - 0.02 && n % 512 == 0;
   }
   if (pair && a3d && b3d && (wide || env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512)) block_n = 512;
+  // A 512-wide tile holds four k-slabs of 48 KB: as four one-slab stages the refill of a stage has three stages'
+  // MMAs to hide behind (two two-slab stages leave one), and with the B stage fetched by ONE copy the two copies per
+  // slab stay below the slab's MMA time (8192^3 fp16: 1463-1472 against 1425-1427 TFLOP/s with two slabs per stage;
+  // with two B copies per stage one slab per stage loses, 1403 against 1415)
+  if (block_n == 512 && force_ks == 0 && env_int("FLAGBLAS_B200_WIDE_MERGED", 1) != 0) ks = 1;
   // 512-wide tiles fetch this CTA's 256 columns of B with one copy (FLAGBLAS_B200_WIDE_MERGED=0: one copy of 128
   // columns per MMA half, the accumulator then holds the tile's columns in order)
   const bool wide_merged = block_n > 256 && env_int("FLAGBLAS_B200_WIDE_MERGED", 1) != 0;

@@ -218,7 +218,7 @@ size_t fb_group_min_workspace_bytes(int group_count);
  *
  * Limits and rules:
  *   - at most fb_no_alloc_max_groups() (= 256) groups per call; more returns FB_ERR_TOO_LARGE;
- *   - the array costs about 185 KB of device memory on every GPU that loads the library, for
+ *   - the array costs about 245 KB of device memory on every GPU that loads the library, for
  *     the life of the process;
  *   - the first call on each device looks the array's address up (cudaGetSymbolAddress); make
  *     that first call before starting any stream capture on that device.  If it is also the

@@ -39,6 +39,10 @@ def test_reference_dense_shapes_at_size(kind, shape):
         torch.cuda.synchronize()
         assert fb.device_status() == 0
         scale = abs(alpha) * k ** 0.5 * 0.25 + abs(beta)
+        if kind == "fp32":
+            # the yard-stick is an fp64 product; an fp32 accumulator (the reference's too) drifts from it by about
+            # sqrt(k) roundings of the running sum, which passes 1e-5 of the typical output size beyond k ~ 8192
+            scale *= max(1.0, k / 8192.0)
         check_samples_fp64(kind, ta, tb, m, n, k, alpha, beta, A, B, C0, C, scale, "%s %dx%dx%d t%d%d" % (kind, m, n, k, ta, tb))
         del A, B, C0, C
 
