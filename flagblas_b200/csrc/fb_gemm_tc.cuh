@@ -620,33 +620,43 @@ __device__ __noinline__ void fill_stage_by_hand(uint8_t* dst, uint32_t bar_addr,
                                                 const uint8_t* base, long long ld, int mn0, int mn_limit, int k0,
                                                 int k_limit) {
   constexpr int kPer = 16 / ESZ, kSpan = 128 / ESZ;
+  constexpr int kBatch = 16;  // units a lane has in flight: all loads of a batch are issued before the first store
   const int lane = threadIdx.x & 31;
   const int total = ks * tile_mn * 8;  // 16-byte units
   const int k_rows = kSpan * ks;
   const uint32_t dst_addr = smem_u32(dst);
-#pragma unroll 4
-  for (int u = lane; u < total; u += 32) {
-    const int unit = u & 7, rr = u >> 3;
-    long long r_src, c_src;  // row and first column of the unit in the stored matrix
-    int valid;
-    uint32_t off;
-    if (!mn_major) {
-      const int slab = rr / tile_mn, row = rr - slab * tile_mn;
-      const int r = mn0 + row, kk = k0 + slab * kSpan + unit * kPer;
-      valid = r < mn_limit ? k_limit - kk : 0;
-      off = static_cast<uint32_t>(rr * 128 + ((unit ^ (row & 7)) << 4));
-      r_src = r; c_src = kk;
-    } else {
-      const int krow = rr % k_rows;
-      const int kk = k0 + krow, mn = mn0 + (rr / k_rows) * kSpan + unit * kPer;
-      valid = kk < k_limit ? mn_limit - mn : 0;
-      const int su = ESZ == 4 ? ((((unit >> 1) ^ (krow & 3)) << 1) | (unit & 1)) : (unit ^ (krow & 7));
-      off = static_cast<uint32_t>(rr * 128 + (su << 4));
-      r_src = kk; c_src = mn;
+  for (int u0 = lane; u0 < total; u0 += 32 * kBatch) {
+    uint4 v[kBatch];
+    uint32_t off[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int u = u0 + 32 * i;
+      v[i] = make_uint4(0u, 0u, 0u, 0u);
+      off[i] = 0xffffffffu;
+      if (u < total) {
+        const int unit = u & 7, rr = u >> 3;
+        long long r_src, c_src;  // row and first column of the unit in the stored matrix
+        int valid;
+        if (!mn_major) {
+          const int slab = rr / tile_mn, row = rr - slab * tile_mn;
+          const int r = mn0 + row, kk = k0 + slab * kSpan + unit * kPer;
+          valid = r < mn_limit ? k_limit - kk : 0;
+          off[i] = static_cast<uint32_t>(rr * 128 + ((unit ^ (row & 7)) << 4));
+          r_src = r; c_src = kk;
+        } else {
+          const int krow = rr % k_rows;
+          const int kk = k0 + krow, mn = mn0 + (rr / k_rows) * kSpan + unit * kPer;
+          valid = kk < k_limit ? mn_limit - mn : 0;
+          const int su = ESZ == 4 ? ((((unit >> 1) ^ (krow & 3)) << 1) | (unit & 1)) : (unit ^ (krow & 7));
+          off[i] = static_cast<uint32_t>(rr * 128 + (su << 4));
+          r_src = kk; c_src = mn;
+        }
+        if (valid > 0) v[i] = load_unit<ESZ, VEC>(base + (r_src * ld + c_src) * ESZ, valid);
+      }
     }
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (valid > 0) v = load_unit<ESZ, VEC>(base + (r_src * ld + c_src) * ESZ, valid);
-    st_shared_v4(dst_addr + off, v);
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (off[i] != 0xffffffffu) st_shared_v4(dst_addr + off[i], v[i]);
   }
   fence_proxy_async_all();
   fence_acq_rel_cluster();

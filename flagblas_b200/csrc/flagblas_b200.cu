@@ -365,13 +365,16 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
       pp.sk_share = static_cast<int>(share);
       FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     } else if (rem > 0 && 2 * rem > workers && dp >= 1 && dp <= 2 && stages >= 16 && BLOCK_N <= 256 &&
-               env_int("FLAGBLAS_B200_STREAMK_FULL", 1) != 0) {
+               env_int("FLAGBLAS_B200_STREAMK_FULL", 0) != 0) {
       // Two or three waves of which the last is more than half full (one rank's share of a GEMM sharded over eight
-      // GPUs: 128 tiles on 74 CTA pairs): whole tiles would leave (workers - rem) workers idle for a whole tile time.
-      // After the whole waves the k stages of the last wave's tiles are dealt evenly over all workers
-      // (FLAGBLAS_B200_STREAMK_FULL=0: whole tiles; =2: deal out the stages of every tile, no whole waves).
+      // GPUs: 128 tiles on 74 CTA pairs): whole tiles leave (workers - rem) workers idle for a whole tile time.
+      // Opt-in (FLAGBLAS_B200_STREAMK_FULL=1): after the whole waves the k stages of the last wave's tiles are dealt
+      // evenly over all workers; =2 deals out the stages of every tile.  Measured slower than whole tiles, so off:
+      // fp16 8192 x 1024 x 8192 118.2 (=1) / 134.8 (=2) against 113.6 us, 5120 x 2560 x 4096 91.1 / 95.1 against 82.6 us
+      // -- every worker parks and re-reads a 256 KB partial tile, the owners' epilogues all fall at the end of the
+      // kernel, and with =2 the workers no longer sweep k in step, so shared operand panels leave L2 between uses.
       pp.sk_enabled = 2;
-      pp.sk_dp = env_int("FLAGBLAS_B200_STREAMK_FULL", 1) == 2 ? 0 : static_cast<int>(dp);
+      pp.sk_dp = env_int("FLAGBLAS_B200_STREAMK_FULL", 0) == 2 ? 0 : static_cast<int>(dp);
       FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     }
   }
@@ -686,7 +689,7 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
                     stages >= env_int("FLAGBLAS_B200_SK_MIN_STAGES", 32) && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
   // ... or stream-K over the whole launch: two or three waves, the last more than half full (see launch_tc)
   if (rem > 0 && 2 * rem > split_workers && dp >= 1 && dp <= 2 && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
-      pl.block_n <= 256 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 && env_int("FLAGBLAS_B200_STREAMK_FULL", 1) != 0)
+      pl.block_n <= 256 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 && env_int("FLAGBLAS_B200_STREAMK_FULL", 0) != 0)
     pl.want_streamk = true;
   return pl;
 }

@@ -171,7 +171,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "edge_fp32.npz"), **out)
     print("edge done")
 
-    # ------------------------------------------- BASELINE config 1: sgemm 512^3
+    # ------------------------------------------- the small fp32 benchmark workload: sgemm 512^3
     gen.manual_seed(0)
     m = n = k = 512
     A = torch.rand(m, k, generator=gen) * 2 - 1

@@ -41,11 +41,6 @@ def test_dense_plan_variants(env, kind, monkeypatch):
     ("fp16", 0, 0, 2560, 4096, 4096),    # 2 whole waves + 12 tail tiles, four workers per tail tile
     ("tf32", 1, 0, 4096, 4096, 2048),    # the same tail in TF32
     ("bf16", 1, 1, 4000, 4000, 4160),    # ragged edge tiles, last k stage half full
-    ("fp16", 0, 0, 8192, 1024, 8192),    # 128 tiles on 74 CTA pairs (one rank's share of 8192^3 over eight GPUs):
-                                         # 1.73 waves -> stream-K over the whole launch
-    ("bf16", 0, 1, 2048, 4096, 2048),    # the same tile count, short k (16 stages), K-contiguous B
-    ("tf32", 1, 0, 2304, 4096, 4096),    # 144 tiles: 1.95 waves, ranges that end a few stages into a tile
-    ("bf16", 0, 0, 5000, 2500, 4096),    # 200 tiles = 2.7 waves with ragged edge tiles
 ])
 def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
     """The stream-K tail (FLAGBLAS_B200_STREAMK=0 switches it off): when the last wave of tiles is at most half
@@ -75,6 +70,39 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
         assert_parity(outs[sk], ref, KINDS[kind][2], sc, "stream-k=%s %s %dx%dx%d" % (sk, kind, m, n, k))
     # different summation order: the two schedules may differ by a rounding step of the output type
     assert_parity(outs["1"], outs["0"], KINDS[kind][2], sc, "stream-k vs whole tiles")
+
+
+@pytest.mark.parametrize("kind,ta,tb,m,n,k", [
+    ("fp16", 0, 0, 8192, 1024, 8192),    # 128 tiles on 74 CTA pairs (one rank's share of 8192^3 over eight GPUs): 1.73 waves
+    ("bf16", 0, 1, 2048, 4096, 2048),    # the same tile count, short k (16 stages), K-contiguous B
+    ("tf32", 1, 0, 2304, 4096, 4096),    # 144 tiles: 1.95 waves, ranges that end a few stages into a tile
+    ("bf16", 0, 0, 5000, 2500, 4096),    # 200 tiles = 2.7 waves with ragged edge tiles
+])
+def test_stream_k_over_the_last_wave(kind, ta, tb, m, n, k, monkeypatch):
+    """Opt-in schedules for two or three waves of tiles of which the last is more than half full
+    (FLAGBLAS_B200_STREAMK_FULL=1: whole waves first, then the k stages of the remaining tiles dealt evenly over all
+    workers; =2: the stages of every tile dealt out): same results as whole tiles within the operator's tolerance."""
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=33, scale=0.25)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    outs = {}
+    for mode in ("0", "1", "2"):
+        monkeypatch.setenv("FLAGBLAS_B200_STREAMK_FULL", mode)
+        fb.reload_env()
+        Cd = C.to(DEV)
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        outs[mode] = Cd.float().cpu()
+    sc = result_scale(k, A, B, 1.5) + 0.5
+    opA = (Ad.t() if ta else Ad).double()
+    opB = (Bd.t() if tb else Bd).double()
+    if kind == "tf32":
+        trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+        opA, opB = trunc(opA), trunc(opB)
+    ref = (1.5 * (opA @ opB) + 0.5 * C.to(DEV).double()).float().cpu()
+    for mode in ("0", "1", "2"):
+        assert_parity(outs[mode], ref, KINDS[kind][2], sc, "last-wave stream-k=%s %s %dx%dx%d" % (mode, kind, m, n, k))
 
 
 @pytest.mark.parametrize("kind,ta,tb,m,n,k,beta", [

@@ -335,7 +335,7 @@ def test_golden_grouped_on_gpu(golden_dir):
 
 
 def test_moe_config4_properties():
-    """BASELINE config 4 at full size: 64 experts, K=4096, N=1536, Zipf(1.2) token counts (zeros allowed)."""
+    """The grouped MoE benchmark workload at full size: 64 experts, K=4096, N=1536, Zipf(1.2) token counts (zeros allowed)."""
     E, K, N, T = 64, 4096, 1536, 32768
     g = torch.Generator().manual_seed(3)
     w = torch.arange(1, E + 1, dtype=torch.float64) ** -1.2

@@ -54,7 +54,7 @@ def test_edge_cases_match_reference(golden_dir):
 
 
 def test_config1_sgemm512(golden_dir):
-    """BASELINE config 1 (sgemm 512^3, U(-1,1), seed 0) as the reference computed it on CPU."""
+    """The small fp32 benchmark workload (sgemm 512^3, U(-1,1), seed 0) as the reference computed it on CPU."""
     import torch
 
     z = _load(golden_dir, "config1_sgemm512.npz")
