@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
 
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int parts = p.ksplit == 2 ? 2 : 1;
+  const int parts = (p.ksplit == 2 || p.ksplit == 4) ? p.ksplit : 1;  // CTAs of one cluster that share the tile's k range
   const int tile = static_cast<int>(blockIdx.x) / parts, part = static_cast<int>(blockIdx.x) % parts;
   const int tile_m = tile / p.tiles_n, tile_n = tile % p.tiles_n;
   const int m0 = tile_m * BM, n0 = tile_n * BN;
@@ -346,12 +346,14 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-  if (parts == 2) {
-    // The mailbox sits behind the ring: [16-byte unit][thread], so a warp's accesses cover 512 consecutive bytes.
+  if (parts > 1) {
+    // The first CTA of the cluster has one mailbox per other part behind its ring, each laid out
+    // [16-byte unit][thread] so that a warp's accesses cover 512 consecutive bytes; the others write their sums into
+    // theirs over distributed shared memory, and the first adds them in part order (the same order every run).
+    constexpr int kBoxFloats = BM * BN;
     float* mailbox = pipe_smem + kPipeStages * (kAFloats + kBFloats);
-    const uint32_t mine = smem_u32(mailbox) + static_cast<uint32_t>(tid) * 16u;
-    if (part == 1) {
-      const uint32_t theirs = mapa_shared(mine, 0);
+    if (part > 0) {
+      const uint32_t theirs = mapa_shared(smem_u32(mailbox + (part - 1) * kBoxFloats) + static_cast<uint32_t>(tid) * 16u, 0);
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -361,14 +363,17 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
     }
     cluster_arrive_release();
     cluster_wait_acquire();
-    if (part == 1) return;
+    if (part > 0) return;
+    for (int q = 1; q < parts; ++q) {
+      const float* box = mailbox + (q - 1) * kBoxFloats;
 #pragma unroll
-    for (int i = 0; i < TM; ++i)
+      for (int i = 0; i < TM; ++i)
 #pragma unroll
-      for (int j = 0; j < TN; j += 4) {
-        const float4 v = *reinterpret_cast<const float4*>(mailbox + ((i * TN + j) / 4) * 1024 + tid * 4);
-        acc[i][j] += v.x; acc[i][j + 1] += v.y; acc[i][j + 2] += v.z; acc[i][j + 3] += v.w;
-      }
+        for (int j = 0; j < TN; j += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(box + ((i * TN + j) / 4) * 1024 + tid * 4);
+          acc[i][j] += v.x; acc[i][j + 1] += v.y; acc[i][j + 2] += v.z; acc[i][j + 3] += v.w;
+        }
+    }
   }
 
   // epilogue: alpha * acc + beta * C, C never read when beta == 0

@@ -465,22 +465,23 @@ static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t 
     FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
     attr_set[dev] = true;
   }
-  if (p.ksplit == 2) {
-    // clusters of two CTAs per tile; the first CTA's mailbox for the second's sums sits behind the ring
+  if (p.ksplit == 2 || p.ksplit == 4) {
+    // clusters of two or four CTAs per tile; the first CTA's mailboxes for the others' sums sit behind the ring
     constexpr int kMailbox = BM * BN * 4;
+    if (kBytes + 3 * kMailbox > kSmemLimit) return FB_ERR_UNSUPPORTED;  // (only 64 x 64 tiles are launched this way)
     static bool attr2_set[64] = {};
     if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
-      FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes + kMailbox));
+      FB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes + 3 * kMailbox));
       attr2_set[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(2 * tiles));
+    cfg.gridDim = dim3(static_cast<unsigned>(p.ksplit * tiles));
     cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = kBytes + kMailbox;
+    cfg.dynamicSmemBytes = kBytes + (p.ksplit - 1) * kMailbox;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.ksplit); attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
@@ -532,6 +533,10 @@ static int run_sgemm_simt(int transa, int transb, long long m, long long n, long
   // 896^3 21.8 -> 27.8, 640 x 640 x 2048 19.4 -> 22.6; FLAGBLAS_B200_SGEMM_KSPLIT=0 switches it off).
   p.ksplit = (!big && tiles <= env_int("FLAGBLAS_B200_SGEMM_KSPLIT_TILES", 2 * sms) && k >= 256 &&
               env_int("FLAGBLAS_B200_SGEMM_KSPLIT", 1) != 0) ? 2 : 1;
+  // few enough tiles that four CTAs per tile still fit two to an SM: clusters of four, each a quarter of k -- two
+  // CTAs (16 warps) per SM hide the shared-memory latency that one CTA of eight warps cannot
+  // (FLAGBLAS_B200_SGEMM_KSPLIT=2 keeps clusters of two)
+  if (p.ksplit == 2 && 4 * tiles <= 2LL * sms && k >= 512 && env_int("FLAGBLAS_B200_SGEMM_KSPLIT", 1) != 2) p.ksplit = 4;
   if (p.a_vec && p.b_vec && env_int("FLAGBLAS_B200_SGEMM_PIPE", 1) != 0)
     return big ? dispatch_sgemm_pipe<128, 128>(p, tiles, stream) : dispatch_sgemm_pipe<64, 64>(p, tiles, stream);
   if (big) sgemm_simt_kernel<128, 128, 8><<<static_cast<int>(tiles), 256, 0, stream>>>(p);
