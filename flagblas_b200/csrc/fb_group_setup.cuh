@@ -67,6 +67,8 @@ struct GroupSetupArgs {
   int span;        // elements per 128 bytes
   int allow3d;     // build 3-D views where a group's extents allow it
   int force_by_hand;  // 1: fetch every operand with ordinary loads, aligned or not (tests, comparisons)
+  int* clear_flags;   // stream-K flags of the GEMM that follows (or null): zeroed here
+  int clear_count;
   int publish_each;  // 1: publish every map with its own copy-and-fence instruction (profiling comparison)
 };
 
@@ -209,6 +211,10 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
   // the GEMM kernel queued behind this one may start its prologue now; it waits for this grid's completion
   // before reading the table (grid_dependency_wait)
   grid_launch_dependents();
+  // this kernel may itself have been launched while its predecessor (the previous call's GEMM, which reads the
+  // tables this one rewrites) was still running: nothing is written before that one has completed
+  grid_dependency_wait();
+  for (int i = tid; i < ga.clear_count; i += kSetupThreads) ga.clear_flags[i] = 0;
 
   for (int pi = 0; pi < 2; ++pi) {
     const GroupPass& ps = pi == 0 ? pass0 : pass1;
@@ -282,6 +288,8 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       // A_g: stored [m, lda], K contiguous -> 2-D extents {k, m}, or 3-D {128 B, m, k / span}
       reinterpret_cast<uint32_t*>(map_slot[warp][0])[lane] = reinterpret_cast<const uint32_t*>(tmpl[a3d ? 2 : 0])[lane];
       reinterpret_cast<uint32_t*>(map_slot[warp][1])[lane] = reinterpret_cast<const uint32_t*>(tmpl[b3d ? 3 : 1])[lane];
+      reinterpret_cast<uint32_t*>(map_slot[warp][2])[lane] = reinterpret_cast<const uint32_t*>(tmpl[a3d ? 2 : 0])[lane];
+      const uint32_t slot_r = smem_u32(map_slot[warp][2]);
       __syncwarp();
       if (lane == 0 && usable && a_tma && k > 0) {
         if (a3d) tensormap_patch3(slot_a, a, static_cast<uint32_t>(m), static_cast<uint32_t>(k / ga.span),
@@ -298,12 +306,14 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
           else tensormap_patch(slot_b, b, static_cast<uint32_t>(n), static_cast<uint32_t>(k), pitch);
         }
       }
-      __syncwarp();
-      // third map: A_g again, with a box of the rows one CTA of the pair fetches of the partial block
-      const uint32_t slot_r = smem_u32(map_slot[warp][2]);
-      reinterpret_cast<uint32_t*>(map_slot[warp][2])[lane] = reinterpret_cast<const uint32_t*>(map_slot[warp][0])[lane];
-      __syncwarp();
-      if (lane == 0 && swap_rows > 0 && usable && a_tma && k > 0) tensormap_patch_box_rows(slot_r, static_cast<uint32_t>(swap_rows / 2));
+      // third map (a third lane, at the same time): A_g again, with a box of the rows one CTA of the pair fetches of
+      // the partial block
+      if (lane == 2 && swap_rows > 0 && usable && a_tma && k > 0) {
+        if (a3d) tensormap_patch3(slot_r, a, static_cast<uint32_t>(m), static_cast<uint32_t>(k / ga.span),
+                                  static_cast<uint64_t>(lda * ga.esz));
+        else tensormap_patch(slot_r, a, static_cast<uint32_t>(k), static_cast<uint32_t>(m), static_cast<uint64_t>(lda * ga.esz));
+        tensormap_patch_box_rows(slot_r, static_cast<uint32_t>(swap_rows / 2));
+      }
       __syncwarp();
       if (ga.publish_each) {
         tensormap_publish(&ps.maps[3 * g], slot_a);

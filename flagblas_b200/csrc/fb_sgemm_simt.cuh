@@ -233,6 +233,10 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
   float* As = pipe_smem;
   float* Bs = pipe_smem + kPipeStages * kAFloats;
 
+  // launched as a programmatic dependent of whatever precedes it on the stream: its own dependents may be scheduled
+  // from here on, and nothing is read or written before the predecessor has completed
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int parts = (p.ksplit == 2 || p.ksplit == 4) ? p.ksplit : 1;  // CTAs of one cluster that share the tile's k range

@@ -479,16 +479,29 @@ static int launch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_t 
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = kBytes + (p.ksplit - 1) * kMailbox;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = static_cast<unsigned>(p.ksplit); attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = env_int("FLAGBLAS_B200_PDL", 1) != 0 ? 2 : 1;
     FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
     return FB_OK;
   }
-  kern<<<static_cast<unsigned>(tiles), 256, kBytes, stream>>>(p);
-  FB_CUDA_OK(cudaGetLastError());
+  // (a programmatic dependent of its predecessor on the stream, like the tensor-core GEMMs: in a sequence of small
+  // calls the launch of one overlaps the tail of the one before)
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = env_int("FLAGBLAS_B200_PDL", 1) != 0 ? 1 : 0;
+  FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
   return FB_OK;
 }
 
@@ -1369,11 +1382,20 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   if (!split && env_int("FLAGBLAS_B200_GROUP_STREAMK", 1) != 0 &&
       workspace_bytes >= group_tail_offset(static_cast<size_t>(G)) + streamk_bytes(di->sm_count, block_n)) {
     tail = ws + group_tail_offset(static_cast<size_t>(G));
-    FB_CUDA_OK(cudaMemsetAsync(tail, 0, kStreamKFlagBytes, stream));  // before the table builder: the GEMM stays its dependent
   }
+  // the table builder also clears the stream-K flags (one launch less than a memset node in front of it)
+  ga.clear_flags = reinterpret_cast<int*>(tail);
+  ga.clear_count = tail ? static_cast<int>(kStreamKFlagBytes / sizeof(int)) : 0;
 
-  group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
-  FB_CUDA_OK(cudaGetLastError());
+  // The builder is itself a programmatic dependent of whatever precedes it on the stream (typically the previous
+  // grouped GEMM, which reads the same tables): it becomes resident as that kernel drains and waits for its
+  // completion before writing anything.
+  if (env_int("FLAGBLAS_B200_PDL", 1) != 0) {
+    FB_CUDA_OK(launch_dependent(group_setup_kernel, 1, kSetupThreads, stream, pass[0], pass[1], ga));
+  } else {
+    group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
+    FB_CUDA_OK(cudaGetLastError());
+  }
 
   for (int i = 0; i < 2; ++i) {
     const GroupPass& ps = pass[i];
