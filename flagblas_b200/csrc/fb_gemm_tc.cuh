@@ -41,6 +41,9 @@ constexpr int kSwizzleBytes = 128;  // bytes of the contiguous dimension per sme
 constexpr int kNumThreads = 256;
 constexpr int kEpiWarp0 = 4;        // first epilogue warp (must be a multiple of 4)
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory
+constexpr int kMaxRing = 12;        // most pipeline stages a launch may use (barriers are laid out for this many)
+constexpr int kSmallMRows = 64;     // small-M plan: rows of a group per tile ...
+constexpr int kSmallMSlot = 32;     // ... and rows of A per CTA and k-slab in the stage slot (half of them)
 
 // How one operand's pipeline stage is fetched and described to the MMA.
 //
@@ -130,6 +133,12 @@ struct TcGemmParams {
   int sk_grouped, sk_head;
   // Grouped mode, CTA-pair tiles: compute every group's partial last row block transposed (GroupRec::swap_rows).
   int swap_partial;
+  // Grouped mode, small-M plan (the caller's hints say the groups have at most a few dozen rows each): EVERY tile is
+  // a transposed block of at most 64 rows of a group (tiles per group = ceil(m / 64) x column tiles), each CTA's A
+  // stage slot shrinks to 32 rows per k-slab, and the shared memory that frees -- together with the epilogue's
+  // staging blocks, which transposed tiles do not use -- holds more stages: such calls stream every group's weights
+  // once and are bound by how many bytes a CTA keeps in flight towards HBM.
+  int small_m;
   uint32_t idesc_swapped;  // instruction descriptor of such a block with N = 0 (the block's row count is added per tile)
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
@@ -719,12 +728,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // 128B-swizzled TMA/UMMA tiles want 1024-byte aligned stage bases.
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + kStages * Cfg::kABytes;
-  uint8_t* ctl = smem + kStages * Cfg::kStageBytes;
+  // [control block: barriers][operand ring: A slots of every stage, then B slots][epilogue staging blocks]; the
+  // small-M plan lets the ring run on into the staging blocks, which it does not use
+  uint8_t* ctl = smem;
+  uint8_t* ring = smem + Cfg::kCtlBytes;
+  uint8_t* epi_staging = ring + kStages * Cfg::kStageBytes;
+  const uint32_t a_slot_bytes = p.small_m ? kSmallMSlot * kSwizzleBytes : Cfg::kABytes;  // one k-slab of A in a stage
+  uint8_t* smem_a = ring;
+  uint8_t* smem_b = ring + static_cast<uint32_t>(p.stages) * p.ks * a_slot_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);
-  uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* empty_bar = full_bar + kMaxRing;
+  uint64_t* tmem_full_bar = empty_bar + kMaxRing;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -744,7 +758,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   grid_launch_dependents();
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(&full_bar[s], 1);   // the (leader's) producer arrival + transaction bytes
       mbar_init(&empty_bar[s], 1);  // one tcgen05.commit arrival
     }
@@ -816,7 +830,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const CUtensorMap* map = load_a ? &tmA : &tmB;
         uint32_t use3d = og.use3d;
         int row_base = 0;
-        int swap_half = 0;             // > 0: a transposed partial block; rows of A_g each CTA of the pair fetches
+        int swap_half = 0;             // > 0: a transposed block; rows of A_g each CTA of the pair contributes
+        int tile_rows = Cfg::kTileM;   // rows of the group per scheduled tile
         int fetch = kFetch2d;          // grouped: how this group's operand is fetched
         const void* raw = nullptr;     // hand-filled operand: base, pitch and extent along M / N
         long long raw_ld = 0;
@@ -832,7 +847,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           fetch = load_a ? gr.a_fetch : gr.b_fetch;
           use3d = fetch == kFetch3d;
           row_base = gr.row_base;
-          if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) {
+          if (PAIR && p.small_m) {
+            // small-M plan: every tile is a transposed block of up to 64 rows; a CTA's box is 32 rows high, of which
+            // the MMA reads the first swap_half (what the box holds beyond them lies past the group's rows or is not used)
+            swap_half = ((min(kSmallMRows, gr.m - tm * kSmallMRows) + 15) >> 4) << 3;
+            tile_rows = kSmallMRows;
+          } else if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) {
             // partial last row block, computed transposed: B_g is fetched as ever; of A_g each CTA fetches its half
             // of the block's rows through the group's third map (or by hand)
             swap_half = gr.swap_rows >> 1;
@@ -850,13 +870,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           kk_total = p.k;
         }
         // first row (A) / first column (B) of the operand slab this CTA fetches
-        const int mn0 = load_a ? row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * (swap_half ? swap_half : kBlockM)
+        const int mn0 = load_a ? row_base + tm * tile_rows + static_cast<int>(cta_rank) * (swap_half ? swap_half : kBlockM)
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * (p.wide_merged ? Cfg::kBRows : Cfg::kBRows / Cfg::kHalves);
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
         if (grouped && !grouped_range(p, k_blocks, role, sharers, item, swap_half != 0)) break;
         const int kb_begin = item.sb, kb_end = item.se;
         // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
-        const uint32_t a_slab_bytes = swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : Cfg::kABytes;
+        const uint32_t a_slab_bytes = p.small_m ? a_slot_bytes
+                                                : (swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : Cfg::kABytes);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (by_hand) {
@@ -865,7 +886,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const long long c1 = p.prof ? clock64() : 0;
           prof_wait += c1 - c0;
           const int k0 = kb * static_cast<int>(p.block_k);
-          const uint32_t a_stage_bytes = p.ks * Cfg::kABytes, b_stage_bytes = p.ks * Cfg::kBBytes;
+          const uint32_t a_stage_bytes = p.ks * a_slot_bytes, b_stage_bytes = p.ks * Cfg::kBBytes;
           uint8_t* dst = load_a ? smem_a + stage * a_stage_bytes : smem_b + stage * b_stage_bytes;
           const uint32_t slab_bytes = load_a ? a_slab_bytes : Cfg::kBBytes;
           uint32_t bar = smem_u32(&full_bar[stage]);
@@ -880,8 +901,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (fetch > kFetch3d) {
             // no tensor map for this operand: the whole warp fills the stage
             fill_stage_dispatch<kTf32 ? 4 : 2>(fetch, dst, bar, static_cast<int>(og.mn_major), static_cast<int>(p.ks),
-                                               load_a ? (swap_half ? swap_half : kBlockM) : Cfg::kBRows, raw, raw_ld, mn0,
-                                               mn_limit, k0, kk_total);
+                                               load_a ? (p.small_m ? kSmallMSlot : (swap_half ? swap_half : kBlockM)) : Cfg::kBRows,
+                                               raw, raw_ld, mn0, mn_limit, k0, kk_total);
           } else if (lane == 0 FB_AND_COPIES_ON(p)) {
             if (use3d) {
               // x is always 0: the innermost extent of the 3-D view is exactly one 128-byte row.
@@ -955,7 +976,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       const uint64_t a_desc0 = make_smem_desc(smem_u32(smem_a), p.a.lbo, p.a.sbo, p.a.layout);
       const uint64_t b_desc0 = make_smem_desc(smem_u32(smem_b), p.b.lbo, p.b.sbo, p.b.layout);
-      const uint32_t a_stage_units = (p.ks * Cfg::kABytes) >> 4, b_stage_units = (p.ks * Cfg::kBBytes) >> 4;
+      const uint32_t a_stage_units = (p.ks * a_slot_bytes) >> 4, b_stage_units = (p.ks * Cfg::kBBytes) >> 4;
       long long prof_wfull = 0, prof_wtmem = 0, prof_mma_issue = 0;
       const long long cstart = p.prof ? clock64() : 0;
       unsigned long long gstart = 0;
@@ -974,13 +995,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // A transposed partial block (GroupRec::swap_rows): the MMA's A operand is the B stage, its B operand the
         // A stage (`swap_half` rows per CTA, so its slabs lie closer together), and N is the block's row count.
         int swap_half = 0;
+        int slab_rows = 0;  // rows between the k-slabs of the A stage (the box height of its copies)
         uint32_t idesc = p.idesc;
         if (grouped) {
           while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
           const GroupRec& gr = p.groups[g];
           const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-          if (PAIR && p.swap_partial && gr.swap_rows > 0 && (t - gr.tile_start) / gr.tiles_n == gr.m / Cfg::kTileM) {
+          if (PAIR && p.small_m) {
+            const int tm = (t - gr.tile_start) / gr.tiles_n;
+            swap_half = ((min(kSmallMRows, gr.m - tm * kSmallMRows) + 15) >> 4) << 3;
+            slab_rows = kSmallMSlot;
+            idesc = p.idesc_swapped | (static_cast<uint32_t>(swap_half >> 2) << 17);
+          } else if (PAIR && p.swap_partial && gr.swap_rows > 0 && (t - gr.tile_start) / gr.tiles_n == gr.m / Cfg::kTileM) {
             swap_half = gr.swap_rows >> 1;
+            slab_rows = swap_half;
             idesc = p.idesc_swapped | (static_cast<uint32_t>(gr.swap_rows >> 3) << 17);
           }
           if (!grouped_range(p, stages_g, role, sharers, item, swap_half != 0)) break;
@@ -1020,7 +1048,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                   if (kH == 1 && swap_half) {
                     // slab j / 4 of the A stage starts swap_half rows of 128 bytes after the previous one
                     da = b_desc + off_b[j];
-                    db = a_desc + static_cast<uint32_t>((j >> 2) * swap_half * (kSwizzleBytes >> 4)) + ((p.a.k_adv_bytes >> 4) * (j & 3));
+                    db = a_desc + static_cast<uint32_t>((j >> 2) * slab_rows * (kSwizzleBytes >> 4)) + ((p.a.k_adv_bytes >> 4) * (j & 3));
                   }
                   umma_pair<kTf32>(d_half, da, db, idesc, accum);
                 } else {
@@ -1089,7 +1117,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int row_base = 0;
       Problem pr;
       bool k_is_zero = false;  // a group with k == 0 contributes beta * C only
-      int swap_rows = 0;       // > 0: the accumulator holds a partial row block transposed (lanes = columns of the tile)
+      int swap_rows = 0;       // > 0: the accumulator holds a row block transposed (lanes = columns of the tile)
+      int tile_rows = Cfg::kTileM;
       if (grouped) {
         while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
         const GroupRec& gr = p.groups[g];
@@ -1101,7 +1130,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         k_is_zero = gr.k == 0;
         row_base = gr.row_base;
         const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) swap_rows = gr.swap_rows;
+        if (PAIR && p.small_m) {
+          swap_rows = ((min(kSmallMRows, gr.m - tm * kSmallMRows) + 15) >> 4) << 4;
+          tile_rows = kSmallMRows;
+        } else if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) {
+          swap_rows = gr.swap_rows;
+        }
         if (!grouped_range(p, stages_g, role, sharers, item, swap_rows != 0)) break;
       } else {
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
@@ -1160,7 +1194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // write 32 neighbouring elements of one output row.
         using T = OutT;
         const int col = tn * BLOCK_N + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
-        const int block_row0 = row_base + tm * Cfg::kTileM;
+        const int block_row0 = row_base + tm * tile_rows;
         const int rows_here = min(swap_rows, pr.m - block_row0);
         const int chunks = (rows_here + 31) >> 5;
         T* ocol = reinterpret_cast<T*>(pr.out) + col;
@@ -1200,7 +1234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if (item.kind == ITEM_FULL || item.kind == ITEM_SPLIT) {
         // the usual case: this warp's 32 rows leave through its staging block as whole row segments
-        uint8_t* stage = ctl + Cfg::kCtlBytes + (warp - kEpiWarp0) * kEpiStageBytes;
+        uint8_t* stage = epi_staging + (warp - kEpiWarp0) * kEpiStageBytes;
         const int row0 = row - lane;
         auto hand_back = [&]() {
           // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
@@ -1298,7 +1332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     cluster_wait_acquire();
   } else {
     if (p.cluster_k > 1)
-      cluster_finish_tile<OutT, BLOCK_N>(p, smem_u32(smem), tmem_base, static_cast<int>(blockIdx.x) / p.cluster_k,
+      cluster_finish_tile<OutT, BLOCK_N>(p, smem_u32(ring), tmem_base, static_cast<int>(blockIdx.x) / p.cluster_k,
                                          !*abort_flag);
   }
   if (warp == 2) {

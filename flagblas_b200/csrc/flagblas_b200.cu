@@ -384,7 +384,13 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
 #else
   pp.debug = 0;
 #endif
-  const int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
+  int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
+  if (p.small_m) {
+    // small-M plan: 32-row A slots, and the ring runs on into the (unused) epilogue staging blocks
+    max_stages = (Cfg::kStages * Cfg::kStageBytes + Cfg::kEpiBytes) /
+                 (static_cast<int>(p.ks) * (kSmallMSlot * kSwizzleBytes + Cfg::kBBytes));
+    if (max_stages > kMaxRing) max_stages = kMaxRing;
+  }
   pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
   if (pp.stages < 1 || pp.stages > max_stages) pp.stages = max_stages;
   pp.prof = g_prof_buffer;
@@ -1291,8 +1297,8 @@ size_t fb_group_workspace_bytes(int group_count) {
   return group_tail_offset(static_cast<size_t>(group_count)) + streamk_bytes(di->sm_count, 256);
 }
 
-static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long n_hint,
-                       void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long m_hint,
+                       long long n_hint, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   const DeviceInfo* di = device_info();
   if (!di) return FB_ERR_LAUNCH;
   if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
@@ -1333,9 +1339,16 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   }
   // One pass of CTA-pair tiles: every whole 256-row block of a group is an ordinary tile, its last, partial block is
   // computed transposed with its row count in the MMA's N slot (FLAGBLAS_B200_GROUP_SWAP=0: an ordinary, padded tile).
-  const bool swap_partial = pair && !split && block_n == 256 && env_int("FLAGBLAS_B200_GROUP_SWAP", 1) != 0;
+  // Small-M plan when the hint says the groups average at most 64 rows (the reference's callers promise that with
+  // use_small_m, runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721; here it only steers the plan, any m_g is
+  // still computed): every tile a transposed block of up to 64 rows, deeper operand ring.
+  // FLAGBLAS_B200_GROUP_SMALL_M = 0 / 1 forces it off / on.
+  const int force_small = env_int("FLAGBLAS_B200_GROUP_SMALL_M", -1);
+  const bool small_m = pair && !split && block_n == 256 && env_int("FLAGBLAS_B200_GROUP_SWAP", 1) != 0 &&
+                       (force_small == 1 || (force_small != 0 && m_hint > 0 && m_hint <= 64LL * G));
+  const bool swap_partial = pair && !split && block_n == 256 && !small_m && env_int("FLAGBLAS_B200_GROUP_SWAP", 1) != 0;
   if (pair) {
-    pass[0].enabled = 1; pass[0].tile_m = 2 * kBlockM; pass_pair[0] = true;
+    pass[0].enabled = 1; pass[0].tile_m = small_m ? kSmallMRows : 2 * kBlockM; pass_pair[0] = true;
     pass[0].swap_partial = swap_partial ? 1 : 0;
     pass_ks[0] = env_int("FLAGBLAS_B200_KS", 2) == 1 ? 1 : 2;
     if (split) {
@@ -1355,12 +1368,13 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     if (!ps.enabled) continue;
     const int ks = pass_ks[i];
     const int b_rows = pass_pair[i] ? block_n / 2 : block_n;
-    int rc = encode_2d(&ps.tmpl_a, dtype, ws, span, kBlockM, kSwizzleBytes, span, kBlockM);
+    const uint32_t a_box_rows = (small_m && i == 0) ? kSmallMSlot : kBlockM;  // rows of A_g one copy fetches
+    int rc = encode_2d(&ps.tmpl_a, dtype, ws, span, kBlockM, kSwizzleBytes, span, a_box_rows);
     if (rc) return rc;
     if (b_k_contig) rc = encode_2d(&ps.tmpl_b, dtype, ws, span, b_rows, kSwizzleBytes, span, b_rows);
     else rc = encode_2d(&ps.tmpl_b, dtype, ws, span, span * ks, kSwizzleBytes, span, span * ks, atom32);
     if (rc) return rc;
-    rc = encode_3d(&ps.tmpl_a3, dtype, ws, span, kBlockM, ks, kSwizzleBytes, kSwizzleBytes, span, kBlockM, ks, false);
+    rc = encode_3d(&ps.tmpl_a3, dtype, ws, span, kBlockM, ks, kSwizzleBytes, kSwizzleBytes, span, a_box_rows, ks, false);
     if (!rc) {
       if (b_k_contig)
         rc = encode_3d(&ps.tmpl_b3, dtype, ws, span, b_rows, ks, kSwizzleBytes, kSwizzleBytes, span, b_rows, ks, false);
@@ -1411,6 +1425,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.b = make_geom(esz, b_rows, !b_k_contig, ks, false);
     p.num_groups = G;
     p.swap_partial = ps.swap_partial;
+    p.small_m = (small_m && i == 0) ? 1 : 0;
     p.idesc_swapped = make_idesc(idesc_fmt(dtype), b_k_contig ? 0 : 1, 0, block_n, 0);  // M slot = the tile's columns
     p.groups = ps.recs;
     p.total_tiles = ps.total_tiles;
@@ -1432,7 +1447,6 @@ int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64
                   const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count, int64_t m_hint,
                   int64_t n_hint, int64_t k_hint, float alpha, float beta, void* workspace, size_t workspace_bytes,
                   void* stream) {
-  (void)m_hint;
   (void)k_hint;
   if (dtype != FB_TF32 && dtype != FB_F16 && dtype != FB_BF16) return FB_ERR_INVALID_ARG;
   if (group_count < 0) return FB_ERR_INVALID_ARG;
@@ -1448,7 +1462,7 @@ int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64
   ga.m_sizes = d_m; ga.n_sizes = d_n; ga.k_sizes = d_k;
   ga.ldas = d_lda; ga.ldbs = d_ldb; ga.ldcs = d_ldc;
   ga.num_groups = group_count;
-  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, alpha, beta, n_hint, workspace, workspace_bytes,
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, alpha, beta, m_hint, n_hint, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
 }
 
@@ -1468,7 +1482,7 @@ int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const
   ga.mm_lda = lda; ga.mm_ldb = ldb; ga.mm_b_group_stride = b_group_stride; ga.mm_ldo = ldc;
   ga.mm_n = static_cast<int>(n); ga.mm_k = static_cast<int>(k);
   ga.num_groups = group_count;
-  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, 1.f, 0.f, n, workspace, workspace_bytes,
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, 1.f, 0.f, /*m_hint=*/0, n, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
 }
 

@@ -20,7 +20,11 @@ _cop = _lib.cop
 
 
 def _group(code, b_k_contig, name, group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes,
-           d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta):
+           d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
+    if use_small_m:
+        # the caller's promise that no group has more than 64 rows: the library takes its small-M plan when the row
+        # hint says so (any m_g is still computed correctly)
+        M = min(int(M), 64 * int(group_size)) if int(M) > 0 else 64 * int(group_size)
     alpha = alpha.item() if isinstance(alpha, torch.Tensor) else float(alpha)
     beta = beta.item() if isinstance(beta, torch.Tensor) else float(beta)
     if group_size == 0:
@@ -50,24 +54,26 @@ def group_bfgemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_siz
     """bf16 grouped GEMM (reference: ops/level3/group_gemm.py:221-262).
 
     ``use_small_m`` is the caller's promise that no group has more than 64 rows (the reference routes such calls
-    to dedicated kernels, runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721); here it steers the tile plan.
+    to dedicated kernels, runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721); here it selects the small-M
+    tile plan (tiles of up to 64 rows computed transposed, a deeper operand ring), which is also chosen by itself
+    when ``M <= 64 * group_size``.  Results do not depend on it.
     """
     return _group(_lib.FB_BF16, 0, "group_bfgemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
-                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m)
 
 
 def group_hgemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas,
                 d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
     """fp16 grouped GEMM (reference: ops/level3/group_gemm.py:380-421)."""
     return _group(_lib.FB_F16, 0, "group_hgemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
-                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m)
 
 
 def group_tf32gemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas,
                    d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m=False):
     """fp32-storage / TF32 grouped GEMM, B_g stored [n_g, k_g] (reference: group_gemm.py:540-581)."""
     return _group(_lib.FB_TF32, 1, "group_tf32gemm", group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs,
-                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta)
+                  d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m)
 
 
 # fp32 tensors run with TF32 tensor-core products (fp32 accumulate), like the reference's fp32 `tl.dot`

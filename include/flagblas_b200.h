@@ -175,8 +175,11 @@ size_t fb_gemv_fp8_workspace_bytes(int64_t m, int64_t n);
  *   src/flag_blas/ops/level3/group_gemm.py:221-262, 380-421, 540-581
  *   (+ src/flag_blas/runtime/backend/_nvidia/hopper/ops/group_gemm.py:699-891).
  * dtype is FB_BF16, FB_F16 or FB_TF32.  m_hint / n_hint / k_hint are the
- * reference's M, N, K arguments: host-side hints (typical sizes) that only
- * steer the tile shape; 0 = unknown.  `workspace` holds the device-built
+ * reference's M, N, K arguments (total rows of all groups, columns, depth):
+ * host-side hints that only steer the tile plan, 0 = unknown.  A call whose
+ * m_hint says the groups average at most 64 rows (m_hint <= 64 * group_count:
+ * the reference's use_small_m case) takes a plan built for groups of a few
+ * rows; results do not depend on the hints.  `workspace` holds the device-built
  * tile table and tensor maps: fb_group_workspace_bytes(group_count) bytes,
  * 256-byte aligned; it may be reused by the next call on the same stream.
  */

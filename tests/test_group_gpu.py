@@ -99,7 +99,9 @@ def test_grouped_alpha_zero_and_beta_zero(kind):
 @pytest.mark.parametrize("env", [{"FLAGBLAS_B200_GROUP_SPLIT": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"}, {"FLAGBLAS_B200_PAIR": "0"},
                                  {"FLAGBLAS_B200_TMA3D": "0"},
                                  {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SWAP": "0"},
-                                 {"FLAGBLAS_B200_GROUP_SWAP": "0", "FLAGBLAS_B200_KS": "1"}])
+                                 {"FLAGBLAS_B200_GROUP_SWAP": "0", "FLAGBLAS_B200_KS": "1"},
+                                 {"FLAGBLAS_B200_GROUP_SMALL_M": "1"}, {"FLAGBLAS_B200_GROUP_SMALL_M": "1", "FLAGBLAS_B200_KS": "1"},
+                                 {"FLAGBLAS_B200_GROUP_SMALL_M": "0"}])
 def test_grouped_tile_plan_variants(env, monkeypatch):
     """The alternative tile plans (two-pass split of every remainder or only of remainders up to 128 rows,
     single-CTA tiles, 2-D copies, one k-slab per stage) compute the same thing."""
@@ -193,7 +195,7 @@ def test_grouped_unaligned_operands(kind):
 
 
 @pytest.mark.parametrize("env", [{}, {"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_KS": "1"}, {"FLAGBLAS_B200_GROUP_SPLIT": "2"},
-                                 {"FLAGBLAS_B200_GROUP_SWAP": "0"}])
+                                 {"FLAGBLAS_B200_GROUP_SWAP": "0"}, {"FLAGBLAS_B200_GROUP_SMALL_M": "1"}])
 def test_grouped_by_hand_matches_tma(env, monkeypatch):
     """Every operand through the load / store path (FLAGBLAS_B200_GROUP_BY_HAND=1), aligned or not, in each tile plan:
     bit for bit what the TMA path gives."""
@@ -238,14 +240,25 @@ def test_grouped_partial_blocks_every_row_count(kind):
     _run_group(kind, ms[:12], 200, 136, 1.0, 0.0, seed=52, var_nk=True)
 
 
-@pytest.mark.parametrize("kind", ["bf16", "tf32"])
-def test_grouped_decode_shape_small_m(kind):
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "tf32"])
+def test_grouped_decode_shape_small_m(kind, monkeypatch):
     """The reference's small-M case (every m_g <= 64, use_small_m=True routes to its dedicated kernels,
-    runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721): here every tile is a transposed partial block."""
+    runtime/backend/_nvidia/hopper/ops/group_gemm.py:717-721): here the small-M plan -- every tile a transposed block of
+    up to 64 rows, 32-row A slots, a deeper ring.  The promise is not relied on: groups with more rows are tiled in
+    64-row blocks.  Same bits as the general plan."""
     import random
     rnd = random.Random(7)
     ms = [rnd.randint(0, 64) for _ in range(64)]
-    _run_group(kind, ms, 1024, 768, 1.5, 0.5, seed=53, use_small_m=True)
+    got = _run_group(kind, ms, 1024, 768, 1.5, 0.5, seed=53, use_small_m=True)
+    monkeypatch.setenv("FLAGBLAS_B200_GROUP_SMALL_M", "0")
+    fb.reload_env()
+    ref = _run_group(kind, ms, 1024, 768, 1.5, 0.5, seed=53, use_small_m=True)
+    assert torch.equal(torch.nan_to_num(got, nan=-7.0), torch.nan_to_num(ref, nan=-7.0))
+    monkeypatch.delenv("FLAGBLAS_B200_GROUP_SMALL_M")
+    fb.reload_env()
+    # the promise broken: a 700-row and a 65-row group among the small ones
+    _run_group(kind, [3, 700, 64, 65, 0, 17, 129], 520, 264, 1.5, 0.5, seed=54, use_small_m=True)
+    _run_group(kind, [40, 200, 64, 33], 200, 136, 1.0, 0.0, seed=55, var_nk=True, use_small_m=True)
 
 
 def test_grouped_many_groups():
