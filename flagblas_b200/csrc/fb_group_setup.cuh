@@ -127,7 +127,7 @@ __device__ __forceinline__ void tensormap_release_all() {
   asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
 
-// 32 warps, one group per warp at a time.  Building a tensor map is a chain of dependent steps (argument
+// CTAs of 32 warps, one group per warp at a time.  Building a tensor map is a chain of dependent steps (argument
 // loads, eight tensormap.replace, the proxy release), so the kernel is organised to keep that chain short:
 // the four templates are staged in shared memory once (lane-indexed reads of kernel parameters are
 // serialised by the constant cache), the arguments of a warp's next group are loaded while the current one is
@@ -197,6 +197,57 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
   return warp_tot[warp] + inc - v;
 }
 
+// What the table builder decides about one group in one pass (the same function serves the CTAs that build the
+// group's record and tensor maps and the CTA that scans the tile counts, so the two always agree).
+struct GroupPlan {
+  bool usable;           // contributes tiles
+  bool bad_alignment;    // non-empty, but an address or pitch is not a multiple of the element size
+  bool a_tma, b_tma;     // fetched through a tensor map (otherwise by hand)
+  bool a3d, b3d;         // ... a 3-D one
+  int a_align, b_align;  // bytes every 16-byte unit of the operand is aligned to (<= 16)
+  long long row_base, rows;
+  int tiles_n, tiles;
+  int swap_rows;
+};
+
+__device__ __forceinline__ GroupPlan plan_group(const GroupSetupArgs& ga, const GroupPass& ps, const GroupIn& in) {
+  GroupPlan pl;
+  const long long m = in.m, n = in.n, k = in.k;
+  const bool empty = (m == 0 || n == 0);
+  // What base and pitch guarantee for every 16-byte unit of the operand: 16 = TMA can address it; less = the
+  // GEMM's producer warps fetch it with loads of that width; less than an element = not a matrix of this type.
+  const uintptr_t a_bits = reinterpret_cast<uintptr_t>(in.a) | static_cast<uintptr_t>(in.lda * ga.esz) | 16u;
+  const uintptr_t b_bits = reinterpret_cast<uintptr_t>(in.b) | static_cast<uintptr_t>(in.ldb * ga.esz) | 16u;
+  pl.a_align = static_cast<int>(a_bits & (~a_bits + 1));
+  pl.b_align = static_cast<int>(b_bits & (~b_bits + 1));
+  pl.usable = !empty && (k == 0 || (pl.a_align >= ga.esz && pl.b_align >= ga.esz));
+  pl.bad_alignment = !empty && !pl.usable;
+  pl.a_tma = pl.a_align == 16 && !ga.force_by_hand;
+  pl.b_tma = pl.b_align == 16 && !ga.force_by_hand;
+  // a 3-D view tiles its third dimension in whole 128-byte rows: that extent must divide evenly
+  pl.a3d = ga.allow3d && pl.usable && pl.a_tma && k > 0 && (k % ga.span) == 0;
+  pl.b3d = ga.allow3d && pl.usable && pl.b_tma && k > 0 && ((ga.b_k_contig ? k : n) % ga.span) == 0;
+  // rows of the group this pass is responsible for: [row_base, row_base + rows)
+  pl.row_base = 0;
+  pl.rows = m;
+  if (ps.rows_mod > 0) {
+    long long lead = m / ps.rows_mod * ps.rows_mod;
+    if (ps.keep_over > 0 && m - lead > ps.keep_over) lead = m;  // a long remainder is one more (padded) tile of the leading pass
+    if (ps.leading) pl.rows = lead;
+    else { pl.row_base = lead; pl.rows = m - lead; }
+  }
+  pl.tiles_n = static_cast<int>((n + ps.block_n - 1) / ps.block_n);
+  pl.tiles = pl.usable ? static_cast<int>((pl.rows + ps.tile_m - 1) / ps.tile_m) * pl.tiles_n : 0;
+  // the last row block of the group, when it is not a whole one, runs transposed with its row count (rounded up
+  // to the MMA's granularity of 16) in the instruction's N slot
+  const int part_rows = ps.swap_partial ? static_cast<int>(m % ps.tile_m) : 0;
+  pl.swap_rows = (part_rows + 15) / 16 * 16;
+  return pl;
+}
+
+// Grid: `builders` CTAs that each build the records and tensor maps of their share of the groups (one warp per
+// group at a time), plus one last CTA that computes every group's tile count itself, scans them and writes the
+// groups' first tile indices, the total and the call-wide flags.  The two kinds of CTA write disjoint fields.
 __global__ void __launch_bounds__(kSetupThreads)
 group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constant__ GroupPass pass1,
                    const GroupSetupArgs ga) {
@@ -205,91 +256,103 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
   __shared__ int counts[kSetupSmemGroups];
   __shared__ int warp_tot[32];
   __shared__ int total_sh;
+  __shared__ int by_hand_sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = ga.num_groups;
   constexpr int kWarps = kSetupThreads / 32;
+  const int builders = static_cast<int>(gridDim.x) - 1;
+  const bool scanner = static_cast<int>(blockIdx.x) == builders;
   // the GEMM kernel queued behind this one may start its prologue now; it waits for this grid's completion
   // before reading the table (grid_dependency_wait)
   grid_launch_dependents();
   // this kernel may itself have been launched while its predecessor (the previous call's GEMM, which reads the
   // tables this one rewrites) was still running: nothing is written before that one has completed
   grid_dependency_wait();
-  for (int i = tid; i < ga.clear_count; i += kSetupThreads) ga.clear_flags[i] = 0;
+
+  if (scanner) {
+    for (int i = tid; i < ga.clear_count; i += kSetupThreads) ga.clear_flags[i] = 0;
+    for (int pi = 0; pi < 2; ++pi) {
+      const GroupPass& ps = pi == 0 ? pass0 : pass1;
+      if (!ps.enabled) continue;
+      if (tid == 0) by_hand_sh = 0;
+      __syncthreads();
+      // ---- exclusive prefix sum of tile counts (each thread owns a contiguous chunk of groups)
+      const int per = (G + kSetupThreads - 1) / kSetupThreads;
+      const int g0 = tid * per;
+      const int g1 = min(G, g0 + per);
+      const bool in_smem = G <= kSetupSmemGroups;  // then per == 1 and a group's count is kept instead of recomputed
+      int s = 0, by_hand = 0;
+      for (int g = g0; g < g1; ++g) {
+        const GroupIn in = load_group(ga, g);
+        const GroupPlan pl = plan_group(ga, ps, in);
+        if (pl.bad_alignment) atomicCAS(&g_fb_status, 0, DEV_GROUP_MISALIGNED);
+        if (pl.usable && in.k > 0 && (!pl.a_tma || !pl.b_tma)) by_hand = 1;
+        if (in_smem) counts[g] = pl.tiles;
+        s += pl.tiles;
+      }
+      if (by_hand) by_hand_sh = 1;
+      int run = block_exclusive_scan(s, warp_tot, &total_sh);
+      if (tid == 0) {
+        ps.total_tiles[0] = total_sh;
+        ps.total_tiles[1] = by_hand_sh;  // some operand has no tensor map: the GEMM's producers run as whole warps
+      }
+      for (int g = g0; g < g1; ++g) {
+        const int c = in_smem ? counts[g] : plan_group(ga, ps, load_group(ga, g)).tiles;
+        ps.recs[g].tile_start = run;
+        run += c;
+      }
+      __syncthreads();
+    }
+    return;
+  }
 
   for (int pi = 0; pi < 2; ++pi) {
     const GroupPass& ps = pi == 0 ? pass0 : pass1;
     if (!ps.enabled) continue;
 
     // first group's arguments are in flight while the templates are staged
+    const int first = static_cast<int>(blockIdx.x) * kWarps + warp, stride = builders * kWarps;
     GroupIn cur{};
-    if (warp < G) cur = load_group(ga, warp);
+    if (first < G) cur = load_group(ga, first);
     if (warp < 4) {
       const CUtensorMap* t = warp == 0 ? &ps.tmpl_a : (warp == 1 ? &ps.tmpl_b : (warp == 2 ? &ps.tmpl_a3 : &ps.tmpl_b3));
       reinterpret_cast<uint32_t*>(tmpl[warp])[lane] = reinterpret_cast<const uint32_t*>(t)[lane];
     }
-    if (tid == 0) ps.total_tiles[1] = 0;  // set below when some operand has to be fetched by hand
     __syncthreads();
 
-    // ---- per-group records + tensor maps (one warp per group, strided)
-    for (int g = warp; g < G; g += kWarps) {
+    // ---- per-group records + tensor maps (one warp per group, strided over all builder CTAs)
+    for (int g = first; g < G; g += stride) {
       const GroupIn in = cur;
-      if (g + kWarps < G) cur = load_group(ga, g + kWarps);  // next group's loads overlap this group's build
+      if (g + stride < G) cur = load_group(ga, g + stride);  // next group's loads overlap this group's build
+      const GroupPlan pl = plan_group(ga, ps, in);
       const long long m = in.m, n = in.n, k = in.k, lda = in.lda, ldb = in.ldb, ldo = in.ldo, ldcin = in.ldo;
       const uint8_t* a = in.a;
       const uint8_t* b = in.b;
-      const void* cin = in.cin;
-      void* out = in.out;
-      const bool empty = (m == 0 || n == 0);
-      // What base and pitch guarantee for every 16-byte unit of the operand: 16 = TMA can address it; less = the
-      // GEMM's producer warps fetch it with loads of that width; less than an element = not a matrix of this type.
-      const uintptr_t a_bits = reinterpret_cast<uintptr_t>(a) | static_cast<uintptr_t>(lda * ga.esz) | 16u;
-      const uintptr_t b_bits = reinterpret_cast<uintptr_t>(b) | static_cast<uintptr_t>(ldb * ga.esz) | 16u;
-      const int a_align = static_cast<int>(a_bits & (~a_bits + 1)), b_align = static_cast<int>(b_bits & (~b_bits + 1));
-      const bool usable = !empty && (k == 0 || (a_align >= ga.esz && b_align >= ga.esz));
-      if (!empty && !usable && lane == 0) atomicCAS(&g_fb_status, 0, DEV_GROUP_MISALIGNED);
-      const bool a_tma = a_align == 16 && !ga.force_by_hand, b_tma = b_align == 16 && !ga.force_by_hand;
-      // a 3-D view tiles its third dimension in whole 128-byte rows: that extent must divide evenly
-      const bool a3d = ga.allow3d && usable && a_tma && k > 0 && (k % ga.span) == 0;
-      const bool b3d = ga.allow3d && usable && b_tma && k > 0 && ((ga.b_k_contig ? k : n) % ga.span) == 0;
-      if (usable && k > 0 && (!a_tma || !b_tma) && lane == 0) ps.total_tiles[1] = 1;  // the GEMM's producers run as whole warps
-      // rows of the group this pass is responsible for: [row_base, row_base + rows)
-      long long row_base = 0, rows = m;
-      if (ps.rows_mod > 0) {
-        long long lead = m / ps.rows_mod * ps.rows_mod;
-        if (ps.keep_over > 0 && m - lead > ps.keep_over) lead = m;  // a long remainder is one more (padded) tile of the leading pass
-        if (ps.leading) rows = lead;
-        else { row_base = lead; rows = m - lead; }
-      }
+      const bool usable = pl.usable, a_tma = pl.a_tma, b_tma = pl.b_tma, a3d = pl.a3d, b3d = pl.b3d;
+      const int swap_rows = pl.swap_rows;
 
-      // the last row block of the group, when it is not a whole one, runs transposed with its row count (rounded up
-      // to the MMA's granularity of 16) in the instruction's N slot
-      const int part_rows = ps.swap_partial ? static_cast<int>(m % ps.tile_m) : 0;
-      const int swap_rows = (part_rows + 15) / 16 * 16;
       if (lane == 0) {
-        GroupRec r;
-        r.swap_rows = swap_rows;
-        r.m = static_cast<int>(m); r.n = static_cast<int>(n); r.k = static_cast<int>(k);
-        r.tiles_n = static_cast<int>((n + ps.block_n - 1) / ps.block_n);
-        // tile_start temporarily holds this group's tile count
-        r.tile_start = usable ? static_cast<int>((rows + ps.tile_m - 1) / ps.tile_m) * r.tiles_n : 0;
-        r.a_fetch = a_tma ? (a3d ? kFetch3d : kFetch2d) : a_align;
-        r.b_fetch = b_tma ? (b3d ? kFetch3d : kFetch2d) : b_align;
-        r.row_base = static_cast<int>(row_base);
-        r.out = out; r.ldo = ldo; r.cin = cin; r.ldcin = ldcin;
-        r.a = a; r.b = b; r.lda = lda; r.ldb = ldb;
-        r.vec_ok = (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(cin)) & 15) == 0 &&
-                    ((ldo * ga.esz) & 15) == 0) ? 1 : 0;
-        ps.recs[g] = r;
-        if (g < kSetupSmemGroups) counts[g] = r.tile_start;
+        // every field but tile_start, which the scanning CTA writes
+        GroupRec* r = &ps.recs[g];
+        r->swap_rows = swap_rows;
+        r->m = static_cast<int>(m); r->n = static_cast<int>(n); r->k = static_cast<int>(k);
+        r->tiles_n = pl.tiles_n;
+        r->a_fetch = a_tma ? (a3d ? kFetch3d : kFetch2d) : pl.a_align;
+        r->b_fetch = b_tma ? (b3d ? kFetch3d : kFetch2d) : pl.b_align;
+        r->row_base = static_cast<int>(pl.row_base);
+        r->out = in.out; r->ldo = ldo; r->cin = in.cin; r->ldcin = ldcin;
+        r->a = a; r->b = b; r->lda = lda; r->ldb = ldb;
+        r->vec_ok = (((reinterpret_cast<uintptr_t>(in.out) | reinterpret_cast<uintptr_t>(in.cin)) & 15) == 0 &&
+                     ((ldo * ga.esz) & 15) == 0) ? 1 : 0;
       }
 
       const uint32_t slot_a = smem_u32(map_slot[warp][0]), slot_b = smem_u32(map_slot[warp][1]);
+      const uint32_t slot_r = smem_u32(map_slot[warp][2]);
       __syncwarp();  // the previous group's copies out of these slots are done
       // A_g: stored [m, lda], K contiguous -> 2-D extents {k, m}, or 3-D {128 B, m, k / span}
       reinterpret_cast<uint32_t*>(map_slot[warp][0])[lane] = reinterpret_cast<const uint32_t*>(tmpl[a3d ? 2 : 0])[lane];
       reinterpret_cast<uint32_t*>(map_slot[warp][1])[lane] = reinterpret_cast<const uint32_t*>(tmpl[b3d ? 3 : 1])[lane];
       reinterpret_cast<uint32_t*>(map_slot[warp][2])[lane] = reinterpret_cast<const uint32_t*>(tmpl[a3d ? 2 : 0])[lane];
-      const uint32_t slot_r = smem_u32(map_slot[warp][2]);
       __syncwarp();
       if (lane == 0 && usable && a_tma && k > 0) {
         if (a3d) tensormap_patch3(slot_a, a, static_cast<uint32_t>(m), static_cast<uint32_t>(k / ga.span),
@@ -318,31 +381,15 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       if (ga.publish_each) {
         tensormap_publish(&ps.maps[3 * g], slot_a);
         tensormap_publish(&ps.maps[3 * g + 1], slot_b);
-        tensormap_publish(&ps.maps[3 * g + 2], slot_r);
+        if (swap_rows > 0) tensormap_publish(&ps.maps[3 * g + 2], slot_r);
       } else {
         tensormap_store(&ps.maps[3 * g], map_slot[warp][0], lane);
         tensormap_store(&ps.maps[3 * g + 1], map_slot[warp][1], lane);
-        tensormap_store(&ps.maps[3 * g + 2], map_slot[warp][2], lane);
+        if (swap_rows > 0) tensormap_store(&ps.maps[3 * g + 2], map_slot[warp][2], lane);
       }
     }
     if (!ga.publish_each) tensormap_release_all();
     __threadfence();
-    __syncthreads();
-
-    // ---- exclusive prefix sum of tile counts (each thread owns a contiguous chunk of groups)
-    const int per = (G + kSetupThreads - 1) / kSetupThreads;
-    const int g0 = tid * per;
-    const int g1 = min(G, g0 + per);
-    const bool in_smem = G <= kSetupSmemGroups;  // then per == 1 and the counts never left the SM
-    int s = 0;
-    for (int g = g0; g < g1; ++g) s += in_smem ? counts[g] : ps.recs[g].tile_start;
-    int run = block_exclusive_scan(s, warp_tot, &total_sh);
-    if (tid == 0) *ps.total_tiles = total_sh;
-    for (int g = g0; g < g1; ++g) {
-      const int c = in_smem ? counts[g] : ps.recs[g].tile_start;
-      ps.recs[g].tile_start = run;
-      run += c;
-    }
     __syncthreads();
   }
 }

@@ -1404,10 +1404,14 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   // The builder is itself a programmatic dependent of whatever precedes it on the stream (typically the previous
   // grouped GEMM, which reads the same tables): it becomes resident as that kernel drains and waits for its
   // completion before writing anything.
+  // builder CTAs (32 groups at a time each, at most 16 of them) + the CTA that scans the tile counts
+  int builders = (G + kSetupThreads / 32 - 1) / (kSetupThreads / 32);
+  if (builders > 16) builders = 16;
+  const unsigned setup_ctas = static_cast<unsigned>(builders + 1);
   if (env_int("FLAGBLAS_B200_PDL", 1) != 0) {
-    FB_CUDA_OK(launch_dependent(group_setup_kernel, 1, kSetupThreads, stream, pass[0], pass[1], ga));
+    FB_CUDA_OK(launch_dependent(group_setup_kernel, setup_ctas, kSetupThreads, stream, pass[0], pass[1], ga));
   } else {
-    group_setup_kernel<<<1, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
+    group_setup_kernel<<<setup_ctas, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
     FB_CUDA_OK(cudaGetLastError());
   }
 

@@ -97,7 +97,7 @@ _gather_streams = {}
 
 def sharded_gemm_gather(name: str, transa: int, transb: int, m: int, n: int, k: int, alpha, A: torch.Tensor, lda: int,
                         B: torch.Tensor, ldb: int, beta, C: torch.Tensor, ldc: int, rank: int, world: int,
-                        align: int = 256, chunks: int = 4, group=None) -> None:
+                        align: int = 256, chunks: int = 4, group=None, launch: Optional[Callable] = None) -> None:
     """:func:`sharded_gemm` followed by :func:`all_gather_columns`, overlapped: the GEMM runs in row blocks of
     ``A`` / ``C`` on the current stream and every finished block is exchanged on a side stream while the next one
     computes, so only the last block's exchange is exposed.  ``A``, ``B``, ``C`` are full-size operands with their
@@ -105,9 +105,21 @@ def sharded_gemm_gather(name: str, transa: int, transb: int, m: int, n: int, k: 
     every rank holds the complete ``C``.  Needs ``transa = N`` to cut row blocks; other layouts run the two phases
     one after the other."""
     if world == 1 or transa != CUBLAS_OP_N or chunks <= 1 or m < 2 * chunks:
-        sharded_gemm(name, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world, align)
+        sharded_gemm(name, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world, align, launch)
         if world > 1:
             all_gather_columns(C, m, n, ldc, rank, world, align, group)
+        return
+    a2 = A.view(-1)[: m * lda].view(m, lda)
+    c2 = C.view(-1)[: m * ldc].view(m, ldc)
+    step = -(-m // chunks)
+    step = -(-step // 256) * 256  # whole 256-row tiles per block
+    blocks = [(r0, min(m, r0 + step)) for r0 in range(0, m, step)]
+    if not C.is_cuda:
+        # host tensors (the CPU tests of the sharding logic): the same blocks, one after the other
+        for r0, r1 in blocks:
+            sharded_gemm(name, transa, transb, r1 - r0, n, k, alpha, a2[r0:r1], lda, B, ldb, beta, c2[r0:r1], ldc, rank,
+                         world, align, launch)
+            all_gather_columns(c2[r0:r1], r1 - r0, n, ldc, rank, world, align, group)
         return
     dev = C.device
     key = dev.index if dev.index is not None else torch.cuda.current_device()
@@ -116,14 +128,9 @@ def sharded_gemm_gather(name: str, transa: int, transb: int, m: int, n: int, k: 
     side = _gather_streams[key]
     cur = torch.cuda.current_stream(dev)
     side.wait_stream(cur)
-    a2 = A.view(-1)[: m * lda].view(m, lda)
-    c2 = C.view(-1)[: m * ldc].view(m, ldc)
-    step = -(-m // chunks)
-    step = -(-step // 256) * 256  # whole 256-row tiles per block
-    for r0 in range(0, m, step):
-        r1 = min(m, r0 + step)
+    for r0, r1 in blocks:
         sharded_gemm(name, transa, transb, r1 - r0, n, k, alpha, a2[r0:r1], lda, B, ldb, beta, c2[r0:r1], ldc, rank, world,
-                     align)
+                     align, launch)
         done = cur.record_event()
         with torch.cuda.stream(side):
             side.wait_event(done)

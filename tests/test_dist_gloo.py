@@ -44,15 +44,24 @@ def _worker(rank, world, port, transb, gather, out_q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     tdist.init_process_group("gloo", rank=rank, world_size=world)
-    m, n, k = 96, 600, 40           # 600 columns, 256-aligned boundaries -> shards [0,512) and [512,600)
+    m, n, k = (96 if gather != "blocks" else 600), 600, 40   # 600 columns, 256-aligned boundaries -> shards [0,512) and [512,600)
     g = torch.Generator().manual_seed(7)
     A = torch.randn(m, k, generator=g)
     B = torch.randn((n, k) if transb else (k, n), generator=g)
     C0 = torch.randn(m, n, generator=g)
     C = C0.clone()
+    ref = 1.5 * (A.double() @ (B.double().t() if transb else B.double())) + 0.5 * C0.double()
+    if gather == "blocks":
+        # GEMM by row blocks, each block's column shards exchanged as soon as it is done (three blocks of 256 rows here)
+        fbdist.sharded_gemm_gather("sgemm", 0, transb, m, n, k, 1.5, A, k, B, B.shape[1], 0.5, C, n, rank, world, chunks=3,
+                                   launch=_host_launch)
+        ok = torch.allclose(C.double(), ref, rtol=1e-5, atol=1e-4)
+        out_q.put((rank, fbdist.column_ranges(n, world)[rank], bool(ok)))
+        tdist.barrier()
+        tdist.destroy_process_group()
+        return
     n0, n1 = fbdist.sharded_gemm("sgemm", 0, transb, m, n, k, 1.5, A, k, B, B.shape[1], 0.5, C, n, rank, world,
                                  launch=_host_launch)
-    ref = 1.5 * (A.double() @ (B.double().t() if transb else B.double())) + 0.5 * C0.double()
     ok = torch.allclose(C[:, n0:n1].double(), ref[:, n0:n1], rtol=1e-5, atol=1e-4)
     # columns of the other rank are untouched
     mask = torch.ones(n, dtype=torch.bool); mask[n0:n1] = False
@@ -65,7 +74,7 @@ def _worker(rank, world, port, transb, gather, out_q):
     tdist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transb,gather", [(0, False), (1, True), (0, True)])
+@pytest.mark.parametrize("transb,gather", [(0, False), (1, True), (0, True), (0, "blocks"), (1, "blocks")])
 def test_two_ranks_column_shards(transb, gather):
     world = 2
     ctx = mp.get_context("spawn")
