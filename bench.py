@@ -611,12 +611,13 @@ def main():
 
     # Device-resident step.  N > 1: column-sharded in place -- every rank holds full-size A, B and C with their
     # original leading dimensions and computes its column block of C (the shard of B / C is a strided view; nothing
-    # is copied or exchanged).  --gather adds the all-gather that completes C on every rank, overlapped by row blocks.
+    # is copied or exchanged).  --gather adds the all-gather that completes C on every rank.
     def step():
         if world == 1:
             opfn(ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc)
         elif args.gather:
-            fbdist.sharded_gemm_gather(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+            fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
+            fbdist.all_gather_columns(C, m, n, ldc, rank, world)
         else:
             fbdist.sharded_gemm(op, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, rank, world)
 

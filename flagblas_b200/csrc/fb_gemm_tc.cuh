@@ -567,10 +567,9 @@ __device__ __forceinline__ bool grouped_tile(const TcGemmParams& p, int worker, 
 
 // Stage range and kind of a grouped work item whose tile has `stages` k-stages.  A tail tile too short to be worth
 // splitting is done whole by its owner; false tells a contributor that it has nothing to do.
-__device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it,
-                                              bool never_split = false) {
+__device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it) {
   it.part = 0;
-  const int share = (sharers > 1 && !never_split) ? (stages - p.sk_head) / sharers : 0;
+  const int share = sharers > 1 ? (stages - p.sk_head) / sharers : 0;
   if (role < 0 || share < 2) {
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
     return role <= 0;
@@ -873,7 +872,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int mn0 = load_a ? row_base + tm * tile_rows + static_cast<int>(cta_rank) * (swap_half ? swap_half : kBlockM)
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * (p.wide_merged ? Cfg::kBRows : Cfg::kBRows / Cfg::kHalves);
         const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
-        if (grouped && !grouped_range(p, k_blocks, role, sharers, item, swap_half != 0)) break;
+        if (grouped && !grouped_range(p, k_blocks, role, sharers, item)) break;
         const int kb_begin = item.sb, kb_end = item.se;
         // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
         const uint32_t a_slab_bytes = p.small_m ? a_slot_bytes
@@ -1011,7 +1010,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             slab_rows = swap_half;
             idesc = p.idesc_swapped | (static_cast<uint32_t>(gr.swap_rows >> 3) << 17);
           }
-          if (!grouped_range(p, stages_g, role, sharers, item, swap_half != 0)) break;
+          if (!grouped_range(p, stages_g, role, sharers, item)) break;
         }
         const int k_blocks = item.se - item.sb;  // stages of this work item
         // PAIR: the peer's epilogue warps arrive remotely -> cluster-scope acquire
@@ -1136,7 +1135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         } else if (PAIR && p.swap_partial && gr.swap_rows > 0 && tm == gr.m / Cfg::kTileM) {
           swap_rows = gr.swap_rows;
         }
-        if (!grouped_range(p, stages_g, role, sharers, item, swap_rows != 0)) break;
+        if (!grouped_range(p, stages_g, role, sharers, item)) break;
       } else {
         swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         pr = p.prob;
@@ -1188,7 +1187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!good) ok = false;  // still drain TMEM below so that the MMA issuer is not left waiting
       }
       if (item.kind == ITEM_CLUSTER) break;  // the accumulator is complete; the whole CTA finishes the tile below
-      if constexpr (PAIR) if (swap_rows) {
+      if constexpr (PAIR) if (swap_rows && item.kind != ITEM_PARTIAL) {  // (a contributor parks its raw sums further down)
         // Transposed partial block: TMEM lane = column of the tile (this CTA's 128 of its 256), TMEM column = row of
         // the block.  A thread holds 32 consecutive rows of one output column; for each of them the warp's 32 lanes
         // write 32 neighbouring elements of one output row.
@@ -1204,6 +1203,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld_32x32(t_lane + static_cast<uint32_t>(c * 32), r);
           tmem_ld_wait();
+          if (item.kind == ITEM_OWNER && ok) {
+            // stream-K tail: add the parts of the tile's k range that the next workers parked (raw accumulator
+            // words, the same lane / column positions whatever the tile's orientation)
+            for (int v = worker + 1; v <= sk_last; ++v) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
+                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
+                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
+                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
+                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
+              }
+            }
+          }
           if (c == chunks - 1) {
             // every row of this accumulator that exists is in registers: hand TMEM back to the MMA issuer
             tc_fence_before();
@@ -1261,8 +1275,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
         continue;
       }
+      // (a transposed block only has as many accumulator columns as it has rows)
+      const int n_chunks = (PAIR && swap_rows) ? (swap_rows + 31) >> 5 : BLOCK_N / 32;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+      for (int c = 0; c < n_chunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
@@ -1283,7 +1299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
         }
-        if (c == BLOCK_N / 32 - 1) {
+        if (c == n_chunks - 1) {
           // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
           tc_fence_before();
           __syncwarp();

@@ -81,9 +81,12 @@ def all_gather_columns(C_local: torch.Tensor, m: int, n: int, ldc: int, rank: in
     width = max(e - s for s, e in ranges)
     c2d = C_local.view(-1)[: m * ldc].view(m, ldc)
     n0, n1 = ranges[rank]
-    packed = torch.zeros(m, width, dtype=C_local.dtype, device=C_local.device)
-    if n1 > n0:
-        packed[:, : n1 - n0].copy_(c2d[:, n0:n1])
+    if n1 - n0 == width:
+        packed = c2d[:, n0:n1].contiguous()
+    else:  # a narrower (or empty) last shard travels zero-padded to the common width
+        packed = torch.zeros(m, width, dtype=C_local.dtype, device=C_local.device)
+        if n1 > n0:
+            packed[:, : n1 - n0].copy_(c2d[:, n0:n1])
     flat = torch.empty(world * m, width, dtype=C_local.dtype, device=C_local.device)  # rank-major concatenation
     dist.all_gather_into_tensor(flat, packed, group=group)
     gathered = flat.view(world, m, width)
@@ -98,9 +101,13 @@ _gather_streams = {}
 def sharded_gemm_gather(name: str, transa: int, transb: int, m: int, n: int, k: int, alpha, A: torch.Tensor, lda: int,
                         B: torch.Tensor, ldb: int, beta, C: torch.Tensor, ldc: int, rank: int, world: int,
                         align: int = 256, chunks: int = 4, group=None, launch: Optional[Callable] = None) -> None:
-    """:func:`sharded_gemm` followed by :func:`all_gather_columns`, overlapped: the GEMM runs in row blocks of
+    """:func:`sharded_gemm` followed by :func:`all_gather_columns`, by row blocks: the GEMM runs in row blocks of
     ``A`` / ``C`` on the current stream and every finished block is exchanged on a side stream while the next one
-    computes, so only the last block's exchange is exposed.  ``A``, ``B``, ``C`` are full-size operands with their
+    computes.  Measured on two B200s (fp16 8192^3, 64 MiB per rank) this is SLOWER than the GEMM followed by one
+    exchange (0.82 against 0.73 ms; the GEMM alone 0.40 ms): a quarter of the rows is 128 tiles on 74 CTA pairs, so
+    every block pays the tile quantisation the whole shard avoids, the persistent GEMM occupies every SM and leaves
+    the collective's kernels little room beside it, and the per-block packing and unpacking launches add up.  Kept
+    for callers whose shards are large enough to amortise that; ``bench.py`` reports both.  ``A``, ``B``, ``C`` are full-size operands with their
     original leading dimensions (the rank's shard of ``C`` is a strided column block of the full ``C``); afterwards
     every rank holds the complete ``C``.  Needs ``transa = N`` to cut row blocks; other layouts run the two phases
     one after the other."""

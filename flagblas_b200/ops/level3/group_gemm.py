@@ -76,7 +76,8 @@ def group_tf32gemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_s
                   d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m)
 
 
-# fp32 tensors run with TF32 tensor-core products (fp32 accumulate), like the reference's fp32 `tl.dot`
+# fp32 tensors run with TF32 tensor-core products (fp32 accumulate, rtol 1e-3): an extension -- the reference's group_mm
+# kernel forms fp32 products in IEEE fp32 (tl.dot(..., allow_tf32=False), ops/level3/group_gemm.py:656)
 _CODES = {torch.bfloat16: _lib.FB_BF16, torch.float16: _lib.FB_F16, torch.float32: _lib.FB_TF32}
 
 
