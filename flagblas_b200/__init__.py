@@ -18,6 +18,7 @@ from ._lib import FlagBlasError, device_status, reload_env  # noqa: F401
 # (src/flag_blas/config.py:35-41); here it is the pybind11 module over the C ABI.
 from . import c_operators  # noqa: E402,F401
 from . import host  # noqa: E402,F401
+from .ops.level3.group_gemm import GroupPlan, group_prepare  # noqa: E402,F401
 from .aten import all_registered_keys, all_registered_ops, enable, only_enable, use_blas  # noqa: E402,F401
 
 device = runtime.device.name
@@ -25,5 +26,5 @@ vendor_name = runtime.device.vendor_name
 __version__ = "0.1.0"
 
 __all__ = list(_ops_all) + ["runtime", "testing", "device", "vendor_name", "c_operators", "FlagBlasError",
-                            "device_status", "reload_env", "host", "enable", "only_enable", "use_blas", "all_registered_ops",
+                            "device_status", "reload_env", "host", "group_prepare", "GroupPlan", "enable", "only_enable", "use_blas", "all_registered_ops",
                             "all_registered_keys"]

@@ -63,6 +63,10 @@ def _load():
     handle.fb_gemv_fp8_workspace_bytes.argtypes = [i64, i64]
     handle.fb_group_gemm.restype = i32
     handle.fb_group_gemm.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp, sz, vp]
+    handle.fb_group_gemm_prepare.restype = i32
+    handle.fb_group_gemm_prepare.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, vp, sz, vp]
+    handle.fb_group_gemm_run.restype = i32
+    handle.fb_group_gemm_run.argtypes = [i32, i32, i32, i64, i64, i64, f32, f32, vp, sz, vp]
     handle.fb_group_gemm_no_alloc.restype = i32
     handle.fb_group_gemm_no_alloc.argtypes = [i32, i32] + [vp] * 10 + [i32, i64, i64, i64, f32, f32, vp]
     handle.fb_no_alloc_max_groups.restype = i32
@@ -107,6 +111,8 @@ EXPORTED_SYMBOLS = (
     "fb_group_gemm",
     "fb_group_mm",
     "fb_group_gemm_no_alloc",
+    "fb_group_gemm_prepare",
+    "fb_group_gemm_run",
     "fb_no_alloc_max_groups",
     "fb_group_workspace_bytes",
     "fb_group_min_workspace_bytes",

@@ -50,6 +50,17 @@ PYBIND11_MODULE(c_operators, m) {
                          cp<int32_t>(dn), cp<int32_t>(dk), cp<int32_t>(dlda), cp<int32_t>(dldb), cp<int32_t>(dldc), groups, mh, nh,
                          kh, alpha, beta, p(ws), ws_bytes, p(stream));
   });
+  m.def("group_gemm_prepare", [](int dtype, int b_k_contig, addr da, addr db, addr dc, addr dout, addr dm, addr dn, addr dk,
+                                 addr dlda, addr dldb, addr dldc, int groups, int64_t mh, int64_t nh, int64_t kh, addr ws,
+                                 size_t ws_bytes, addr stream) {
+    return fb_group_gemm_prepare(dtype, b_k_contig, cp<int64_t>(da), cp<int64_t>(db), cp<int64_t>(dc), cp<int64_t>(dout),
+                                 cp<int32_t>(dm), cp<int32_t>(dn), cp<int32_t>(dk), cp<int32_t>(dlda), cp<int32_t>(dldb),
+                                 cp<int32_t>(dldc), groups, mh, nh, kh, p(ws), ws_bytes, p(stream));
+  });
+  m.def("group_gemm_run", [](int dtype, int b_k_contig, int groups, int64_t mh, int64_t nh, int64_t kh, float alpha, float beta,
+                             addr ws, size_t ws_bytes, addr stream) {
+    return fb_group_gemm_run(dtype, b_k_contig, groups, mh, nh, kh, alpha, beta, p(ws), ws_bytes, p(stream));
+  });
   m.def("group_gemm_no_alloc", [](int dtype, int b_k_contig, addr da, addr db, addr dc, addr dout, addr dm, addr dn, addr dk,
                                   addr dlda, addr dldb, addr dldc, int groups, int64_t mh, int64_t nh, int64_t kh, float alpha,
                                   float beta, addr stream) {

@@ -165,6 +165,9 @@ struct TcGemmParams {
   // 256 h + 128 q + c holds tile column 256 q + 128 h + c); 0 = two copies of 128 columns, one per MMA half
   // (accumulator columns in tile order).  One copy instruction less per stage.
   int wide_merged;
+  // 1: the staged epilogue writes C with streaming (evict-first) stores, so that a large output does not displace the
+  // operand panels other tiles still need from L2
+  int c_streaming;
   // Optional cycle accounting (profiling builds of a call): 16 counters written by CTA 0, or null.
   long long* prof;
 };
@@ -265,7 +268,8 @@ constexpr int kEpiStageBytes = 32 * 128;
 template <class T, int BLOCK_N, class HandBack>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* stage, const Problem& pr, int row0,
                                                      int col_base, float alpha, float beta, int lane, bool zero_acc,
-                                                     HandBack hand_back, bool wide_merged = false) {
+                                                     HandBack hand_back, bool wide_merged = false,
+                                                     bool streaming = false) {
   constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
   constexpr int kLoads = kW / 32;
   constexpr int kSteps = BLOCK_N / kW;
@@ -341,8 +345,11 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
     for (int j = 0; j < 8; ++j) {
       const int lr = j * 4 + sub_row;
       const uint4 raw = ld_shared_v4(stage_addr + static_cast<uint32_t>(lr * 128 + ((unit ^ (lr & 7)) << 4)));
-      if (row0 + lr < pr.m)
-        *(reinterpret_cast<uint4*>(reinterpret_cast<T*>(pr.out) + static_cast<size_t>(row0 + lr) * pr.ldo + col0) + unit) = raw;
+      if (row0 + lr < pr.m) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pr.out) + static_cast<size_t>(row0 + lr) * pr.ldo + col0) + unit;
+        if (streaming) __stcs(dst, raw);  // evict-first: the output is not read again by this kernel
+        else *dst = raw;
+      }
     }
     __syncwarp();  // the block is rewritten by the next step
   }
@@ -1267,7 +1274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back);
         } else if (FB_STORES_ON(p) && ok) {
           epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
-                                              p.wide_merged != 0);
+                                              p.wide_merged != 0, p.c_streaming != 0);
         } else {
           hand_back();
         }

@@ -1134,11 +1134,12 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   // They need the one-copy-per-stage 3-D views of both operands.
   // Chosen by itself for large beta = 0 calls: with random data the GPU is power-limited, the smaller operand stream
   // leaves more of the budget to the tensor pipe (8192^3, 300 launches back to back: 0.955 -> 0.884 ms, SM clock
-  // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower; k = 4096 is break-even, k = 2048
-  // loses 3 %).  It needs at least four
-  // waves of tiles, and a wave count that wastes no more than the 256-wide tiling does.
+  // 1312 -> 1365 MHz; with all-zero operands, which do not throttle, it is 2 % slower).  It needs at least one full
+  // wave of tiles, and a wave count that wastes no more than the 256-wide tiling does.
   bool wide = false;
-  const bool long_k = esz == 4 ? k >= 4096 : k > 4096;  // (TF32 8192 x 8192 x 4096: +1.6 %, k = 8192: +4.2 %, k = 3072: -1.2 %)
+  // with the merged B copy and one-slab stages (bf16 8192 x 8192 x k: k = 4096 +3.1 %, 2048 -1.2 %, 1024 -15 %; TF32 TN:
+  // k = 8192 +9 %, 4096 +8 %, 2048 +1.4 %)
+  const bool long_k = esz == 4 ? k >= 2048 : k >= 4096;
   if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && long_k &&
       env_int("FLAGBLAS_B200_BLOCK_N", 0) == 0 && env_int("FLAGBLAS_B200_WIDE_TILES", 1) != 0) {
     const long long pairs = di->sm_count / 2;
@@ -1146,7 +1147,8 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     const long long t256 = rows * ((n + 255) / 256), t512 = rows * ((n + 511) / 512);
     const double e256 = static_cast<double>(t256) / static_cast<double>((t256 + pairs - 1) / pairs * pairs);
     const double e512 = static_cast<double>(t512) / static_cast<double>((t512 + pairs - 1) / pairs * pairs);
-    wide = t512 >= 4 * pairs && e512 >= e256 - 0.02 && n % 512 == 0;
+    // (at least one full wave of wide tiles: 4096^3 = 1.73 waves +3.7 %, 16384 x 1536 x 4096 = 2.6 waves +3.8 %)
+    wide = t512 >= pairs && e512 >= e256 - 0.02 && n % 512 == 0;
   }
   if (pair && a3d && b3d && (wide || env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512)) block_n = 512;
   // A 512-wide tile holds four k-slabs of 48 KB: as four one-slab stages the refill of a stage has three stages'
@@ -1208,6 +1210,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
   p.wide_merged = wide_merged ? 1 : 0;
+  p.c_streaming = env_int("FLAGBLAS_B200_C_STREAMING", 0) != 0 ? 1 : 0;
   p.wait_prior = packed ? 1 : 0;
   // Optional stream-K scratch behind the packed operands: used only when the caller provided it.
   if (dplan.want_streamk && block_n <= 256 && workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
@@ -1297,8 +1300,12 @@ size_t fb_group_workspace_bytes(int group_count) {
   return group_tail_offset(static_cast<size_t>(group_count)) + streamk_bytes(di->sm_count, 256);
 }
 
+// `phases`: kGroupBuild = run the table builder, kGroupRun = launch the GEMM over tables already in the workspace;
+// a plain call does both.
+enum : int { kGroupBuild = 1, kGroupRun = 2 };
 static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha, float beta, long long m_hint,
-                       long long n_hint, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                       long long n_hint, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                       int phases = kGroupBuild | kGroupRun) {
   const DeviceInfo* di = device_info();
   if (!di) return FB_ERR_LAUNCH;
   if (di->cc_major != 10) return FB_ERR_UNSUPPORTED;
@@ -1400,6 +1407,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   // the table builder also clears the stream-K flags (one launch less than a memset node in front of it)
   ga.clear_flags = reinterpret_cast<int*>(tail);
   ga.clear_count = tail ? static_cast<int>(kStreamKFlagBytes / sizeof(int)) : 0;
+  if (!(phases & kGroupBuild) && tail) FB_CUDA_OK(cudaMemsetAsync(tail, 0, kStreamKFlagBytes, stream));  // tables reused
 
   // The builder is itself a programmatic dependent of whatever precedes it on the stream (typically the previous
   // grouped GEMM, which reads the same tables): it becomes resident as that kernel drains and waits for its
@@ -1408,12 +1416,15 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
   int builders = (G + kSetupThreads / 32 - 1) / (kSetupThreads / 32);
   if (builders > 16) builders = 16;
   const unsigned setup_ctas = static_cast<unsigned>(builders + 1);
-  if (env_int("FLAGBLAS_B200_PDL", 1) != 0) {
-    FB_CUDA_OK(launch_dependent(group_setup_kernel, setup_ctas, kSetupThreads, stream, pass[0], pass[1], ga));
-  } else {
-    group_setup_kernel<<<setup_ctas, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
-    FB_CUDA_OK(cudaGetLastError());
+  if (phases & kGroupBuild) {
+    if (env_int("FLAGBLAS_B200_PDL", 1) != 0) {
+      FB_CUDA_OK(launch_dependent(group_setup_kernel, setup_ctas, kSetupThreads, stream, pass[0], pass[1], ga));
+    } else {
+      group_setup_kernel<<<setup_ctas, kSetupThreads, 0, stream>>>(pass[0], pass[1], ga);
+      FB_CUDA_OK(cudaGetLastError());
+    }
   }
+  if (!(phases & kGroupRun)) return FB_OK;
 
   for (int i = 0; i < 2; ++i) {
     const GroupPass& ps = pass[i];
@@ -1468,6 +1479,41 @@ int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64
   ga.num_groups = group_count;
   return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, alpha, beta, m_hint, n_hint, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
+}
+
+int fb_group_gemm_prepare(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                          const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                          const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count,
+                          int64_t m_hint, int64_t n_hint, int64_t k_hint, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  (void)k_hint;
+  if (dtype != FB_TF32 && dtype != FB_F16 && dtype != FB_BF16) return FB_ERR_INVALID_ARG;
+  if (group_count < 0) return FB_ERR_INVALID_ARG;
+  if (group_count == 0) return FB_OK;
+  if (!d_a || !d_b || !d_out || !d_m || !d_n || !d_k || !d_lda || !d_ldb || !d_ldc) return FB_ERR_INVALID_ARG;
+  GroupSetupArgs ga{};
+  ga.mode = 0;
+  ga.a_ptrs = reinterpret_cast<const long long*>(d_a);
+  ga.b_ptrs = reinterpret_cast<const long long*>(d_b);
+  ga.c_ptrs = reinterpret_cast<const long long*>(d_c ? d_c : d_out);
+  ga.out_ptrs = reinterpret_cast<const long long*>(d_out);
+  ga.m_sizes = d_m; ga.n_sizes = d_n; ga.k_sizes = d_k;
+  ga.ldas = d_lda; ga.ldbs = d_ldb; ga.ldcs = d_ldc;
+  ga.num_groups = group_count;
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, 1.f, 0.f, m_hint, n_hint, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), kGroupBuild);
+}
+
+int fb_group_gemm_run(int dtype, int b_k_contiguous, int group_count, int64_t m_hint, int64_t n_hint, int64_t k_hint,
+                      float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)k_hint;
+  if (dtype != FB_TF32 && dtype != FB_F16 && dtype != FB_BF16) return FB_ERR_INVALID_ARG;
+  if (group_count < 0) return FB_ERR_INVALID_ARG;
+  if (group_count == 0) return FB_OK;
+  GroupSetupArgs ga{};
+  ga.num_groups = group_count;
+  return run_grouped(dtype, b_k_contiguous ? 1 : 0, ga, alpha, beta, m_hint, n_hint, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), kGroupRun);
 }
 
 int fb_group_mm(int dtype, int b_k_contiguous, const void* A, int64_t lda, const void* B, int64_t ldb,

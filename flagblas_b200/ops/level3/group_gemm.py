@@ -76,6 +76,61 @@ def group_tf32gemm(group_out, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_s
                   d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs, group_size, M, N, K, alpha, beta, use_small_m)
 
 
+class GroupPlan:
+    """A grouped GEMM whose tile table and tensor maps are built once and reused by several runs
+    (``fb_group_gemm_prepare`` / ``fb_group_gemm_run``; the reference has no such split, its kernels rebuild
+    their per-group descriptors on every call).  Made by :func:`group_prepare`; ``run`` computes
+    ``out_g = alpha * A_g @ B_g + beta * C_g`` with the addresses, sizes and pitches the arrays held at
+    preparation time.  The plan owns its workspace and keeps the argument tensors alive."""
+
+    def __init__(self, code, b_k_contig, name, arrays, group_size, M, N, K):
+        self.code, self.b_k_contig, self.name = code, b_k_contig, name
+        self.arrays, self.group_size, self.hints = arrays, int(group_size), (int(M), int(N), int(K))
+        self.device = arrays[0].device
+        self.workspace = None
+        if self.group_size:
+            nbytes = _cop.group_workspace_bytes(self.group_size)
+            self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            stream, prev = _lib.enter(self.device)
+            try:
+                status = _cop.group_gemm_prepare(code, b_k_contig, *[t.data_ptr() for t in arrays], self.group_size,
+                                                 *self.hints, self.workspace.data_ptr(), nbytes, stream)
+            finally:
+                _lib.leave(prev)
+            _lib.check(status, name + " (prepare)")
+
+    def run(self, group_out, alpha, beta):
+        alpha = alpha.item() if isinstance(alpha, torch.Tensor) else float(alpha)
+        beta = beta.item() if isinstance(beta, torch.Tensor) else float(beta)
+        if self.group_size:
+            stream, prev = _lib.enter(self.device)
+            try:
+                status = _cop.group_gemm_run(self.code, self.b_k_contig, self.group_size, *self.hints, alpha, beta,
+                                             self.workspace.data_ptr(), self.workspace.numel(), stream)
+            finally:
+                _lib.leave(prev)
+            _lib.check(status, self.name)
+        return group_out
+
+
+_PLAN_KINDS = {"group_bfgemm": (_lib.FB_BF16, 0), "group_hgemm": (_lib.FB_F16, 0), "group_tf32gemm": (_lib.FB_TF32, 1)}
+
+
+def group_prepare(name, d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs,
+                  d_ldcs, group_size, M, N, K, use_small_m=False) -> GroupPlan:
+    """Build the device-side tables of ``name`` (``"group_bfgemm"``, ``"group_hgemm"`` or ``"group_tf32gemm"``) for
+    these argument arrays once; ``plan.run(group_out, alpha, beta)`` then only launches the GEMM kernel."""
+    code, b_k_contig = _PLAN_KINDS[name]
+    for t in (d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs):
+        assert t.dtype == torch.int64 and t.is_cuda and t.is_contiguous() and t.numel() >= group_size
+    for t in (d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs):
+        assert t.dtype == torch.int32 and t.is_cuda and t.is_contiguous() and t.numel() >= group_size
+    if use_small_m:
+        M = min(int(M), 64 * int(group_size)) if int(M) > 0 else 64 * int(group_size)
+    arrays = (d_a_ptrs, d_b_ptrs, d_c_ptrs, d_output_ptrs, d_m_sizes, d_n_sizes, d_k_sizes, d_ldas, d_ldbs, d_ldcs)
+    return GroupPlan(code, b_k_contig, name, arrays, group_size, M, N, K)
+
+
 # fp32 tensors run with TF32 tensor-core products (fp32 accumulate, rtol 1e-3): an extension -- the reference's group_mm
 # kernel forms fp32 products in IEEE fp32 (tl.dot(..., allow_tf32=False), ops/level3/group_gemm.py:656)
 _CODES = {torch.bfloat16: _lib.FB_BF16, torch.float16: _lib.FB_F16, torch.float32: _lib.FB_TF32}

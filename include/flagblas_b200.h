@@ -190,6 +190,26 @@ int fb_group_gemm(int dtype, int b_k_contiguous, const int64_t* d_a, const int64
                   void* stream);
 
 /*
+ * The grouped GEMM in two steps, for callers that run one grouping more than once (the layers of a model that
+ * share a routing; a benchmark loop).  (No counterpart in the reference, whose kernels rebuild their per-group
+ * descriptors on every call.)
+ *   fb_group_gemm_prepare  builds the tile table and the tensor maps of the groups in `workspace`
+ *                          (fb_group_workspace_bytes(group_count) bytes; fb_group_min_workspace_bytes for whole tiles only);
+ *   fb_group_gemm_run      runs the GEMM over a prepared workspace: out_g <- alpha * A_g * B_g + beta * C_g with the
+ *                          addresses, sizes and pitches the arrays held when prepare ran.
+ * dtype, b_k_contiguous, group_count and the three hints must be the same in both calls (they select the tile plan);
+ * the workspace must stay untouched between them; the environment switches must not change in between.
+ * fb_group_gemm(...) = prepare + run.  A beta != 0 run needs d_c to have been given to prepare.
+ */
+int fb_group_gemm_prepare(int dtype, int b_k_contiguous, const int64_t* d_a, const int64_t* d_b, const int64_t* d_c,
+                          const int64_t* d_out, const int32_t* d_m, const int32_t* d_n, const int32_t* d_k,
+                          const int32_t* d_lda, const int32_t* d_ldb, const int32_t* d_ldc, int group_count,
+                          int64_t m_hint, int64_t n_hint, int64_t k_hint, void* workspace, size_t workspace_bytes,
+                          void* stream);
+int fb_group_gemm_run(int dtype, int b_k_contiguous, int group_count, int64_t m_hint, int64_t n_hint, int64_t k_hint,
+                      float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Grouped matmul over row segments of one matrix:
  *     C[o_{g-1}:o_g, :] <- A[o_{g-1}:o_g, :] @ B[g]        (o_{-1} = 0)
  *   A [M, lda>=k]; B[g] at b + g*b_group_stride with rows `ldb` apart, stored

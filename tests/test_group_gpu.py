@@ -261,6 +261,35 @@ def test_grouped_decode_shape_small_m(kind, monkeypatch):
     _run_group(kind, [40, 200, 64, 33], 200, 136, 1.0, 0.0, seed=55, var_nk=True, use_small_m=True)
 
 
+def test_group_prepare_then_run_matches_the_plain_call():
+    """Tables and tensor maps built once (fb_group_gemm_prepare), the GEMM run several times over them
+    (fb_group_gemm_run) with different scalars and new operand data: bit for bit what the plain call gives."""
+    g = torch.Generator().manual_seed(61)
+    ms, K, N = [300, 0, 70, 512, 33, 1], 512, 384
+    E, T = len(ms), sum(ms)
+    A = torch.randn(T, K, generator=g).bfloat16().to(DEV)
+    B = (torch.randn(E * K, N, generator=g) * K ** -0.5).bfloat16().to(DEV)
+    C = torch.randn(T, N, generator=g).bfloat16().to(DEV)
+    starts = [sum(ms[:e]) for e in range(E)]
+
+    def arrays(out):
+        return (_i64([A.data_ptr() + s * K * 2 for s in starts]), _i64([B.data_ptr() + e * K * N * 2 for e in range(E)]),
+                _i64([C.data_ptr() + s * N * 2 for s in starts]), _i64([out.data_ptr() + s * N * 2 for s in starts]),
+                _i32(ms), _i32([N] * E), _i32([K] * E), _i32([K] * E), _i32([N] * E), _i32([N] * E))
+
+    out_p = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    plan = fb.group_prepare("group_bfgemm", *arrays(out_p), E, T, N, K)
+    for alpha, beta in ((1.0, 0.0), (1.5, 0.5)):
+        out_ref = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        fb.group_bfgemm(out_ref, *arrays(out_ref), E, T, N, K, alpha, beta)
+        assert plan.run(out_p, alpha, beta) is out_p
+        torch.cuda.synchronize()
+        assert torch.equal(out_p, out_ref)
+        A.mul_(0.5)          # new data in the same buffers: the plan holds addresses, not values
+    assert not torch.isnan(out_p).any()
+    assert fb.device_status() == 0
+
+
 def test_grouped_many_groups():
     _run_group("bf16", [((7 * i) % 90) for i in range(600)], 128, 256, 1.0, 0.0, seed=7)
     # more groups than the table builder keeps in shared memory (its tile counts then go through global memory)
