@@ -1,5 +1,6 @@
-"""The dense kernel's alternative configurations (single-CTA tiles, 2-D copies, one k-slab per stage,
-narrow tiles) must compute the same results as the default plan."""
+"""The dense kernel's alternative configurations (single-CTA tiles, 2-D copies, one or two k-slabs per stage,
+narrow and 512-wide tiles with the B stage fetched by one copy or two, streaming stores) must compute the same
+results as the default plan."""
 import pytest
 import torch
 
@@ -13,7 +14,11 @@ DEV = "cuda"
 @pytest.mark.parametrize("env", [{"FLAGBLAS_B200_PAIR": "0"}, {"FLAGBLAS_B200_TMA3D": "0"}, {"FLAGBLAS_B200_KS": "1"},
                                  {"FLAGBLAS_B200_BLOCK_N": "128"}, {"FLAGBLAS_B200_PAIR": "0", "FLAGBLAS_B200_BLOCK_N": "64"},
                                  {"FLAGBLAS_B200_STAGES": "2"}, {"FLAGBLAS_B200_GROUP_M": "3"},
-                                 {"FLAGBLAS_B200_BLOCK_N": "512"}, {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_KS": "1"}])
+                                 {"FLAGBLAS_B200_BLOCK_N": "512"}, {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_KS": "2"},
+                                 {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_WIDE_MERGED": "0"},
+                                 {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_WIDE_MERGED": "0", "FLAGBLAS_B200_KS": "1"},
+                                 {"FLAGBLAS_B200_BLOCK_N": "512", "FLAGBLAS_B200_C_STREAMING": "1"},
+                                 {"FLAGBLAS_B200_C_STREAMING": "1"}])
 @pytest.mark.parametrize("kind", ["bf16", "tf32"])
 def test_dense_plan_variants(env, kind, monkeypatch):
     for k, v in env.items():
