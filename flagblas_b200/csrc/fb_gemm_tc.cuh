@@ -139,7 +139,6 @@ struct TcGemmParams {
   // staging blocks, which transposed tiles do not use -- holds more stages: such calls stream every group's weights
   // once and are bound by how many bytes a CTA keeps in flight towards HBM.
   int small_m;
-  int map_prefetch;  // grouped mode: prefetch the tensor maps of the worker's next tile when it belongs to another group
   uint32_t idesc_swapped;  // instruction descriptor of such a block with N = 0 (the block's row count is added per tile)
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [workers], zeroed before the launch
@@ -871,21 +870,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mn_limit = load_a ? gr.m : gr.n;
           } else if (lane == 0) {
             fence_tensormap_acquire(map);
-          }
-          if (lane == 0 && p.map_prefetch) {
-            // The worker's next tile often belongs to another group, whose tensor map is not in the descriptor cache
-            // yet: ask for it now, a whole tile ahead of its first copy.
-            int t2, role2, sharers2;
-            if (grouped_tile(p, worker, num_workers, num_tiles, idx + 1, t2, role2, sharers2)) {
-              int g2 = g;
-              while (g2 + 1 < p.num_groups && t2 >= p.groups[g2 + 1].tile_start) ++g2;
-              if (g2 != g) {
-                const GroupRec& gn = p.groups[g2];
-                const bool swapped2 = PAIR && !p.small_m && p.swap_partial && gn.swap_rows > 0 &&
-                                      (t2 - gn.tile_start) / gn.tiles_n == gn.m / Cfg::kTileM;
-                prefetch_tensormap(&p.group_maps[3 * g2 + (load_a ? (swapped2 ? 2 : 0) : 1)]);
-              }
-            }
           }
         } else {
           swizzled_tile(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);

@@ -1441,7 +1441,6 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.num_groups = G;
     p.swap_partial = ps.swap_partial;
     p.small_m = (small_m && i == 0) ? 1 : 0;
-    p.map_prefetch = env_int("FLAGBLAS_B200_GROUP_PREFETCH", 1) != 0 ? 1 : 0;
     p.idesc_swapped = make_idesc(idesc_fmt(dtype), b_k_contig ? 0 : 1, 0, block_n, 0);  // M slot = the tile's columns
     p.groups = ps.recs;
     p.total_tiles = ps.total_tiles;
