@@ -118,6 +118,11 @@ struct TcGemmParams {
   // grouped mode (num_groups > 0): table + per-group tensor maps in global memory
   int num_groups;
   const GroupRec* groups;
+  // first tile index of every group once more, as a dense int array: a worker's next tile is typically several groups
+  // further on, and walking there through the 104-byte records costs one dependent L2 round trip per group (measured:
+  // that walk, done by the producers, the MMA issuer and the epilogue for every tile, shows in calls with many small
+  // groups); here 32 groups share a cache line
+  const int* group_starts;
   const int* total_tiles;        // written by the table builder: [0] tile count, [1] some operand is fetched by hand
   const CUtensorMap* group_maps;  // [3 * num_groups]: A_g, B_g, A_g boxed for the partial block
   // Stream-K tail (dense mode only).  When `sk_enabled`, every worker first takes `sk_dp` whole tiles
@@ -843,7 +848,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         long long raw_ld = 0;
         int mn_limit = 0;
         if (grouped) {
-          while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
+          while (g + 1 < p.num_groups && t >= __ldg(p.group_starts + g + 1)) ++g;
           const GroupRec& gr = p.groups[g];
           const int lt = t - gr.tile_start;
           tm = lt / gr.tiles_n;
@@ -1004,7 +1009,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int slab_rows = 0;  // rows between the k-slabs of the A stage (the box height of its copies)
         uint32_t idesc = p.idesc;
         if (grouped) {
-          while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
+          while (g + 1 < p.num_groups && t >= __ldg(p.group_starts + g + 1)) ++g;
           const GroupRec& gr = p.groups[g];
           const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
           if (PAIR && p.small_m) {
@@ -1126,7 +1131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int swap_rows = 0;       // > 0: the accumulator holds a row block transposed (lanes = columns of the tile)
       int tile_rows = Cfg::kTileM;
       if (grouped) {
-        while (g + 1 < p.num_groups && t >= p.groups[g + 1].tile_start) ++g;
+        while (g + 1 < p.num_groups && t >= __ldg(p.group_starts + g + 1)) ++g;
         const GroupRec& gr = p.groups[g];
         const int lt = t - gr.tile_start;
         tm = lt / gr.tiles_n;

@@ -36,6 +36,7 @@ struct GroupPass {
                      // transposed (see GroupRec::swap_rows); a third tensor map per group fetches its rows
   int block_n;
   GroupRec* recs;       // [num_groups]
+  int* starts;          // [num_groups]: first tile index of every group (the same as recs[g].tile_start, densely packed)
   int* total_tiles;     // device: [0] = tile count of the pass, [1] = 1 when some operand has no tensor map
   CUtensorMap* maps;    // [3 * num_groups]: A_g, B_g, and A_g with the box of the partial block's rows
   CUtensorMap tmpl_a, tmpl_b, tmpl_a3, tmpl_b3;  // templates: 2-D A, 2-D B, 3-D A, 3-D B
@@ -299,6 +300,7 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
       for (int g = g0; g < g1; ++g) {
         const int c = in_smem ? counts[g] : plan_group(ga, ps, load_group(ga, g)).tiles;
         ps.recs[g].tile_start = run;
+        ps.starts[g] = run;
         run += c;
       }
       __syncthreads();

@@ -1280,7 +1280,8 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
 
 // Workspace of one pass: records, the tile count, tensor maps.
 static constexpr size_t group_pass_bytes(size_t groups) {
-  return (sizeof(GroupRec) * groups + 255) / 256 * 256 + 256 + sizeof(CUtensorMap) * 3 * groups;
+  return (sizeof(GroupRec) * groups + 255) / 256 * 256 + 256 + (sizeof(int) * groups + 255) / 256 * 256 +
+         sizeof(CUtensorMap) * 3 * groups;
 }
 static constexpr size_t group_ws_bytes(size_t groups) { return 2 * group_pass_bytes(groups); }
 
@@ -1341,7 +1342,8 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     uint8_t* base = ws + i * group_pass_bytes(G);
     ps.recs = reinterpret_cast<GroupRec*>(base);
     ps.total_tiles = reinterpret_cast<int*>(base + round_up(sizeof(GroupRec) * static_cast<size_t>(G), 256));
-    ps.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ps.total_tiles) + 256);
+    ps.starts = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(ps.total_tiles) + 256);
+    ps.maps = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(ps.starts) + round_up(sizeof(int) * static_cast<size_t>(G), 256));
     ps.block_n = block_n;
   }
   // One pass of CTA-pair tiles: every whole 256-row block of a group is an ordinary tile, its last, partial block is
@@ -1443,6 +1445,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     p.small_m = (small_m && i == 0) ? 1 : 0;
     p.idesc_swapped = make_idesc(idesc_fmt(dtype), b_k_contig ? 0 : 1, 0, block_n, 0);  // M slot = the tile's columns
     p.groups = ps.recs;
+    p.group_starts = ps.starts;
     p.total_tiles = ps.total_tiles;
     p.group_maps = ps.maps;
     if (tail) {
