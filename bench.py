@@ -716,16 +716,32 @@ def main():
     else:
         Bl, Cl = B, C
     ldbl, ldcl = Bl.shape[1], Cl.shape[1]
+    from flagblas_b200 import host as fbhost
+
     hA, hB = A.cpu().pin_memory(), Bl.cpu().pin_memory()
     hC = torch.empty(Cl.shape, dtype=dt).pin_memory()
-
-    from flagblas_b200 import host as fbhost
 
     def e2e_step():
         fbhost.gemm_from_host_sharded(op, ta, tb, m, nl, k, alpha, hA, lda, hB, ldbl, beta, hC, ldcl, A, Bl, Cl, rank, world)
         torch.cuda.synchronize()
 
     e2e_step()
+    # the host result of the end-to-end call against this rank's device-resident result of the same product
+    if beta == 0:
+        dev_ref = Cl.clone()
+        if world > 1:
+            opfn(ta, tb, m, nl, k, alpha, A, lda, Bl, ldbl, beta, dev_ref, ldcl)
+        else:
+            step()
+            dev_ref = C.clone()
+        torch.cuda.synchronize()
+        e2e_checked = bool(torch.allclose(hC.to(dev).float(), dev_ref.float(), rtol=2e-3, atol=2e-3 * float(k) ** 0.5))
+        if use_dist:  # true only if it holds on every rank
+            t = torch.tensor([1 if e2e_checked else 0], device=dev)
+            tdist.all_reduce(t, op=tdist.ReduceOp.MIN)
+            e2e_checked = bool(t.item())
+    else:
+        e2e_checked = None  # (C is updated in place: every step changes the operand)
     e2e_ms = timed(e2e_step, args.e2e_steps)
     a_rows_from_host = (A.numel() // world) if (world > 1 and ta == 0 and m % world == 0) else A.numel()
     h2d = world * a_rows_from_host * esz + (n * k + (m * n if beta != 0 else 0)) * esz   # whole job, all ranks
@@ -755,7 +771,7 @@ def main():
                          "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
                          "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "checked_against_device_result": e2e_checked},
             "gpu_launches": args.steps,
             "other_configs": others,
             "clocks": clk.summary(),

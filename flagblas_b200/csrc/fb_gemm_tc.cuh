@@ -132,6 +132,8 @@ struct TcGemmParams {
   // `sk_partials` (one slot per worker) and raises `sk_flags[worker]`.  The owner's part is the longer one, by
   // about the time a contributor needs to park its sums, so that it does not have to wait for them.
   // sk_enabled == 2: stream-K over the whole launch instead (see dense_work_item).
+  // sk_enabled == 3: a last wave more than half full: `sk_rem` owners take the heads of its tiles, the other workers
+  // the tails of `sk_share` stages each, parked in one slot per tile.
   int sk_enabled, sk_dp, sk_rem, sk_group, sk_share;
   // Grouped mode takes the same tail (`sk_grouped`): the tile count is only known on the device, so the workers
   // derive the split themselves; `sk_head` = the owner's head start in stages.
@@ -146,7 +148,9 @@ struct TcGemmParams {
   int small_m;
   uint32_t idesc_swapped;  // instruction descriptor of such a block with N = 0 (the block's row count is added per tile)
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
-  int* sk_flags;       // [workers], zeroed before the launch
+  int* sk_flags;       // [slots][8]: one word per CTA of the pair and epilogue warp; a contributor's warp stores the
+                       // launch's `sk_epoch` there when its rows of the slot are parked (nothing has to be zeroed)
+  int sk_epoch;        // differs from launch to launch (and is never what a stale or cleared word holds)
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
   // by different CTAs; each writes its raw fp32 sums to `splitk_out + part * m * n` (row pitch n) and a second
   // kernel adds the parts in order and applies alpha, beta and the output cast.  For shapes with too few
@@ -269,11 +273,12 @@ constexpr int kEpiStageBytes = 32 * 128;
 // (16-byte units XOR-swizzled by the row, which keeps both directions free of bank conflicts) and
 // reads it back so that eight neighbouring lanes write one whole 128-byte row segment; the C operand
 // of a beta term comes in the same way.  Column spans that are ragged or unaligned fall back to the
-// per-thread path.  `hand_back` runs once, right after the last TMEM read.
-template <class T, int BLOCK_N, class HandBack>
+// per-thread path.  `hand_back` runs once, right after the last TMEM read; `add_parts(c, r)` may add to the 32
+// sums `r` of accumulator columns [32 c, 32 c + 32) (a stream-K owner: the parts other workers parked).
+template <class T, int BLOCK_N, class HandBack, class AddParts>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* stage, const Problem& pr, int row0,
                                                      int col_base, float alpha, float beta, int lane, bool zero_acc,
-                                                     HandBack hand_back, bool wide_merged = false,
+                                                     HandBack hand_back, AddParts add_parts, bool wide_merged = false,
                                                      bool streaming = false) {
   constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
   constexpr int kLoads = kW / 32;
@@ -313,6 +318,8 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[q][j] = 0u;
     }
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) add_parts(s * kLoads + q, r[q]);
     if (!fast) {
 #pragma unroll
       for (int q = 0; q < kLoads; ++q) epilogue_chunk<T>(r[q], pr, row0 + lane, col0 + q * 32, alpha, beta);
@@ -460,6 +467,7 @@ struct WorkItem {
   int sb, se;
   int kind;
   int part;  // ITEM_SPLIT: which k part
+  int slot;  // stream-K: >= 0 names the partial slot of the tile (one contributor); < 0: slots go by worker
 };
 
 // The idx-th work item of `worker` in dense mode (see the stream-K fields of TcGemmParams).
@@ -468,6 +476,7 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
                                                 WorkItem& it) {
   const int tiles = p.tiles_m * p.tiles_n;
   it.part = 0;
+  it.slot = -1;
   if (p.cluster_k > 1) {
     // the grid is exactly tiles x cluster_k CTAs: one work item each, the cluster rank picks the k part
     if (idx > 0) return false;
@@ -494,6 +503,35 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
     it.tile = worker + idx * workers;
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
     return it.tile < tiles;
+  }
+  if (p.sk_enabled == 3) {
+    // Last wave more than half full ("heads and tails"): after `sk_dp` whole waves the first `sk_rem` workers each own
+    // one of the remaining tiles and sweep its first stages, all in step like a whole wave, so the operand panels
+    // they share are fetched once.  The other workers are helpers: each takes the last `sk_share` stages of one
+    // owner's tile after another (helper h: tiles h, h + helpers, ...; also in step with one another), parks
+    // the partial sums in the tile's slot, and the owner adds them in its epilogue.  The owners' share is sized so
+    // that a helper's last tail is parked when the owners finish.
+    if (idx < p.sk_dp) {
+      it.tile = worker + idx * workers;
+      it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
+      return true;
+    }
+    const int j = idx - p.sk_dp;
+    const int first = p.sk_dp * workers;
+    const int owner_len = stages - p.sk_share;
+    if (worker < p.sk_rem) {
+      if (j > 0) return false;
+      it.tile = first + worker;
+      it.sb = 0; it.se = owner_len; it.kind = ITEM_OWNER;
+      it.slot = worker;
+      return true;
+    }
+    const int tl = worker - p.sk_rem + j * (workers - p.sk_rem);
+    if (tl >= p.sk_rem) return false;
+    it.tile = first + tl;
+    it.sb = owner_len; it.se = stages; it.kind = ITEM_PARTIAL;
+    it.slot = tl;
+    return true;
   }
   if (p.sk_enabled == 2) {
     // Few waves, the last one more than half full: the first `sk_dp` waves run whole tiles, all workers sweeping k
@@ -581,6 +619,7 @@ __device__ __forceinline__ bool grouped_tile(const TcGemmParams& p, int worker, 
 // splitting is done whole by its owner; false tells a contributor that it has nothing to do.
 __device__ __forceinline__ bool grouped_range(const TcGemmParams& p, int stages, int role, int sharers, WorkItem& it) {
   it.part = 0;
+  it.slot = -1;
   const int share = sharers > 1 ? (stages - p.sk_head) / sharers : 0;
   if (role < 0 || share < 2) {
     it.sb = 0; it.se = stages; it.kind = ITEM_FULL;
@@ -1113,10 +1152,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int g = 0;
     bool ok = true;
     long long prof_ewait = 0, prof_ebody = 0;
-    constexpr int kSkWarps = PAIR ? 8 : 4;  // epilogue warps that park one work item's partials
     for (int idx = 0; ok; ++idx) {
       WorkItem item;
       item.kind = ITEM_FULL;
+      item.slot = -1;
       int t, role = -1, sharers = p.sk_group;
       if (grouped) {
         if (!grouped_tile(p, worker, num_workers, num_tiles, idx, t, role, sharers)) break;
@@ -1165,25 +1204,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row = row_base + tm * Cfg::kTileM + static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
-      // Stream-K: this thread's row inside a worker's partial slot, and for an owner the workers
-      // (worker + 1 .. sk_last) that hold the rest of the tile's k range.
+      // Stream-K: this thread's row inside a partial slot, for an owner the slots (sk_first .. sk_last) that hold
+      // the rest of the tile's k range, for a contributor the slot it parks in (its own, or the tile's).
       // Layout of a slot: [16-byte unit of the row][row of the tile], so that the 32 rows of a warp sit side by
       // side and every access of a warp covers 512 consecutive bytes.
       const size_t sk_row = static_cast<size_t>(static_cast<int>(cta_rank) * kBlockM + lane_group * 32 + lane);
       constexpr size_t kSkSlot = static_cast<size_t>(Cfg::kTileM) * BLOCK_N;
-      int sk_last = worker;
+      int sk_first = worker + 1, sk_last = worker, sk_park = worker;
+      if (item.slot >= 0) { sk_first = sk_park = item.slot; sharers = 2; }
       if (item.kind == ITEM_OWNER) {
         if (!grouped && p.sk_enabled == 2) sharers = item.part;
-        sk_last = worker + sharers - 1;
-        // wait (bounded) until every contributor has parked its partial sums
+        sk_last = sk_first + sharers - 2;
+        // wait (bounded) until every contributor has parked the rows this warp needs
         uint32_t good = 1;
         if (lane == 0) {
           const long long w0 = clock64();
-          for (int v = worker + 1; v <= sk_last && good; ++v) {
+          for (int v = sk_first; v <= sk_last && good; ++v) {
+            const int* flag = p.sk_flags + v * 8 + static_cast<int>(cta_rank) * 4 + lane_group;
             while (true) {
               int f;
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.sk_flags + v) : "memory");
-              if (f >= kSkWarps) break;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
+              if (f == p.sk_epoch) break;
               if (*abort_flag) { good = 0; break; }
               if (clock64() - w0 > FB_WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
@@ -1218,7 +1259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (item.kind == ITEM_OWNER && ok) {
             // stream-K tail: add the parts of the tile's k range that the next workers parked (raw accumulator
             // words, the same lane / column positions whatever the tile's orientation)
-            for (int v = worker + 1; v <= sk_last; ++v) {
+            for (int v = sk_first; v <= sk_last; ++v) {
               const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
@@ -1258,7 +1299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
         continue;
       }
-      if (item.kind == ITEM_FULL || item.kind == ITEM_SPLIT) {
+      if (item.kind != ITEM_PARTIAL) {
         // the usual case: this warp's 32 rows leave through its staging block as whole row segments
         uint8_t* stage = epi_staging + (warp - kEpiWarp0) * kEpiStageBytes;
         const int row0 = row - lane;
@@ -1271,22 +1312,74 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             else mbar_arrive(&tmem_empty_bar[acc]);
           }
         };
+        auto nothing_to_add = [](int, uint32_t (&)[32]) {};
         if (item.kind == ITEM_SPLIT) {
           Problem part = pr;
           part.out = p.splitk_out + static_cast<size_t>(item.part) * pr.m * pr.n;
           part.ldo = pr.n; part.cin = nullptr; part.ldcin = 0;
           part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
-          epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back);
-        } else if (FB_STORES_ON(p) && ok) {
-          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
-                                              p.wide_merged != 0, p.c_streaming != 0);
-        } else {
+          epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back,
+                                               nothing_to_add);
+        } else if (!(FB_STORES_ON(p) && ok)) {
           hand_back();
+        } else if (item.kind == ITEM_OWNER) {
+          // stream-K: add the parts of the tile's k range that other workers parked (raw accumulator words).
+          // Read with plain loads the 64 KB to 128 KB of a part cost a latency per batch of eight; when this is the
+          // worker's last item (no copy will touch the operand ring again: its MMAs are complete) the first part is
+          // first brought into the ring with asynchronous 16-byte copies, all in flight at once, each thread
+          // fetching exactly the words it will read back.
+          constexpr bool kRingHoldsPart = Cfg::kStages * Cfg::kStageBytes >= kBlockM * BLOCK_N * 4;
+          bool in_ring = false;
+          const uint32_t ring_row = smem_u32(ring) + static_cast<uint32_t>(lane_group * 32 + lane) * 16u;
+          if constexpr (kRingHoldsPart) {
+            WorkItem nxt;
+            int t2, role2, sh2;
+            const bool last_item = grouped ? !grouped_tile(p, worker, num_workers, num_tiles, idx + 1, t2, role2, sh2)
+                                           : !dense_work_item(p, worker, num_workers, dense_stages, idx + 1, nxt);
+            if (last_item && !p.small_m) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_partials + sk_first * kSkSlot) + sk_row;
+#pragma unroll 16
+              for (int u = 0; u < BLOCK_N / 4; ++u)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_row + static_cast<uint32_t>(u * kBlockM * 16)),
+                             "l"(src + static_cast<size_t>(u) * Cfg::kTileM) : "memory");
+              asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+              in_ring = true;
+            }
+          }
+          auto add_parked = [&](int c, uint32_t (&r)[32]) {
+            if (in_ring) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint4 x = ld_shared_v4(ring_row + static_cast<uint32_t>((c * 8 + q) * kBlockM * 16));
+                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + __uint_as_float(x.x));
+                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + __uint_as_float(x.y));
+                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + __uint_as_float(x.z));
+                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + __uint_as_float(x.w));
+              }
+            }
+            for (int v = in_ring ? sk_first + 1 : sk_first; v <= sk_last; ++v) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
+                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
+                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
+                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
+                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
+              }
+            }
+          };
+          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
+                                              add_parked);
+        } else {
+          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
+                                              nothing_to_add, p.wide_merged != 0, p.c_streaming != 0);
         }
         if (p.prof) prof_ebody += clock64() - e1;
         if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
         continue;
       }
+      // A contributor of a stream-K tile parks its raw fp32 partial sums in a slot.
       // (a transposed block only has as many accumulator columns as it has rows)
       const int n_chunks = (PAIR && swap_rows) ? (swap_rows + 31) >> 5 : BLOCK_N / 32;
 #pragma unroll 1
@@ -1298,19 +1391,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (item.kind == ITEM_OWNER && ok) {
-          for (int v = worker + 1; v <= sk_last; ++v) {
-            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
-              r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
-              r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
-              r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
-              r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
-            }
-          }
-        }
         if (c == n_chunks - 1) {
           // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
           tc_fence_before();
@@ -1320,22 +1400,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             else mbar_arrive(&tmem_empty_bar[acc]);
           }
         }
-        if (item.kind == ITEM_PARTIAL) {
-          // park the raw fp32 partial sums in this worker's slot
-          float4* dst = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot) + sk_row;
+        float4* dst = reinterpret_cast<float4*>(p.sk_partials + sk_park * kSkSlot) + sk_row;
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            __stcg(dst + static_cast<size_t>(c * 8 + q) * Cfg::kTileM, make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]),
-                                        __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3])));
-        } else if (FB_STORES_ON(p) && ok) {
-          epilogue_chunk<OutT>(r, pr, row, tn * BLOCK_N + c * 32, p.alpha, p.beta);
-        }
+        for (int q = 0; q < 8; ++q)
+          __stcg(dst + static_cast<size_t>(c * 8 + q) * Cfg::kTileM,
+                 make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                             __uint_as_float(r[q * 4 + 3])));
       }
-      if (item.kind == ITEM_PARTIAL) {
-        __threadfence();  // the partial sums are visible GPU-wide before the flag says so
-        __syncwarp();
-        if (lane == 0) atomicAdd(p.sk_flags + worker, 1);
-      }
+      __threadfence();  // the partial sums are visible GPU-wide before the flag says so
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + sk_park * 8 + static_cast<int>(cta_rank) * 4 + lane_group),
+                     "r"(p.sk_epoch) : "memory");
       if (p.prof) prof_ebody += clock64() - e1;
       if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }

@@ -68,8 +68,6 @@ struct GroupSetupArgs {
   int span;        // elements per 128 bytes
   int allow3d;     // build 3-D views where a group's extents allow it
   int force_by_hand;  // 1: fetch every operand with ordinary loads, aligned or not (tests, comparisons)
-  int* clear_flags;   // stream-K flags of the GEMM that follows (or null): zeroed here
-  int clear_count;
   int publish_each;  // 1: publish every map with its own copy-and-fence instruction (profiling comparison)
 };
 
@@ -271,7 +269,6 @@ group_setup_kernel(const __grid_constant__ GroupPass pass0, const __grid_constan
   grid_dependency_wait();
 
   if (scanner) {
-    for (int i = tid; i < ga.clear_count; i += kSetupThreads) ga.clear_flags[i] = 0;
     for (int pi = 0; pi < 2; ++pi) {
       const GroupPass& ps = pi == 0 ? pass0 : pass1;
       if (!ps.enabled) continue;

@@ -273,7 +273,7 @@ static int choose_block_n(long long m, long long n, int tile_m, int workers, boo
 }
 
 
-constexpr size_t kStreamKFlagBytes = 1024;  // one int per worker (at most 148), padded
+constexpr size_t kStreamKFlagBytes = 8192;  // eight ints per slot (at most 148 slots), padded
 
 // Bytes of stream-K scratch for a dense call: one fp32 partial tile per worker plus the flags.
 static size_t streamk_bytes(int sm_count, int block_n) {
@@ -285,6 +285,34 @@ struct KernelState {
   bool attr_set = false;
   int max_clusters = 0;  // PAIR only: CTA pairs that can be co-resident
 };
+
+// A last wave of `rem` tiles on `workers` workers that is more than half full leaves workers - rem of them idle for
+// a whole tile time.  Those "helpers" can take the tails of the wave's tiles instead: each sweeps the last x k-slabs
+// (128-byte chunks of k) of q = ceil(rem / helpers) tiles, one after the other, and parks the sums for the tile's
+// owner, which sweeps the first slabs - x.  x balances the two: slabs - x = q * x + head, `head` being the time a
+// helper needs to park its last partial tile.  Returns x (even: whole two-slab stages), or 0 where a tail would be
+// too short to pay for the owner's fix-up (FLAGBLAS_B200_SK_TAIL_MIN, in slabs) or the plan is switched off
+// (FLAGBLAS_B200_STREAMK_TAILS=0).
+static long long tail_slabs(long long slabs, long long workers, long long rem);
+
+// Value a stream-K launch stores in its flags: another one for every launch of the process, and neither 0 nor a
+// small number that uninitialised or cleared scratch is likely to hold, so that the flags never need zeroing.
+static int next_streamk_epoch() {
+  static std::atomic<uint32_t> counter{0};
+  return static_cast<int>(0x5EED0000u + (counter.fetch_add(1, std::memory_order_relaxed) & 0x0FFFFFFFu) * 2u + 1u);
+}
+
+static long long tail_slabs(long long slabs, long long workers, long long rem) {
+  if (rem <= 0 || 2 * rem <= workers || rem >= workers) return 0;
+  if (env_int("FLAGBLAS_B200_STREAMK_TAILS", 1) == 0) return 0;
+  const long long helpers = workers - rem;
+  const long long q = (rem + helpers - 1) / helpers;
+  // (measured, fp16 8192 x 1024 x 8192 in a loop: 113.7 / 112.7 / 111.5 us at head = 4 / 12 / 20, whole tiles 114.0)
+  const long long head = env_int("FLAGBLAS_B200_SK_TAIL_HEAD", 20);
+  long long x = (slabs - head) / (q + 1);
+  x &= ~1LL;
+  return x >= env_int("FLAGBLAS_B200_SK_TAIL_MIN", 24) ? x : 0;
+}
 
 template <int KIND, int BLOCK_N, bool PAIR>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, long long tiles,
@@ -363,7 +391,15 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
       pp.sk_rem = static_cast<int>(rem);
       pp.sk_group = static_cast<int>(group);
       pp.sk_share = static_cast<int>(share);
-      FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
+    } else if (tail_slabs(stages * p.ks, workers, rem) / p.ks > 0 && BLOCK_N <= 256 &&
+               env_int("FLAGBLAS_B200_STREAMK_FULL", 0) == 0) {
+      // Last wave more than half full (one rank's share of an 8192^3 GEMM sharded over eight GPUs: 128 tiles on 74 CTA
+      // pairs): whole tiles would leave (workers - rem) workers idle for a whole tile time.  The idle workers
+      // take the last stages of the wave's tiles instead (dense_work_item, sk_enabled == 3).
+      pp.sk_enabled = 3;
+      pp.sk_dp = static_cast<int>(dp);
+      pp.sk_rem = static_cast<int>(rem);
+      pp.sk_share = static_cast<int>(tail_slabs(stages * p.ks, workers, rem) / p.ks);
     } else if (rem > 0 && 2 * rem > workers && dp >= 1 && dp <= 2 && stages >= 16 && BLOCK_N <= 256 &&
                env_int("FLAGBLAS_B200_STREAMK_FULL", 0) != 0) {
       // Two or three waves of which the last is more than half full (one rank's share of a GEMM sharded over eight
@@ -375,10 +411,10 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
       // kernel, and with =2 the workers no longer sweep k in step, so shared operand panels leave L2 between uses.
       pp.sk_enabled = 2;
       pp.sk_dp = env_int("FLAGBLAS_B200_STREAMK_FULL", 0) == 2 ? 0 : static_cast<int>(dp);
-      FB_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, stream));
     }
   }
   if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
+  if (pp.sk_enabled || pp.sk_grouped) pp.sk_epoch = next_streamk_epoch();
 #ifdef FB_PROFILING_SWITCHES
   pp.debug = env_int("FLAGBLAS_B200_DEBUG_SKIP", 0);
 #else
@@ -711,6 +747,10 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const long long dp = pl.tiles / split_workers, rem = pl.tiles - dp * split_workers;
   pl.want_streamk = rem > 0 && dp < 9 && 2 * rem <= split_workers && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
                     stages >= env_int("FLAGBLAS_B200_SK_MIN_STAGES", 32) && env_int("FLAGBLAS_B200_STREAMK", 1) != 0;
+  // ... or, for a last wave more than half full, its tiles' last stages go to the workers it leaves idle
+  if (tail_slabs((k + span - 1) / span, split_workers, rem) > 0 && pl.cluster_k == 1 && pl.splitk == 1 && pl.block_n <= 256 &&
+      env_int("FLAGBLAS_B200_STREAMK", 1) != 0)
+    pl.want_streamk = true;
   // ... or stream-K over the whole launch: two or three waves, the last more than half full (see launch_tc)
   if (rem > 0 && 2 * rem > split_workers && dp >= 1 && dp <= 2 && stages >= 16 && pl.cluster_k == 1 && pl.splitk == 1 &&
       pl.block_n <= 256 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 && env_int("FLAGBLAS_B200_STREAMK_FULL", 0) != 0)
@@ -1407,9 +1447,6 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
     tail = ws + group_tail_offset(static_cast<size_t>(G));
   }
   // the table builder also clears the stream-K flags (one launch less than a memset node in front of it)
-  ga.clear_flags = reinterpret_cast<int*>(tail);
-  ga.clear_count = tail ? static_cast<int>(kStreamKFlagBytes / sizeof(int)) : 0;
-  if (!(phases & kGroupBuild) && tail) FB_CUDA_OK(cudaMemsetAsync(tail, 0, kStreamKFlagBytes, stream));  // tables reused
 
   // The builder is itself a programmatic dependent of whatever precedes it on the stream (typically the previous
   // grouped GEMM, which reads the same tables): it becomes resident as that kernel drains and waits for its

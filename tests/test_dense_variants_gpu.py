@@ -110,6 +110,39 @@ def test_stream_k_over_the_last_wave(kind, ta, tb, m, n, k, monkeypatch):
         assert_parity(outs[mode], ref, KINDS[kind][2], sc, "last-wave stream-k=%s %s %dx%dx%d" % (mode, kind, m, n, k))
 
 
+@pytest.mark.parametrize("kind,ta,tb,m,n,k", [
+    ("fp16", 0, 0, 8192, 1024, 8192),    # one whole wave, then 54 tiles on 74 CTA pairs: 20 helpers, three tails each
+    ("bf16", 0, 1, 2560, 1280, 8192),    # 50 tiles: no whole wave before the shared one
+    ("tf32", 1, 0, 2048, 4096, 8192),    # 128 tiles, 256 k-slabs
+    ("bf16", 0, 0, 5000, 1500, 8192),    # 120 tiles with ragged edge tiles: 28 helpers, two tails each
+])
+def test_tails_of_a_last_wave_go_to_idle_workers(kind, ta, tb, m, n, k, monkeypatch):
+    """A last wave more than half full: the workers it would leave idle take the last k stages of its tiles
+    (FLAGBLAS_B200_STREAMK_TAILS=0 keeps whole tiles).  Both plans agree with the fp64 product."""
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=35, scale=0.25)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("FLAGBLAS_B200_STREAMK_TAILS", mode)
+        fb.reload_env()
+        Cd = C.to(DEV)
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        outs[mode] = Cd.float().cpu()
+    sc = result_scale(k, A, B, 1.5) + 0.5
+    opA = (Ad.t() if ta else Ad).double()
+    opB = (Bd.t() if tb else Bd).double()
+    if kind == "tf32":
+        trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+        opA, opB = trunc(opA), trunc(opB)
+    ref = (1.5 * (opA @ opB) + 0.5 * C.to(DEV).double()).float().cpu()
+    for mode in ("0", "1"):
+        assert_parity(outs[mode], ref, KINDS[kind][2], sc, "tails=%s %s %dx%dx%d" % (mode, kind, m, n, k))
+    assert not torch.equal(outs["0"], outs["1"])  # another summation order somewhere: the second plan really ran
+
+
 @pytest.mark.parametrize("kind,ta,tb,m,n,k,beta", [
     ("bf16", 0, 1, 16, 4096, 4096, 0.0),     # a few tokens against a square weight matrix, stored [n, k]
     ("bf16", 0, 0, 64, 2048, 8192, 0.5),     # stored [k, n], beta != 0
