@@ -1189,6 +1189,12 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     const double e512 = static_cast<double>(t512) / static_cast<double>((t512 + pairs - 1) / pairs * pairs);
     // (at least one full wave of wide tiles: 4096^3 = 1.73 waves +3.7 %, 16384 x 1536 x 4096 = 2.6 waves +3.8 %)
     wide = t512 >= pairs && e512 >= e256 - 0.02 && n % 512 == 0;
+    // ... or a single wave of them more than three quarters full, where 256-wide tiles make two waves of which the
+    // second is more than half full (one rank's share of 8192^3 over eight GPUs, fp16 8192 x 1024 x 8192: 103.0 us
+    // against 112.8 with the narrow tiles' last stages dealt to the idle workers and 114.6 with whole narrow tiles;
+    // 4096 x 2048 x 8192 100.9 against 109.3; 8192 x 1024 x 4096 55.6 against 59.4).  Less full than that the
+    // narrow tiles' stream-K tail wins (6144 x 1024 x 8192, 48 wide tiles: 94.4 against 89.8 us).
+    if (t512 < pairs && 4 * t512 > 3 * pairs && n % 512 == 0) wide = true;
   }
   if (pair && a3d && b3d && (wide || env_int("FLAGBLAS_B200_BLOCK_N", 0) == 512)) block_n = 512;
   // A 512-wide tile holds four k-slabs of 48 KB: as four one-slab stages the refill of a stage has three stages'

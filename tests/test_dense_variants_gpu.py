@@ -143,6 +143,34 @@ def test_tails_of_a_last_wave_go_to_idle_workers(kind, ta, tb, m, n, k, monkeypa
     assert not torch.equal(outs["0"], outs["1"])  # another summation order somewhere: the second plan really ran
 
 
+@pytest.mark.parametrize("kind,ta,tb,m,n,k", [
+    ("fp16", 0, 0, 8192, 1024, 8192),    # 64 tiles of 256 x 512 on 74 CTA pairs (one rank's share of 8192^3 over eight GPUs)
+    ("bf16", 0, 1, 4096, 2048, 4096),    # the same count, K-contiguous B
+    ("tf32", 1, 0, 4096, 2048, 2048),    # TF32, A transposed
+])
+def test_single_wave_of_wide_tiles(kind, ta, tb, m, n, k, monkeypatch):
+    """beta = 0 calls whose 512-wide tiles fill more than three quarters of one wave take them instead of two waves of
+    256-wide tiles (FLAGBLAS_B200_WIDE_TILES=0 keeps the narrow ones): both agree with the fp64 product."""
+    A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=37, scale=0.25)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    op = getattr(fb, KINDS[kind][1])
+    opA = (Ad.t() if ta else Ad).double()
+    opB = (Bd.t() if tb else Bd).double()
+    if kind == "tf32":
+        trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
+        opA, opB = trunc(opA), trunc(opB)
+    ref = (1.5 * (opA @ opB)).float().cpu()
+    sc = result_scale(k, A, B, 1.5)
+    for mode in ("1", "0"):
+        monkeypatch.setenv("FLAGBLAS_B200_WIDE_TILES", mode)
+        fb.reload_env()
+        Cd = torch.full((m, ldc), float("nan"), dtype=C.dtype, device=DEV)  # beta = 0 must not read C
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.0, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], sc, "wide=%s %s %dx%dx%d" % (mode, kind, m, n, k))
+
+
 @pytest.mark.parametrize("kind,ta,tb,m,n,k,beta", [
     ("bf16", 0, 1, 16, 4096, 4096, 0.0),     # a few tokens against a square weight matrix, stored [n, k]
     ("bf16", 0, 0, 64, 2048, 8192, 0.5),     # stored [k, n], beta != 0
