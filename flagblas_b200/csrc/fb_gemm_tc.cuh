@@ -151,6 +151,7 @@ struct TcGemmParams {
   int* sk_flags;       // [slots][8]: one word per CTA of the pair and epilogue warp; a contributor's warp stores the
                        // launch's `sk_epoch` there when its rows of the slot are parked (nothing has to be zeroed)
   int sk_epoch;        // differs from launch to launch (and is never what a stale or cleared word holds)
+  int c_tma;           // dense, beta = 0: whole tiles leave through TMA stores described by the kernel's third map
   // Split-K (dense mode only, `splitk` > 1): every tile's k range is cut into `splitk` contiguous parts handled
   // by different CTAs; each writes its raw fp32 sums to `splitk_out + part * m * n` (row pitch n) and a second
   // kernel adds the parts in order and applies alpha, beta and the output cast.  For shapes with too few
@@ -364,6 +365,74 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
       }
     }
     __syncwarp();  // the block is rewritten by the next step
+  }
+}
+
+// The same for beta = 0 when C can be described by a tensor map (`c_map`: base and row pitch multiples of 16 bytes):
+// the warp writes its 32 rows x 128 bytes of a step into one of its two staging blocks (the 128-byte swizzle the map
+// declares is the XOR the staged path uses anyway) and one lane hands the block to the TMA unit, which writes the row
+// segments and clips them at the matrix edge.  The warp neither reads the block back nor issues the global stores,
+// and with two blocks it fills one while the other drains: what a tile's epilogue keeps the accumulator busy for is
+// about the TMEM reads and the conversion.  `seq` counts this warp's steps over the whole kernel (block = seq & 1).
+template <class T, int BLOCK_N, class HandBack, class AddParts>
+__device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* blocks, const void* c_map, int m, int n, int row0,
+                                                  int col_base, float alpha, int lane, bool zero_acc, HandBack hand_back,
+                                                  AddParts add_parts, bool wide_merged, uint32_t& seq) {
+  constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
+  constexpr int kLoads = kW / 32;
+  constexpr int kSteps = BLOCK_N / kW;
+  constexpr int kPerVec = 16 / static_cast<int>(sizeof(T));
+  const uint32_t base = smem_u32(blocks);
+#pragma unroll 1
+  for (int s = 0; s < kSteps; ++s) {
+    int acc_col = s * kW;  // accumulator column of this step -> column of the tile
+    if (BLOCK_N == 512 && wide_merged) acc_col = ((acc_col >> 7) & 1) * 256 + (acc_col >> 8) * 128 + (acc_col & 127);
+    uint32_t r[kLoads][32];
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) tmem_ld_32x32(t_row + static_cast<uint32_t>(s * kW + q * 32), r[q]);
+    tmem_ld_wait();
+    if (s == kSteps - 1) hand_back();
+    if (zero_acc) {
+#pragma unroll
+      for (int q = 0; q < kLoads; ++q)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[q][j] = 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < kLoads; ++q) add_parts(s * kLoads + q, r[q]);
+    const uint32_t blk = base + (seq & 1u) * static_cast<uint32_t>(kEpiStageBytes);
+    ++seq;
+    // the store that read this block two steps ago must be done reading it (only lane 0 owns bulk groups)
+    if (lane == 0) bulk_wait_group_read<1>();
+    __syncwarp();
+    const uint32_t own_row = blk + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float v[kPerVec];
+#pragma unroll
+      for (int j = 0; j < kPerVec; ++j) {
+        const int e = u * kPerVec + j;  // column of this step
+        v[j] = alpha * __uint_as_float(r[e >> 5][e & 31]);
+      }
+      uint4 raw;
+      if constexpr (sizeof(T) == 4) {
+        raw.x = __float_as_uint(v[0]); raw.y = __float_as_uint(v[1]);
+        raw.z = __float_as_uint(v[2]); raw.w = __float_as_uint(v[3]);
+      } else {
+        raw.x = pack2(from_f32<T>(v[0]), from_f32<T>(v[1]));
+        raw.y = pack2(from_f32<T>(v[2]), from_f32<T>(v[3]));
+        raw.z = pack2(from_f32<T>(v[4]), from_f32<T>(v[5]));
+        raw.w = pack2(from_f32<T>(v[6]), from_f32<T>(v[7]));
+      }
+      st_shared_v4(own_row + static_cast<uint32_t>((u ^ (lane & 7)) << 4), raw);
+    }
+    fence_proxy_async();  // this thread's writes to the block, before the TMA unit reads it
+    __syncwarp();
+    const int col0 = col_base + acc_col;
+    if (lane == 0 && row0 < m && col0 < n) {
+      tma_store_2d(c_map, blk, col0, row0);
+      bulk_commit_group();
+    }
   }
 }
 
@@ -747,7 +816,7 @@ struct TcCfg {
   static constexpr int kBBytes = kBRows * kSwizzleBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kCtlBytes = 1024;
-  static constexpr int kEpiBytes = 4 * kEpiStageBytes;  // staging blocks of the four epilogue warps
+  static constexpr int kEpiBytes = 8 * kEpiStageBytes;  // two staging blocks for each of the four epilogue warps
   static constexpr int kStages = (kSmemLimit - 1024 - kCtlBytes - kEpiBytes) / kStageBytes > 8
                                      ? 8
                                      : (kSmemLimit - 1024 - kCtlBytes - kEpiBytes) / kStageBytes;
@@ -768,7 +837,7 @@ struct TcCfg {
 template <int KIND, int BLOCK_N, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const TcGemmParams p) {
+               const __grid_constant__ CUtensorMap tmC, const TcGemmParams p) {
   using Cfg = TcCfg<KIND, BLOCK_N, PAIR>;
   using OutT = typename OutOf<KIND>::T;
   constexpr bool kTf32 = (KIND == 2);
@@ -1152,6 +1221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int g = 0;
     bool ok = true;
     long long prof_ewait = 0, prof_ebody = 0;
+    uint32_t epi_seq = 0;  // steps this warp has passed through its staging blocks (TMA-store epilogue)
     for (int idx = 0; ok; ++idx) {
       WorkItem item;
       item.kind = ITEM_FULL;
@@ -1301,7 +1371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       if (item.kind != ITEM_PARTIAL) {
         // the usual case: this warp's 32 rows leave through its staging block as whole row segments
-        uint8_t* stage = epi_staging + (warp - kEpiWarp0) * kEpiStageBytes;
+        uint8_t* stage = epi_staging + (warp - kEpiWarp0) * 2 * kEpiStageBytes;  // (this warp's two blocks)
         const int row0 = row - lane;
         auto hand_back = [&]() {
           // every column of this accumulator is in registers: hand TMEM back to the MMA issuer
@@ -1369,8 +1439,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             }
           };
-          epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
-                                              add_parked);
+          if (p.c_tma)
+            epilogue_tile_tma<OutT, BLOCK_N>(t_row, stage, &tmC, pr.m, pr.n, row0, tn * BLOCK_N, p.alpha, lane, k_is_zero,
+                                             hand_back, add_parked, false, epi_seq);
+          else
+            epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero,
+                                                hand_back, add_parked);
+        } else if (p.c_tma) {
+          epilogue_tile_tma<OutT, BLOCK_N>(t_row, stage, &tmC, pr.m, pr.n, row0, tn * BLOCK_N, p.alpha, lane, k_is_zero,
+                                           hand_back, nothing_to_add, p.wide_merged != 0, epi_seq);
         } else {
           epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero, hand_back,
                                               nothing_to_add, p.wide_merged != 0, p.c_streaming != 0);
@@ -1415,6 +1492,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (p.prof) prof_ebody += clock64() - e1;
       if (++acc == Cfg::kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
+    if (p.c_tma && lane == 0) bulk_wait_group<0>();  // this warp's stores have left its staging blocks and landed
     if (p.prof && blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
       p.prof[7] = prof_ewait; p.prof[8] = prof_ebody;
       p.prof[14] = clock64();  // timeline: last store issued

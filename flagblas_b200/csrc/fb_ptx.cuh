@@ -177,6 +177,25 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
       : "memory");
 }
 
+// 2-D tiled store this CTA's shared memory -> global, as one bulk group per call site's commit.  The box is clipped
+// at the tensor's extents; x * element size must be a multiple of 16 bytes, and neither coordinate negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups are still reading their shared-memory source ...
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// ... or until at most N of them are not yet complete (writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Same, issued from either CTA of a 2-CTA pair: the data lands in the issuing
 // CTA's shared memory, the byte count is credited to the barrier at
 // `bar_cluster_addr`, which may live in the pair's leader CTA.

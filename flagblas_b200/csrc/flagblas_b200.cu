@@ -315,7 +315,7 @@ static long long tail_slabs(long long slabs, long long workers, long long rem) {
 }
 
 template <int KIND, int BLOCK_N, bool PAIR>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, long long tiles,
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcGemmParams& p, long long tiles,
                      int sm_count, cudaStream_t stream) {
   using Cfg = TcCfg<KIND, BLOCK_N, PAIR>;
   auto kern = gemm_tc_kernel<KIND, BLOCK_N, PAIR>;
@@ -430,24 +430,24 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmP
   pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
   if (pp.stages < 1 || pp.stages > max_stages) pp.stages = max_stages;
   pp.prof = g_prof_buffer;
-  FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, pp));
+  FB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, pp));
   return FB_OK;
 }
 
 // tiles < 0: grouped mode, the tile count lives on the device -> one worker per SM.
 static int dispatch_tc(int dtype, int block_n, bool pair, const CUtensorMap& ma, const CUtensorMap& mb,
-                       const TcGemmParams& p, long long tiles, int sm_count, cudaStream_t stream) {
+                       const CUtensorMap& mc, const TcGemmParams& p, long long tiles, int sm_count, cudaStream_t stream) {
   if (tiles < 0) tiles = 1LL << 40;
 #define FB_CASE(KIND)                                                                              \
   if (pair) {                                                                                      \
-    if (block_n == 512) return launch_tc<KIND, 512, true>(ma, mb, p, tiles, sm_count, stream);     \
-    if (block_n == 256) return launch_tc<KIND, 256, true>(ma, mb, p, tiles, sm_count, stream);     \
-    return launch_tc<KIND, 128, true>(ma, mb, p, tiles, sm_count, stream);                         \
+    if (block_n == 512) return launch_tc<KIND, 512, true>(ma, mb, mc, p, tiles, sm_count, stream); \
+    if (block_n == 256) return launch_tc<KIND, 256, true>(ma, mb, mc, p, tiles, sm_count, stream); \
+    return launch_tc<KIND, 128, true>(ma, mb, mc, p, tiles, sm_count, stream);                     \
   }                                                                                                \
   switch (block_n) {                                                                               \
-    case 256: return launch_tc<KIND, 256, false>(ma, mb, p, tiles, sm_count, stream);              \
-    case 128: return launch_tc<KIND, 128, false>(ma, mb, p, tiles, sm_count, stream);              \
-    default: return launch_tc<KIND, 64, false>(ma, mb, p, tiles, sm_count, stream);                \
+    case 256: return launch_tc<KIND, 256, false>(ma, mb, mc, p, tiles, sm_count, stream);          \
+    case 128: return launch_tc<KIND, 128, false>(ma, mb, mc, p, tiles, sm_count, stream);          \
+    default: return launch_tc<KIND, 64, false>(ma, mb, mc, p, tiles, sm_count, stream);            \
   }
   if (dtype == FB_F16) { FB_CASE(0) }
   if (dtype == FB_BF16) { FB_CASE(1) }
@@ -1290,7 +1290,16 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     fprintf(stderr, "fb_gemm plan: %lld x %lld x %lld pair=%d block_n=%d ks=%d stages=%lld split=%d cluster=%d ctas=%lld\n",
             static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k), pair ? 1 : 0, block_n, ks,
             k_stages, p.splitk, p.cluster_k, tiles);
-  rc = dispatch_tc(dtype, block_n, pair, ma, mb, p, tiles, di->sm_count, stream);
+  // beta = 0 and whole tiles: C leaves through TMA stores when a tensor map can describe it (FLAGBLAS_B200_C_TMA=0:
+  // through the epilogue warps' own stores)
+  CUtensorMap mc = ma;  // (unused unless c_tma)
+  p.c_tma = 0;
+  if (beta == 0.f && p.splitk <= 1 && p.cluster_k <= 1 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      (static_cast<uint64_t>(ldc) * esz) % 16 == 0 && env_int("FLAGBLAS_B200_C_TMA", 1) != 0 &&
+      encode_2d(&mc, dtype, C, static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(ldc) * esz,
+                kSwizzleBytes / esz, 32) == FB_OK)
+    p.c_tma = 1;
+  rc = dispatch_tc(dtype, block_n, pair, ma, mb, mc, p, tiles, di->sm_count, stream);
   if (rc || p.splitk <= 1) return rc;
   long long blocks = (m * n + 255) / 256;
   if (blocks > 4LL * di->sm_count) blocks = 4LL * di->sm_count;
@@ -1497,7 +1506,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
       p.sk_flags = reinterpret_cast<int*>(tail);
       p.sk_partials = reinterpret_cast<float*>(tail + kStreamKFlagBytes);
     }
-    const int rc = dispatch_tc(dtype, block_n, pass_pair[i], ps.tmpl_a, ps.tmpl_b, p, /*tiles=*/-1, di->sm_count, stream);
+    const int rc = dispatch_tc(dtype, block_n, pass_pair[i], ps.tmpl_a, ps.tmpl_b, ps.tmpl_a, p, /*tiles=*/-1, di->sm_count, stream);
     if (rc) return rc;
   }
   return FB_OK;
