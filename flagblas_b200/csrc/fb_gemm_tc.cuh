@@ -378,42 +378,38 @@ template <class T, int BLOCK_N, class HandBack, class AddParts>
 __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* blocks, const void* c_map, int m, int n, int row0,
                                                   int col_base, float alpha, int lane, bool zero_acc, HandBack hand_back,
                                                   AddParts add_parts, bool wide_merged, uint32_t& seq) {
-  constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
-  constexpr int kLoads = kW / 32;
-  constexpr int kSteps = BLOCK_N / kW;
+  constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step (one staging block)
+  constexpr int kLoads = kW / 32;                        // 32-column chunks (one TMEM load each) per step
+  constexpr int kChunks = BLOCK_N / 32;
   constexpr int kPerVec = 16 / static_cast<int>(sizeof(T));
+  constexpr int kUnits = 32 / kPerVec;                   // 16-byte units of a row that one chunk fills
   const uint32_t base = smem_u32(blocks);
-#pragma unroll 1
-  for (int s = 0; s < kSteps; ++s) {
-    int acc_col = s * kW;  // accumulator column of this step -> column of the tile
-    if (BLOCK_N == 512 && wide_merged) acc_col = ((acc_col >> 7) & 1) * 256 + (acc_col >> 8) * 128 + (acc_col & 127);
-    uint32_t r[kLoads][32];
-#pragma unroll
-    for (int q = 0; q < kLoads; ++q) tmem_ld_32x32(t_row + static_cast<uint32_t>(s * kW + q * 32), r[q]);
+  // The TMEM load of chunk c + 1 is in flight while chunk c is converted and written to the block: two register
+  // sets, which the loop (unrolled in pairs) alternates between.
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(t_row, ra);
+  auto chunk = [&](int c, uint32_t (&r)[32], uint32_t (&r_next)[32]) {
     tmem_ld_wait();
-    if (s == kSteps - 1) hand_back();
+    if (c + 1 < kChunks) tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 1) * 32), r_next);
+    else hand_back();  // the last column of the accumulator is in registers
     if (zero_acc) {
 #pragma unroll
-      for (int q = 0; q < kLoads; ++q)
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[q][j] = 0u;
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
     }
-#pragma unroll
-    for (int q = 0; q < kLoads; ++q) add_parts(s * kLoads + q, r[q]);
+    add_parts(c, r);
+    const int q = c % kLoads;  // which part of the step's 128 bytes per row
     const uint32_t blk = base + (seq & 1u) * static_cast<uint32_t>(kEpiStageBytes);
-    ++seq;
-    // the store that read this block two steps ago must be done reading it (only lane 0 owns bulk groups)
-    if (lane == 0) bulk_wait_group_read<1>();
-    __syncwarp();
+    if (q == 0) {
+      // the store that read this block two steps ago must be done reading it (only lane 0 owns bulk groups)
+      if (lane == 0) bulk_wait_group_read<1>();
+      __syncwarp();
+    }
     const uint32_t own_row = blk + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < kUnits; ++u) {
       float v[kPerVec];
 #pragma unroll
-      for (int j = 0; j < kPerVec; ++j) {
-        const int e = u * kPerVec + j;  // column of this step
-        v[j] = alpha * __uint_as_float(r[e >> 5][e & 31]);
-      }
+      for (int j = 0; j < kPerVec; ++j) v[j] = alpha * __uint_as_float(r[u * kPerVec + j]);
       uint4 raw;
       if constexpr (sizeof(T) == 4) {
         raw.x = __float_as_uint(v[0]); raw.y = __float_as_uint(v[1]);
@@ -424,15 +420,26 @@ __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* block
         raw.z = pack2(from_f32<T>(v[4]), from_f32<T>(v[5]));
         raw.w = pack2(from_f32<T>(v[6]), from_f32<T>(v[7]));
       }
-      st_shared_v4(own_row + static_cast<uint32_t>((u ^ (lane & 7)) << 4), raw);
+      st_shared_v4(own_row + static_cast<uint32_t>(((q * kUnits + u) ^ (lane & 7)) << 4), raw);
     }
-    fence_proxy_async();  // this thread's writes to the block, before the TMA unit reads it
-    __syncwarp();
-    const int col0 = col_base + acc_col;
-    if (lane == 0 && row0 < m && col0 < n) {
-      tma_store_2d(c_map, blk, col0, row0);
-      bulk_commit_group();
+    if (q == kLoads - 1) {
+      fence_proxy_async();  // this thread's writes to the block, before the TMA unit reads it
+      __syncwarp();
+      int acc_col = (c / kLoads) * kW;  // accumulator column of this step -> column of the tile
+      if (BLOCK_N == 512 && wide_merged) acc_col = ((acc_col >> 7) & 1) * 256 + (acc_col >> 8) * 128 + (acc_col & 127);
+      const int col0 = col_base + acc_col;
+      if (lane == 0 && row0 < m && col0 < n) {
+        tma_store_2d(c_map, blk, col0, row0);
+        bulk_commit_group();
+      }
+      ++seq;
     }
+  };
+  static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
+#pragma unroll 1
+  for (int c = 0; c < kChunks; c += 2) {
+    chunk(c, ra, rb);
+    chunk(c + 1, rb, ra);
   }
 }
 
