@@ -1179,8 +1179,11 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   bool wide = false;
   // with the merged B copy and one-slab stages (bf16 8192 x 8192 x k: k = 4096 +3.1 %, 2048 -1.2 %, 1024 -15 %; TF32 TN:
   // k = 8192 +9 %, 4096 +8 %, 2048 +1.4 %)
-  const bool long_k = esz == 4 ? k >= 2048 : k >= 4096;
-  if (pair && a3d && b3d && beta == 0.f && block_n == 256 && dplan.splitk == 1 && long_k &&
+  // beta != 0: the epilogue also reads C and every tile's is exposed, which only a four times longer k loop pays for,
+  // and for 16-bit types only (bf16 NT beta = 1: 8192 x 8192 x 16384 +4.6 %, fp16 8192^3 +0.9 %, 16384 x 14336 x 4096
+  // -11 %; TF32 TN beta = 0.5: 8192^3 +2.6 %, but 16384^3 -4 to +7 % from run to run and 8192 x 8192 x 4096 -3.5 %)
+  const bool long_k = beta == 0.f ? (esz == 4 ? k >= 2048 : k >= 4096) : (esz == 2 && k >= 16384);
+  if (pair && a3d && b3d && block_n == 256 && dplan.splitk == 1 && long_k &&
       env_int("FLAGBLAS_B200_BLOCK_N", 0) == 0 && env_int("FLAGBLAS_B200_WIDE_TILES", 1) != 0) {
     const long long pairs = di->sm_count / 2;
     const long long rows = (m + 2 * kBlockM - 1) / (2 * kBlockM);

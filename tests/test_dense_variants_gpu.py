@@ -123,6 +123,7 @@ def test_tails_of_a_last_wave_go_to_idle_workers(kind, ta, tb, m, n, k, monkeypa
     Ad, Bd = A.to(DEV), B.to(DEV)
     op = getattr(fb, KINDS[kind][1])
     outs = {}
+    monkeypatch.setenv("FLAGBLAS_B200_WIDE_TILES", "0")  # (a very long k would take one wave of 512-wide tiles instead)
     for mode in ("0", "1"):
         monkeypatch.setenv("FLAGBLAS_B200_STREAMK_TAILS", mode)
         fb.reload_env()
