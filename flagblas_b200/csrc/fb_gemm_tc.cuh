@@ -280,7 +280,7 @@ template <class T, int BLOCK_N, class HandBack, class AddParts>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* stage, const Problem& pr, int row0,
                                                      int col_base, float alpha, float beta, int lane, bool zero_acc,
                                                      HandBack hand_back, AddParts add_parts, bool wide_merged = false,
-                                                     bool streaming = false) {
+                                                     bool streaming = false, int s_begin = 0, int s_end = -1) {
   constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step
   constexpr int kLoads = kW / 32;
   constexpr int kSteps = BLOCK_N / kW;
@@ -289,8 +289,9 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
   const uint32_t own_row = stage_addr + static_cast<uint32_t>(lane) * 128u;
   const int sub_row = lane >> 3, unit = lane & 7;  // read-out role: row within a group of four, 16-byte unit
   const bool with_c = beta != 0.f;
+  const int s_stop = s_end < 0 ? kSteps : s_end;  // (a stream-K sharer finishes only steps [s_begin, s_end) of the tile)
 #pragma unroll 1
-  for (int s = 0; s < kSteps; ++s) {
+  for (int s = s_begin; s < s_stop; ++s) {
     int acc_col = s * kW;  // accumulator column of this step -> column of the tile
     if (BLOCK_N == 512 && wide_merged) acc_col = ((acc_col >> 7) & 1) * 256 + (acc_col >> 8) * 128 + (acc_col & 127);
     const int col0 = col_base + acc_col;
@@ -312,7 +313,7 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
 #pragma unroll
     for (int q = 0; q < kLoads; ++q) tmem_ld_32x32(t_row + static_cast<uint32_t>(s * kW + q * 32), r[q]);
     tmem_ld_wait();
-    if (s == kSteps - 1) hand_back();
+    if (s == s_stop - 1) hand_back();
     if (zero_acc) {
 #pragma unroll
       for (int q = 0; q < kLoads; ++q)
@@ -377,7 +378,8 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
 template <class T, int BLOCK_N, class HandBack, class AddParts>
 __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* blocks, const void* c_map, int m, int n, int row0,
                                                   int col_base, float alpha, int lane, bool zero_acc, HandBack hand_back,
-                                                  AddParts add_parts, bool wide_merged, uint32_t& seq) {
+                                                  AddParts add_parts, bool wide_merged, uint32_t& seq, int c_begin = 0,
+                                                  int c_end = BLOCK_N / 32) {
   constexpr int kW = 128 / static_cast<int>(sizeof(T));  // columns per step (one staging block)
   constexpr int kLoads = kW / 32;                        // 32-column chunks (one TMEM load each) per step
   constexpr int kChunks = BLOCK_N / 32;
@@ -386,11 +388,12 @@ __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* block
   const uint32_t base = smem_u32(blocks);
   // The TMEM load of chunk c + 1 is in flight while chunk c is converted and written to the block: two register
   // sets, which the loop (unrolled in pairs) alternates between.
+  // (A stream-K sharer finishes only chunks [c_begin, c_end) of the tile, whole steps.)
   uint32_t ra[32], rb[32];
-  tmem_ld_32x32(t_row, ra);
+  tmem_ld_32x32(t_row + static_cast<uint32_t>(c_begin * 32), ra);
   auto chunk = [&](int c, uint32_t (&r)[32], uint32_t (&r_next)[32]) {
     tmem_ld_wait();
-    if (c + 1 < kChunks) tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 1) * 32), r_next);
+    if (c + 1 < c_end) tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 1) * 32), r_next);
     else hand_back();  // the last column of the accumulator is in registers
     if (zero_acc) {
 #pragma unroll
@@ -437,9 +440,9 @@ __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* block
   };
   static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
 #pragma unroll 1
-  for (int c = 0; c < kChunks; c += 2) {
+  for (int c = c_begin; c < c_end; c += 2) {
     chunk(c, ra, rb);
-    chunk(c + 1, rb, ra);
+    if (c + 1 < c_end) chunk(c + 1, rb, ra);
   }
 }
 
@@ -537,12 +540,13 @@ __device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint3
 }
 
 // One unit of work of a persistent worker: stages [sb, se) of the k loop of one output tile.
-enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3, ITEM_CLUSTER = 4 };
+enum : int { ITEM_FULL = 0, ITEM_PARTIAL = 1, ITEM_OWNER = 2, ITEM_SPLIT = 3, ITEM_CLUSTER = 4, ITEM_SHARED = 5 };
 struct WorkItem {
   int tile;
   int sb, se;
   int kind;
-  int part;  // ITEM_SPLIT: which k part
+  int part;  // ITEM_SPLIT: which k part; ITEM_SHARED: this worker's place among the tile's sharers
+  int first; // ITEM_SHARED: the first of the workers that share the tile
   int slot;  // stream-K: >= 0 names the partial slot of the tile (one contributor); < 0: slots go by worker
 };
 
@@ -552,6 +556,7 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
                                                 WorkItem& it) {
   const int tiles = p.tiles_m * p.tiles_n;
   it.part = 0;
+  it.first = 0;
   it.slot = -1;
   if (p.cluster_k > 1) {
     // the grid is exactly tiles x cluster_k CTAs: one work item each, the cluster rank picks the k part
@@ -655,15 +660,32 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
     return true;
   }
   if (idx > p.sk_dp) return false;
+  // the tail: tile `tl` is shared by workers tl * sk_group .. + sk_group - 1
   const int tl = worker / p.sk_group, j = worker % p.sk_group;
   if (tl >= p.sk_rem) return false;  // more workers than tail parts: this one is done
-  const int owner_len = stages - (p.sk_group - 1) * p.sk_share;
   it.tile = p.sk_dp * workers + tl;
-  if (j == 0) {
-    it.sb = 0; it.se = owner_len; it.kind = ITEM_OWNER;
-  } else {
-    it.sb = owner_len + (j - 1) * p.sk_share; it.se = it.sb + p.sk_share; it.kind = ITEM_PARTIAL;
+  if (p.sk_group == 2) {
+    // Two sharers: the first owns the tile (the head of the k range, longer by about the time the other needs to
+    // park its sums, and the whole epilogue), the second contributes `sk_share` stages.  (Measured against both
+    // finishing half of the columns each: 512 x 4096 x 4096 25.2 against 26.9 us, 256 x 8192 x 8192 43.1 / 44.3,
+    // 512 x 4096 x 14336 57.4 / 60.7 -- the exchange is bound by L2 bandwidth either way, and the owner's head start
+    // hides the other's parking.)
+    const int owner_len = stages - p.sk_share;
+    if (j == 0) {
+      it.sb = 0; it.se = owner_len; it.kind = ITEM_OWNER;
+    } else {
+      it.sb = owner_len; it.se = stages; it.kind = ITEM_PARTIAL;
+    }
+    return true;
   }
+  // Three or four sharers: equal parts of the k range, and every sharer finishes a part of the tile's columns
+  // (1024 x 1536 x 4096, three sharers: 24.3 - 25.5 us against 25.8 - 26.9 with one owner adding two parked parts).
+  const int base = stages / p.sk_group, extra = stages % p.sk_group;
+  it.sb = j * base + min(j, extra);
+  it.se = it.sb + base + (j < extra ? 1 : 0);
+  it.kind = ITEM_SHARED;
+  it.part = j;
+  it.first = worker - j;
   return true;
 }
 
@@ -1390,6 +1412,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         };
         auto nothing_to_add = [](int, uint32_t (&)[32]) {};
+        // Stream-K: adding the parts of the tile's k range that other workers parked (raw accumulator words) to
+        // chunks [c_lo, c_hi) of 32 columns.  Read with plain loads the 64 KB to 128 KB of a part cost an L2 latency
+        // per batch of eight.  When this is the worker's last item (no copy will touch the operand ring again: its
+        // MMAs are complete) the parts come through the ring instead, one chunk of every part at a time with
+        // asynchronous 16-byte copies, each thread fetching exactly the words it will read back: three slots, so
+        // that the copies of two chunks are in flight while one is added.
+        constexpr int kPartSlots = 3, kMaxParts = 3, kChunksTotal = BLOCK_N / 32;
+        constexpr uint32_t kPartUnit = kBlockM * 16;                     // one 16-byte unit of every row
+        constexpr uint32_t kPartSlotBytes = kMaxParts * 8 * kPartUnit;   // one chunk of every part
+        constexpr bool kRingHoldsParts = Cfg::kStages * Cfg::kStageBytes >= kPartSlots * static_cast<int>(kPartSlotBytes);
+        // the slots to add: n_parts consecutive ones from part_first on, leaving out slot part_skip
+        int part_first = 0, part_skip = -1, n_parts = 0, c_lo = 0, c_hi = kChunksTotal;
+        auto part_slot = [&](int j) { const int v = part_first + j; return v >= part_skip && part_skip >= 0 ? v + 1 : v; };
+        bool in_ring = false;
+        const uint32_t ring_row = smem_u32(ring) + static_cast<uint32_t>(lane_group * 32 + lane) * 16u;
+        auto fetch_chunk = [&](int c) {
+          const uint32_t dst0 = ring_row + static_cast<uint32_t>(c % kPartSlots) * kPartSlotBytes;
+          for (int j = 0; j < n_parts; ++j) {
+            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + part_slot(j) * kSkSlot) + sk_row +
+                                static_cast<size_t>(c * 8) * Cfg::kTileM;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + static_cast<uint32_t>(j * 8 + q) * kPartUnit),
+                           "l"(src + static_cast<size_t>(q) * Cfg::kTileM) : "memory");
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto start_parts = [&]() {  // after part_slot, n_parts, c_lo, c_hi are set (and the parts are known to be parked)
+          if constexpr (kRingHoldsParts) {
+            WorkItem nxt;
+            int t2, role2, sh2;
+            const bool last_item = grouped ? !grouped_tile(p, worker, num_workers, num_tiles, idx + 1, t2, role2, sh2)
+                                           : !dense_work_item(p, worker, num_workers, dense_stages, idx + 1, nxt);
+            if (last_item && !p.small_m && n_parts <= kMaxParts && c_hi > c_lo) {
+              fetch_chunk(c_lo);
+              if (c_lo + 1 < c_hi) fetch_chunk(c_lo + 1);
+              in_ring = true;
+            }
+          }
+        };
+        auto add_parked = [&](int c, uint32_t (&r)[32]) {
+          if (in_ring) {
+            // chunk c has landed (the copies of chunk c + 1 may still be in flight)
+            if (c + 1 < c_hi) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            const uint32_t src0 = ring_row + static_cast<uint32_t>(c % kPartSlots) * kPartSlotBytes;
+            for (int j = 0; j < n_parts; ++j) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint4 x = ld_shared_v4(src0 + static_cast<uint32_t>(j * 8 + q) * kPartUnit);
+                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + __uint_as_float(x.x));
+                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + __uint_as_float(x.y));
+                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + __uint_as_float(x.z));
+                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + __uint_as_float(x.w));
+              }
+            }
+            if (c + 2 < c_hi) fetch_chunk(c + 2);  // (into the slot chunk c - 1 was read from)
+            return;
+          }
+          for (int j = 0; j < n_parts; ++j) {
+            const float4* src = reinterpret_cast<const float4*>(p.sk_partials + part_slot(j) * kSkSlot) + sk_row;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
+              r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
+              r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
+              r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
+              r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
+            }
+          }
+        };
         if (item.kind == ITEM_SPLIT) {
           Problem part = pr;
           part.out = p.splitk_out + static_cast<size_t>(item.part) * pr.m * pr.n;
@@ -1397,61 +1490,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           part.vec_ok = (pr.n & 3) == 0 ? 1 : 0;
           epilogue_tile_staged<float, BLOCK_N>(t_row, stage, part, row0, tn * BLOCK_N, 1.f, 0.f, lane, k_is_zero, hand_back,
                                                nothing_to_add);
-        } else if (!(FB_STORES_ON(p) && ok)) {
-          hand_back();
-        } else if (item.kind == ITEM_OWNER) {
-          // stream-K: add the parts of the tile's k range that other workers parked (raw accumulator words).
-          // Read with plain loads the 64 KB to 128 KB of a part cost a latency per batch of eight; when this is the
-          // worker's last item (no copy will touch the operand ring again: its MMAs are complete) the first part is
-          // first brought into the ring with asynchronous 16-byte copies, all in flight at once, each thread
-          // fetching exactly the words it will read back.
-          constexpr bool kRingHoldsPart = Cfg::kStages * Cfg::kStageBytes >= kBlockM * BLOCK_N * 4;
-          bool in_ring = false;
-          const uint32_t ring_row = smem_u32(ring) + static_cast<uint32_t>(lane_group * 32 + lane) * 16u;
-          if constexpr (kRingHoldsPart) {
-            WorkItem nxt;
-            int t2, role2, sh2;
-            const bool last_item = grouped ? !grouped_tile(p, worker, num_workers, num_tiles, idx + 1, t2, role2, sh2)
-                                           : !dense_work_item(p, worker, num_workers, dense_stages, idx + 1, nxt);
-            if (last_item && !p.small_m) {
-              const float4* src = reinterpret_cast<const float4*>(p.sk_partials + sk_first * kSkSlot) + sk_row;
-#pragma unroll 16
-              for (int u = 0; u < BLOCK_N / 4; ++u)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_row + static_cast<uint32_t>(u * kBlockM * 16)),
-                             "l"(src + static_cast<size_t>(u) * Cfg::kTileM) : "memory");
-              asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-              in_ring = true;
+        } else if (item.kind == ITEM_SHARED || item.kind == ITEM_OWNER) {
+          constexpr int kW = 128 / static_cast<int>(sizeof(OutT)), kLoads = kW / 32, kSteps = BLOCK_N / kW;
+          if (item.kind == ITEM_OWNER) {
+            // the other workers' parts of the whole tile (their flags were awaited above)
+            part_first = sk_first; n_parts = sk_last - sk_first + 1;
+          } else {
+          // A tile whose k range `sk_group` workers share, all of them finishing a part of its columns: this worker
+          // parks its sums of the other workers' columns in its slot, raises its flag, waits for theirs, adds
+          // their sums of its own columns to its accumulator and stores those.  Every worker reads 1 / sk_group of
+          // what a single owner would, and the k ranges are equal.
+          const int g = p.sk_group, mine = item.part;
+          const int s_lo = mine * kSteps / g, s_hi = (mine + 1) * kSteps / g;  // the steps (128 bytes of a row) it finishes
+          c_lo = s_lo * kLoads; c_hi = s_hi * kLoads;
+          float4* park = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot) + sk_row;
+#pragma unroll 1
+          for (int c = 0; c < kChunksTotal; ++c) {
+            if (c >= c_lo && c < c_hi) continue;
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              __stcg(park + static_cast<size_t>(c * 8 + q) * Cfg::kTileM,
+                     make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                 __uint_as_float(r[q * 4 + 3])));
+          }
+          __threadfence();  // the partial sums are visible GPU-wide before the flag says so
+          __syncwarp();
+          const int flag_pos = static_cast<int>(cta_rank) * 4 + lane_group;
+          uint32_t good = 1;
+          if (lane == 0) {
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + worker * 8 + flag_pos), "r"(p.sk_epoch) : "memory");
+            const long long w0 = clock64();
+            for (int v = item.first; v < item.first + g && good; ++v) {
+              if (v == worker) continue;
+              while (true) {
+                int f;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.sk_flags + v * 8 + flag_pos) : "memory");
+                if (f == p.sk_epoch) break;
+                if (*abort_flag) { good = 0; break; }
+                if (clock64() - w0 > FB_WAIT_LIMIT_CYCLES) {
+                  *abort_flag = 1;
+                  atomicCAS(&g_fb_status, 0, DEV_TIMEOUT_STREAMK_PARTIAL);
+                  good = 0;
+                  break;
+                }
+                __nanosleep(64);
+              }
             }
           }
-          auto add_parked = [&](int c, uint32_t (&r)[32]) {
-            if (in_ring) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const uint4 x = ld_shared_v4(ring_row + static_cast<uint32_t>((c * 8 + q) * kBlockM * 16));
-                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + __uint_as_float(x.x));
-                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + __uint_as_float(x.y));
-                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + __uint_as_float(x.z));
-                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + __uint_as_float(x.w));
-              }
-            }
-            for (int v = in_ring ? sk_first + 1 : sk_first; v <= sk_last; ++v) {
-              const float4* src = reinterpret_cast<const float4*>(p.sk_partials + v * kSkSlot) + sk_row;
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 x = __ldcg(src + static_cast<size_t>(c * 8 + q) * Cfg::kTileM);
-                r[q * 4 + 0] = __float_as_uint(__uint_as_float(r[q * 4 + 0]) + x.x);
-                r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
-                r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
-                r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
-              }
-            }
-          };
-          if (p.c_tma)
-            epilogue_tile_tma<OutT, BLOCK_N>(t_row, stage, &tmC, pr.m, pr.n, row0, tn * BLOCK_N, p.alpha, lane, k_is_zero,
-                                             hand_back, add_parked, false, epi_seq);
-          else
-            epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero,
-                                                hand_back, add_parked);
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) ok = false;
+          part_first = item.first; part_skip = worker; n_parts = g - 1;
+          }
+          if (c_hi > c_lo && FB_STORES_ON(p) && ok) {
+            start_parts();
+            if (p.c_tma)
+              epilogue_tile_tma<OutT, BLOCK_N>(t_row, stage, &tmC, pr.m, pr.n, row0, tn * BLOCK_N, p.alpha, lane, k_is_zero,
+                                               hand_back, add_parked, false, epi_seq, c_lo, c_hi);
+            else
+              epilogue_tile_staged<OutT, BLOCK_N>(t_row, stage, pr, row0, tn * BLOCK_N, p.alpha, p.beta, lane, k_is_zero,
+                                                  hand_back, add_parked, false, false, c_lo / kLoads, c_hi / kLoads);
+          } else {
+            hand_back();
+          }
+        } else if (!(FB_STORES_ON(p) && ok)) {
+          hand_back();
         } else if (p.c_tma) {
           epilogue_tile_tma<OutT, BLOCK_N>(t_row, stage, &tmC, pr.m, pr.n, row0, tn * BLOCK_N, p.alpha, lane, k_is_zero,
                                            hand_back, nothing_to_add, p.wide_merged != 0, epi_seq);

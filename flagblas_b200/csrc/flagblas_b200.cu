@@ -381,10 +381,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
     const long long dp = tiles / workers, rem = tiles - dp * workers;
     long long group = rem > 0 ? workers / rem : 0;  // workers per tail tile
     if (group > 4) group = 4;
-    // head start of the owner over a contributor, which still has to park a 128 x 256 fp32 tile per CTA: in 64-deep
-    // stages; measured flat between 8 and 16 (4096 x 4096 x 8192: 1358 / 1361 / 1355 / 1350 TFLOP/s at 4 / 12 / 20 / 28)
+    // Two sharers: an owner and a contributor of `share` stages; the owner's part is longer by `head`, about the time
+    // the contributor needs to park a 128 x 256 fp32 tile per CTA (in 64-deep stages; measured flat between 8 and 16:
+    // 4096 x 4096 x 8192 1358 / 1361 / 1355 / 1350 TFLOP/s at 4 / 12 / 20 / 28).  Three or four: equal parts of the
+    // k range, every sharer finishing a part of the tile's columns (dense_work_item).
     const long long head = (env_int("FLAGBLAS_B200_SK_HEAD", 12) + p.ks - 1) / p.ks;
-    const long long share = group >= 2 ? (stages - head) / group : 0;
+    const long long share = group == 2 ? (stages - head) / 2 : (group > 2 ? stages / group : 0);
     if (group >= 2 && share >= 2 && dp < 9) {
       pp.sk_enabled = 1;
       pp.sk_dp = static_cast<int>(dp);
@@ -415,6 +417,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   }
   if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
   if (pp.sk_enabled || pp.sk_grouped) pp.sk_epoch = next_streamk_epoch();
+  if (env_int("FLAGBLAS_B200_PLAN_DEBUG", 0) != 0 && p.num_groups == 0)
+    fprintf(stderr, "fb_gemm launch: workers=%lld grid=%u stream-k mode=%d whole waves=%d tail tiles=%d sharers=%d share=%d stages, c_tma=%d\n",
+            workers, cfg.gridDim.x, pp.sk_enabled, pp.sk_dp, pp.sk_rem, pp.sk_group, pp.sk_share, pp.c_tma);
 #ifdef FB_PROFILING_SWITCHES
   pp.debug = env_int("FLAGBLAS_B200_DEBUG_SKIP", 0);
 #else
@@ -661,6 +666,26 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   const long long stages = (k + 2 * span - 1) / (2 * span);  // with two k-slabs per stage
   pl.splitk = 1;
   pl.cluster_k = 1;
+  // CTA-pair tiles of 256 x 256 that fill at most half the pairs share their k ranges (the stream-K tail: up to four
+  // workers per tile, one kernel).  In two-slab stages a shared tile costs stages / sharers + a fix-up (the owner adds
+  // one parked part out of the idle operand ring, ~8 stages, or two or three with plain loads, ~12) against
+  // 0.83 x stages for the 128-wide tiles choose_block_n prefers when they fit one wave (bf16 NT 256 x 8192 x 8192:
+  // 43.1 against 49 us; 512 x 4096 x 14336: 57.4 / 72.2; 512 x 4096 x 4096: 25.2 / 27.3; 1024 x 1536 x 4096: 26.9 / 27.2).
+  double pair_shared_cost = 0.0;  // > 0: cost of that plan in the units of the search below (stages x columns)
+  if (pl.pair && force_bn == 0 && stages >= 32 && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 &&
+      env_int("FLAGBLAS_B200_SPLITK", -1) < 0) {
+    const long long t256 = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
+    if (2 * t256 <= workers && 4 * t256 >= workers) {
+      const long long g = workers / t256;  // 2 or 3 (4 sharers only when 4 * t256 == workers)
+      const double shared = static_cast<double>(stages) / static_cast<double>(g) + (g == 2 ? 8.0 : 12.0);
+      pair_shared_cost = (shared + 4.0) * 256.0;
+      if (pl.block_n == 128) {
+        const long long t128 = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 127) / 128);
+        const long long waves128 = (t128 + workers - 1) / workers;
+        if (shared < 0.83 * static_cast<double>(stages) * static_cast<double>(waves128)) pl.block_n = 256;
+      }
+    }
+  }
   // Few output tiles and a long k (a handful of rows against a large matrix, or a small square problem): whole-k
   // tiles leave most SMs idle, and a CTA needs the same ~0.3 us per 64-deep stage whatever its tile width.  So the
   // tile width and a split of the k range are picked together over 128-row tiles:
@@ -718,7 +743,15 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
                                   2.1e-4 * static_cast<double>(m) * n * sp * 4.0;
         if (sp >= 2 && split_cost < pair_cost) pair_cost = split_cost;
       }
-      take = best_sp == 1 && best < 0.8 * pair_cost;
+      // ... or share their k ranges through the stream-K tail (bf16 1024 x 1536 x 4096: cluster split-K of 128 x 256
+      // tiles 29.1 us, 24 pair tiles sharing 26.9; 512 x 4096 x 4096: 28.9 / 25.2; 256 x 8192 x 8192: 51.1 / 43.1;
+      // 512 x 4096 x 14336: 72.2 / 57.4 -- while 16 pair tiles and fewer lose to the 128-row plans: 256 x 4096 x 4096
+      // 19.7 against 25.6 us, 512 x 1536 x 4096 19.3 against 25.9)
+      if (pair_shared_cost > 0.0 && pl.block_n == 256) {
+        take = best_sp == 1 && best < 0.95 * pair_shared_cost;
+      } else {
+        take = best_sp == 1 && best < 0.8 * pair_cost;
+      }
     }
     if (take) {
       pl.pair = false;
@@ -731,7 +764,11 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   // CTA-pair tiles with a deep k and few output tiles (200 x 200 x 20000: one tile; 129 x 4096 x 4096: 16): give the
   // idle pairs a part of every tile's k range, as long as a part keeps four stages and the fp32 parts stay small.
   // (Measured: below 32 stages the second kernel costs more than the shorter k loop saves.)
-  if (pl.pair && force_split != 0 && stages >= 32 && 2 * pl.tiles <= split_workers) {
+  // With at least a quarter as many tiles as pairs the stream-K tail (up to four workers per tile, one kernel) keeps
+  // every pair busy and is the faster of the two (1024 x 1536 x 4096: 26.9 against 33.2 us; 512 x 4096 x 4096: 25.2 /
+  // 38.9; 256 x 8192 x 8192: 43.1 / 58.5; 256 x 8192 x 28672: 116 / 127), so the split through scratch is for fewer.
+  const bool tail_covers = 4 * pl.tiles >= split_workers && env_int("FLAGBLAS_B200_STREAMK", 1) != 0 && force_split < 0;
+  if (pl.pair && force_split != 0 && stages >= 32 && 2 * pl.tiles <= split_workers && !tail_covers) {
     long long sp = split_workers / pl.tiles;
     if (sp > stages / 4) sp = stages / 4;
     if (sp > 32) sp = 32;
