@@ -46,11 +46,17 @@ def test_dense_plan_variants(env, kind, monkeypatch):
     ("fp16", 0, 0, 2560, 4096, 4096),    # 2 whole waves + 12 tail tiles, four workers per tail tile
     ("tf32", 1, 0, 4096, 4096, 2048),    # the same tail in TF32
     ("bf16", 1, 1, 4000, 4000, 4160),    # ragged edge tiles, last k stage half full
+    ("bf16", 0, 1, 1024, 1536, 4096),    # 24 pair tiles and no whole wave: three sharers, each finishing a part of the columns
+    ("fp16", 0, 0, 1000, 1500, 4104),    # the same with ragged edges
+    ("bf16", 0, 1, 256, 8192, 8192),     # 32 pair tiles: two sharers, owner and contributor
+    ("tf32", 1, 0, 512, 4096, 4096),     # TF32, 32 pair tiles
 ])
-def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
+@pytest.mark.parametrize("beta", [0.5, 0.0])
+def test_stream_k_tail(kind, ta, tb, m, n, k, beta, monkeypatch):
     """The stream-K tail (FLAGBLAS_B200_STREAMK=0 switches it off): when the last wave of tiles is at most half
-    full and k is long, each tail tile is shared by 2-4 workers (partial sums parked in the workspace, added by
-    the tile's owner).  Same tolerance as every other dense test, and close agreement with whole tiles."""
+    full and k is long, each tail tile is shared by 2-4 workers (partial sums parked in the workspace; two sharers:
+    the tile's owner adds the other's; more: every sharer finishes a part of the columns).  beta = 0 takes the
+    epilogue that stores through TMA.  Same tolerance as every other dense test, and close agreement with whole tiles."""
     A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=31, scale=0.25)
     Ad, Bd = A.to(DEV), B.to(DEV)
     op = getattr(fb, KINDS[kind][1])
@@ -59,20 +65,20 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, monkeypatch):
         monkeypatch.setenv("FLAGBLAS_B200_STREAMK", sk)
         fb.reload_env()
         Cd = C.to(DEV)
-        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
+        op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, beta, Cd, ldc)
         torch.cuda.synchronize()
         assert fb.device_status() == 0
         outs[sk] = Cd.float().cpu()
-    sc = result_scale(k, A, B, 1.5) + 0.5
+    sc = result_scale(k, A, B, 1.5) + beta
     # both schedules against fp64 on the GPU-resident data (the numpy oracle is too slow at these sizes)
     opA = (Ad.t() if ta else Ad).double()
     opB = (Bd.t() if tb else Bd).double()
     if kind == "tf32":
         trunc = lambda x: (x.float().contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32).double()  # noqa: E731
         opA, opB = trunc(opA), trunc(opB)
-    ref = (1.5 * (opA @ opB) + 0.5 * C.to(DEV).double()).float().cpu()
+    ref = (1.5 * (opA @ opB) + beta * C.to(DEV).double()).float().cpu()
     for sk in ("1", "0"):
-        assert_parity(outs[sk], ref, KINDS[kind][2], sc, "stream-k=%s %s %dx%dx%d" % (sk, kind, m, n, k))
+        assert_parity(outs[sk], ref, KINDS[kind][2], sc, "stream-k=%s %s %dx%dx%d beta=%g" % (sk, kind, m, n, k, beta))
     # different summation order: the two schedules may differ by a rounding step of the output type
     assert_parity(outs["1"], outs["0"], KINDS[kind][2], sc, "stream-k vs whole tiles")
 
