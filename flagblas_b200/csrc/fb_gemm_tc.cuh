@@ -194,6 +194,17 @@ __device__ __forceinline__ uint32_t pack2(__nv_bfloat16 lo, __nv_bfloat16 hi) {
   __nv_bfloat162 v = __halves2bfloat162(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two fp32 values rounded (to nearest even, each on its own) and packed by one conversion instruction.
+template <class T> __device__ __forceinline__ uint32_t pack2_f32(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2_f32<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2_f32<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2_f32<float>(float lo, float) { return __float_as_uint(lo); }  // (unused)
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -347,10 +358,10 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t t_row, uint8_t* st
         raw.x = __float_as_uint(v[0]); raw.y = __float_as_uint(v[1]);
         raw.z = __float_as_uint(v[2]); raw.w = __float_as_uint(v[3]);
       } else {
-        raw.x = pack2(from_f32<T>(v[0]), from_f32<T>(v[1]));
-        raw.y = pack2(from_f32<T>(v[2]), from_f32<T>(v[3]));
-        raw.z = pack2(from_f32<T>(v[4]), from_f32<T>(v[5]));
-        raw.w = pack2(from_f32<T>(v[6]), from_f32<T>(v[7]));
+        raw.x = pack2_f32<T>(v[0], v[1]);
+        raw.y = pack2_f32<T>(v[2], v[3]);
+        raw.z = pack2_f32<T>(v[4], v[5]);
+        raw.w = pack2_f32<T>(v[6], v[7]);
       }
       st_shared_v4(slot, raw);
     }
@@ -418,10 +429,10 @@ __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* block
         raw.x = __float_as_uint(v[0]); raw.y = __float_as_uint(v[1]);
         raw.z = __float_as_uint(v[2]); raw.w = __float_as_uint(v[3]);
       } else {
-        raw.x = pack2(from_f32<T>(v[0]), from_f32<T>(v[1]));
-        raw.y = pack2(from_f32<T>(v[2]), from_f32<T>(v[3]));
-        raw.z = pack2(from_f32<T>(v[4]), from_f32<T>(v[5]));
-        raw.w = pack2(from_f32<T>(v[6]), from_f32<T>(v[7]));
+        raw.x = pack2_f32<T>(v[0], v[1]);
+        raw.y = pack2_f32<T>(v[2], v[3]);
+        raw.z = pack2_f32<T>(v[4], v[5]);
+        raw.w = pack2_f32<T>(v[6], v[7]);
       }
       st_shared_v4(own_row + static_cast<uint32_t>(((q * kUnits + u) ^ (lane & 7)) << 4), raw);
     }
