@@ -680,6 +680,10 @@ def main():
         with ClockSampler(local_rank, period=0.01) as sclk:
             sus_ms = timed(step, n_sus)
         sus_peak, sus_src = measured("bf16_tflops_sustained", 1400.0)
+        if kind == "fp32":
+            sus_peak, sus_src = 148 * 128 * 2 * 1.965e9 / 1e12, "nominal FFMA rate at the maximum SM clock"
+        elif kind == "tf32":
+            sus_peak, sus_src = sus_peak / 2, "assumed: " + sus_src + " / 2 (no measured TF32 figure)"
         sus_val = flops / (sus_ms * 1e-3) / 1e12
         sustained = {"value": sus_val, "unit": "TFLOP/s", "steps": n_sus, "seconds": sus_ms * n_sus * 1e-3,
                      "ms_per_step": sus_ms, "clocks": sclk.summary(), "peak": sus_peak, "peak_source": sus_src,
@@ -760,6 +764,11 @@ def main():
 
     if rank == 0:
         peak, peak_src = measured_peak()
+        bound = "tensor"
+        if kind == "fp32":    # IEEE fp32 runs on the CUDA cores: SMs x FP32 lanes x 2 FLOP x max SM clock
+            peak, peak_src, bound = 148 * 128 * 2 * 1.965e9 / 1e12, "nominal FFMA rate at the maximum SM clock", "fp32 FFMA"
+        elif kind == "tf32":  # no measured TF32 figure: half the measured bf16 rate
+            peak, peak_src = peak / 2, "assumed: " + peak_src + " / 2 (no measured TF32 figure)"
         traffic = ncu_traffic(args.workload) if world == 1 else None
         line = {
             "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -767,9 +776,9 @@ def main():
             "vs_baseline": None, "dtype": {"fp16": "f16", "bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[kind],
             "data": "synthetic",
             "config": dense_config(args.workload, world, args.gather),
-            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+            "roofline": {"bound": bound, "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                          "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
-                         "frac_of_nominal_2250": value / world / 2250.0, "per_gpu": True},
+                         "frac_of_nominal_2250": value / world / 2250.0 if kind in ("fp16", "bf16") else None, "per_gpu": True},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "checked_against_device_result": e2e_checked},
             "gpu_launches": args.steps,

@@ -194,6 +194,34 @@ struct PipeTile {
   static constexpr int kFloats = KMAJ ? TILE * kPipeLdk : kPipeK * TILE;
 };
 
+// A K-contiguous B tile stored for packed FMAs: neighbouring columns (2 p, 2 p + 1) interleaved along k,
+// [pair p][k][2] with 34 floats per pair, so that one 64-bit shared load yields the two B values of a packed FMA in
+// an aligned register pair and the 16 threads that differ in tx (pairs p, p + 1, ...) cover all 32 banks.
+constexpr int kPipePairLd = 2 * kPipeK + 2;
+template <int TILE>
+struct PipePairTile {
+  static constexpr int kFloats = (TILE / 2) * kPipePairLd;
+};
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, int src_bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// This thread's share of the copies of one (TILE x 16) slice of a K-contiguous operand into the pair-interleaved
+// layout: 4-byte copies (the scatter is finer than 16 bytes), 16 consecutive threads reading 64 consecutive bytes.
+template <int TILE>
+__device__ __forceinline__ void pipe_load_pairs(float* __restrict__ s, const float* __restrict__ base, long long ld, int mn0,
+                                                int k0, int mn_lim, int k_lim, int tid) {
+#pragma unroll
+  for (int e = tid; e < TILE * kPipeK; e += 256) {
+    const int kk = e & (kPipeK - 1), c = e >> 4;
+    const bool valid = mn0 + c < mn_lim && k0 + kk < k_lim;
+    const float* src = valid ? base + static_cast<long long>(mn0 + c) * ld + k0 + kk : base;
+    cp_async4(s + (c >> 1) * kPipePairLd + kk * 2 + (c & 1), src, valid ? 4 : 0);
+  }
+}
+
 __device__ __forceinline__ void cp_async16(float* dst, const float* src, int src_bytes) {
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
@@ -223,12 +251,14 @@ __device__ __forceinline__ void pipe_load(float* __restrict__ s, const float* __
 // PACK: the FMAs are issued as packed pairs (fma.rn.f32x2, two IEEE fp32 FMAs per instruction on sm_100):
 // the same arithmetic in half the issue slots, which leaves room for the shared-memory loads next to them.
 // 1 = pairs of neighbouring columns (B fragments arrive as float4: the pair is already adjacent in registers),
-// 2 = pairs of neighbouring rows (the same for A), 0 = scalar FMAs.
+// 2 = pairs of neighbouring rows (the same for A), 3 = pairs of neighbouring columns of a K-contiguous B, whose tile
+// is then stored pair-interleaved (PipePairTile), 0 = scalar FMAs.
 template <int BM, int BN, bool AK, bool BKM, int PACK>
 __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) {
   constexpr int TM = BM / 16, TN = BN / 16;
   constexpr int RG = TM / 4, CG = TN / 4;
-  constexpr int kAFloats = PipeTile<BM, AK>::kFloats, kBFloats = PipeTile<BN, BKM>::kFloats;
+  constexpr bool BPAIR = BKM && PACK == 3;  // K-contiguous B in the pair-interleaved layout, FMAs packed over column pairs
+  constexpr int kAFloats = PipeTile<BM, AK>::kFloats, kBFloats = BPAIR ? PipePairTile<BN>::kFloats : PipeTile<BN, BKM>::kFloats;
   extern __shared__ __align__(16) float pipe_smem[];
   float* As = pipe_smem;
   float* Bs = pipe_smem + kPipeStages * kAFloats;
@@ -255,14 +285,18 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
 
   // row / column of output (i, j) of this thread inside the tile
   auto row_of = [&](int i) { return (i / 4) * (BM / RG) + ty * 4 + (i % 4); };
-  auto col_of = [&](int j) { return BKM ? tx + 16 * j : (j / 4) * (BN / CG) + tx * 4 + (j % 4); };
+  auto col_of = [&](int j) {
+    if (BPAIR) return (j / 2) * 32 + tx * 2 + (j % 2);  // pairs of neighbouring columns, 32 columns apart
+    return BKM ? tx + 16 * j : (j / 4) * (BN / CG) + tx * 4 + (j % 4);
+  };
 
   const int k_iters = k_end > k_begin ? (k_end - k_begin + kPipeK - 1) / kPipeK : 0;
 #pragma unroll
   for (int s = 0; s < kPipeStages - 1; ++s) {
     if (s < k_iters) {
       pipe_load<BM, AK>(As + s * kAFloats, p.A, p.lda, m0, k_begin + s * kPipeK, p.m, k_end, tid);
-      pipe_load<BN, BKM>(Bs + s * kBFloats, p.B, p.ldb, n0, k_begin + s * kPipeK, p.n, k_end, tid);
+      if constexpr (BPAIR) pipe_load_pairs<BN>(Bs + s * kBFloats, p.B, p.ldb, n0, k_begin + s * kPipeK, p.n, k_end, tid);
+      else pipe_load<BN, BKM>(Bs + s * kBFloats, p.B, p.ldb, n0, k_begin + s * kPipeK, p.n, k_end, tid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
@@ -275,7 +309,8 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
       if (nx < k_iters) {
         const int slot = nx % kPipeStages;
         pipe_load<BM, AK>(As + slot * kAFloats, p.A, p.lda, m0, k_begin + nx * kPipeK, p.m, k_end, tid);
-        pipe_load<BN, BKM>(Bs + slot * kBFloats, p.B, p.ldb, n0, k_begin + nx * kPipeK, p.n, k_end, tid);
+        if constexpr (BPAIR) pipe_load_pairs<BN>(Bs + slot * kBFloats, p.B, p.ldb, n0, k_begin + nx * kPipeK, p.n, k_end, tid);
+        else pipe_load<BN, BKM>(Bs + slot * kBFloats, p.B, p.ldb, n0, k_begin + nx * kPipeK, p.n, k_end, tid);
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -299,7 +334,15 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
             af[h][g * 4 + 0] = v.x; af[h][g * 4 + 1] = v.y; af[h][g * 4 + 2] = v.z; af[h][g * 4 + 3] = v.w;
           }
       }
-      if (BKM) {
+      if (BPAIR) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int jp = 0; jp < TN / 2; ++jp) {
+            const float2 v = *reinterpret_cast<const float2*>(bs + (jp * 16 + tx) * kPipePairLd + (2 * kb + h) * 2);
+            bf[h][2 * jp] = v.x; bf[h][2 * jp + 1] = v.y;
+          }
+      } else if (BKM) {
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
           const float2 v = *reinterpret_cast<const float2*>(bs + col_of(j) * kPipeLdk + 2 * kb);
@@ -314,7 +357,7 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
             bf[h][g * 4 + 0] = v.x; bf[h][g * 4 + 1] = v.y; bf[h][g * 4 + 2] = v.z; bf[h][g * 4 + 3] = v.w;
           }
       }
-      if (PACK == 1) {
+      if (PACK == 1 || PACK == 3) {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -410,6 +453,23 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
               dst[j] = r;
             }
           }
+        }
+      }
+    } else if (BPAIR) {
+#pragma unroll
+      for (int j = 0; j < TN; j += 2) {
+        const int col = n0 + col_of(j);
+        float* dst = crow + col;
+        float v0 = p.alpha * acc[i][j], v1 = p.alpha * acc[i][j + 1];
+        if (col + 1 < p.n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+          if (p.beta != 0.f) {
+            const float2 c = *reinterpret_cast<const float2*>(dst);
+            v0 += p.beta * c.x; v1 += p.beta * c.y;
+          }
+          *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+        } else {
+          if (col < p.n) { if (p.beta != 0.f) v0 += p.beta * dst[0]; dst[0] = v0; }
+          if (col + 1 < p.n) { if (p.beta != 0.f) v1 += p.beta * dst[1]; dst[1] = v1; }
         }
       }
     } else {

@@ -560,7 +560,13 @@ static int dispatch_sgemm_pipe(const SimtParams& p, long long tiles, cudaStream_
   const bool ak = !p.a_mn_contig, bk = !p.b_mn_contig;  // K-contiguous storage
   const bool pack = env_int("FLAGBLAS_B200_SGEMM_FFMA2", 1) != 0;
   if (ak) {
-    if (bk) return launch_sgemm_pipe<BM, BN, true, true, 0>(p, tiles, stream);
+    // both K-contiguous (a linear layer's x W^T): with 128 x 128 tiles B's tile is stored pair-interleaved so that the
+    // FMAs can be packed over neighbouring columns (4096^3 39.8 -> 43.6 TFLOP/s, 8192^3 40.5 -> 44.4, 2048^3 34.4 ->
+    // 36.2; the 64 x 64 tiles of small problems lose with it: 1024^3 26.3 -> 24.7, 512^3 17.2 -> 15.6;
+    // FLAGBLAS_B200_SGEMM_NT_PAIRS=0: scalar FMAs on plain K-contiguous tiles)
+    if (bk) return (pack && BM >= 128 && env_int("FLAGBLAS_B200_SGEMM_NT_PAIRS", 1) != 0)
+                       ? launch_sgemm_pipe<BM, BN, true, true, 3>(p, tiles, stream)
+                       : launch_sgemm_pipe<BM, BN, true, true, 0>(p, tiles, stream);
     return pack ? launch_sgemm_pipe<BM, BN, true, false, 1>(p, tiles, stream)
                 : launch_sgemm_pipe<BM, BN, true, false, 0>(p, tiles, stream);
   }

@@ -142,6 +142,34 @@ def test_alpha_beta_pairs_and_tensor_scalars(kind):
 
 
 # ------------------------------------------------------------------ reference-made golden vectors on the GPU
+@pytest.mark.parametrize("ta,tb", TRANS)
+@pytest.mark.parametrize("m,n,k,pad", [
+    (2048, 2048, 1024, 0),    # 256 tiles of 128 x 128
+    (1920, 1666, 1000, 0),    # ragged edge tiles, k not a multiple of the 16-deep slice
+    (1600, 2000, 520, 4),     # padded leading dimensions
+    (1664, 1792, 768, 3),     # odd leading dimensions: the register-staged kernel instead of the cp.async pipeline
+])
+def test_sgemm_large_tiles_every_layout(ta, tb, m, n, k, pad, monkeypatch):
+    """IEEE fp32 with 128 x 128 tiles in all four layouts (NT stores B's slices pair-interleaved for packed FMAs;
+    FLAGBLAS_B200_SGEMM_NT_PAIRS=0 keeps plain tiles and scalar FMAs): both against the fp64 product."""
+    A, lda, B, ldb, C, ldc = make_dense("fp32", ta, tb, m, n, k, pad=pad, seed=41, scale=0.5)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    opA = (Ad[:, :m].t() if ta else Ad[:, :k]).double()
+    opB = (Bd[:, :k].t() if tb else Bd[:, :n]).double()
+    ref = (1.25 * (opA @ opB) + 0.5 * C.to(DEV)[:, :n].double()).float().cpu()
+    sc = result_scale(k, A, B, 1.25) + 0.5
+    for pairs in ("1", "0"):
+        monkeypatch.setenv("FLAGBLAS_B200_SGEMM_NT_PAIRS", pairs)
+        fb.reload_env()
+        Cd = C.to(DEV)
+        fb.sgemm(ta, tb, m, n, k, 1.25, Ad, lda, Bd, ldb, 0.5, Cd, ldc)
+        torch.cuda.synchronize()
+        assert fb.device_status() == 0
+        assert_parity(Cd[:, :n].float().cpu(), ref, KINDS["fp32"][2], sc, "sgemm pairs=%s ta=%d tb=%d %dx%dx%d" % (pairs, ta, tb, m, n, k))
+        if pad:
+            assert torch.equal(Cd[:, n:].cpu(), C[:, n:]), "padding columns of C were touched"
+
+
 @pytest.mark.parametrize("kind", ["fp32", "fp16"])
 def test_golden_dense_on_gpu(golden_dir, kind):
     z = np.load(os.path.join(golden_dir, "dense_%s.npz" % kind))
