@@ -302,6 +302,32 @@ static int next_streamk_epoch() {
   return static_cast<int>(0x5EED0000u + (counter.fetch_add(1, std::memory_order_relaxed) & 0x0FFFFFFFu) * 2u + 1u);
 }
 
+// Stream-K launches have CTAs that wait for other CTAs of the same launch, so two of them must not share the SMs:
+// each could hold a part and wait for CTAs that cannot start.  On one stream they run one after the other anyway;
+// when a stream-K launch follows one made on ANOTHER stream, it is made to wait for everything submitted to that
+// stream so far (an event recorded there now).  Nothing is added on the common path, where the stream is the same.
+// Streams being captured into a graph are left alone (the capture fixes the order itself).
+static void streamk_gate(cudaStream_t stream) {
+  struct Gate { cudaStream_t last = nullptr; bool any = false; cudaEvent_t ev = nullptr; };
+  static Gate gates[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+  std::lock_guard<std::mutex> lk(mu);
+  Gate& g = gates[dev];
+  if (g.any && g.last != stream) {
+    cudaStreamCaptureStatus a = cudaStreamCaptureStatusNone, b = cudaStreamCaptureStatusNone;
+    const bool ok = cudaStreamIsCapturing(stream, &a) == cudaSuccess && cudaStreamIsCapturing(g.last, &b) == cudaSuccess;
+    if (ok && a == cudaStreamCaptureStatusNone && b == cudaStreamCaptureStatusNone) {
+      if (!g.ev && cudaEventCreateWithFlags(&g.ev, cudaEventDisableTiming) != cudaSuccess) g.ev = nullptr;
+      if (g.ev && cudaEventRecord(g.ev, g.last) == cudaSuccess) cudaStreamWaitEvent(stream, g.ev, 0);
+    }
+    cudaGetLastError();  // (a stream that no longer exists is not an error of this call)
+  }
+  g.last = stream;
+  g.any = true;
+}
+
 static long long tail_slabs(long long slabs, long long workers, long long rem) {
   if (rem <= 0 || 2 * rem <= workers || rem >= workers) return 0;
   if (env_int("FLAGBLAS_B200_STREAMK_TAILS", 1) == 0) return 0;
@@ -417,6 +443,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   }
   if (pp.sk_enabled) cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));  // every worker takes part
   if (pp.sk_enabled || pp.sk_grouped) pp.sk_epoch = next_streamk_epoch();
+  if (pp.sk_enabled) streamk_gate(stream);  // (grouped calls pass the gate before their table builder)
   if (env_int("FLAGBLAS_B200_PLAN_DEBUG", 0) != 0 && p.num_groups == 0)
     fprintf(stderr, "fb_gemm launch: workers=%lld grid=%u stream-k mode=%d whole waves=%d tail tiles=%d sharers=%d share=%d stages, c_tma=%d\n",
             workers, cfg.gridDim.x, pp.sk_enabled, pp.sk_dp, pp.sk_rem, pp.sk_group, pp.sk_share, pp.c_tma);
@@ -1507,7 +1534,7 @@ static int run_grouped(int dtype, int b_k_contig, GroupSetupArgs ga, float alpha
       workspace_bytes >= group_tail_offset(static_cast<size_t>(G)) + streamk_bytes(di->sm_count, block_n)) {
     tail = ws + group_tail_offset(static_cast<size_t>(G));
   }
-  // the table builder also clears the stream-K flags (one launch less than a memset node in front of it)
+  if (tail) streamk_gate(stream);
 
   // The builder is itself a programmatic dependent of whatever precedes it on the stream (typically the previous
   // grouped GEMM, which reads the same tables): it becomes resident as that kernel drains and waits for its

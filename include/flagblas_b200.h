@@ -78,10 +78,11 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
  * stream-K tail of a half-empty last wave of tiles); without the optional part the call runs unsplit.
  * A call that uses the stream-K part has CTAs that wait (bounded, about a second) for other CTAs of the same
  * launch; it never launches more CTAs than the device can hold, and whatever precedes it on its stream finishes
- * without it.  Two such calls running at the same time on different streams of one device can each hold a part of
- * the SMs and wait for CTAs that cannot start; the waits then run out and both calls end with device status 107
- * instead of hanging.  A caller that overlaps large GEMMs on several streams passes only the required part of the
- * workspace (or sets FLAGBLAS_B200_STREAMK=0) and gets whole tiles. */
+ * without it.  Two such calls must not share the SMs (each could hold a part and wait for CTAs that cannot start;
+ * the waits would run out and both end with device status 107), so a stream-K call that follows one made through
+ * this library on another stream of the device first waits for everything submitted to that stream so far.
+ * Streams under graph capture are not ordered this way: a caller that captures large GEMMs on several streams of
+ * one graph passes only the required part of the workspace (or sets FLAGBLAS_B200_STREAMK=0) and gets whole tiles. */
 size_t fb_gemm_workspace_bytes(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, const void* A,
                                int64_t lda, const void* B, int64_t ldb);
 

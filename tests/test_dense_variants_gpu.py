@@ -83,6 +83,27 @@ def test_stream_k_tail(kind, ta, tb, m, n, k, beta, monkeypatch):
     assert_parity(outs["1"], outs["0"], KINDS[kind][2], sc, "stream-k vs whole tiles")
 
 
+def test_stream_k_calls_on_two_streams():
+    """Calls whose tiles share their k ranges, issued alternately on two streams: the library orders a stream-K
+    launch behind the previous one made on another stream, so both streams finish with correct results."""
+    m, n, k = 1024, 1536, 4096
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    data = []
+    for seed in (51, 52):
+        A, lda, B, ldb, C, ldc = make_dense("bf16", 0, 1, m, n, k, seed=seed, scale=0.25)
+        data.append((A.to(DEV), B.to(DEV), torch.empty(m, n, dtype=torch.bfloat16, device=DEV), A, B))
+    torch.cuda.synchronize()
+    for _ in range(10):
+        for s, (Ad, Bd, Cd, _, _) in zip((s1, s2), data):
+            with torch.cuda.stream(s):
+                fb.bfgemm(0, 1, m, n, k, 1.0, Ad, k, Bd, k, 0.0, Cd, n)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    for Ad, Bd, Cd, A, B in data:
+        ref = (Ad.double() @ Bd.double().t()).float().cpu()
+        assert_parity(Cd.float().cpu(), ref, KINDS["bf16"][2], result_scale(k, A, B, 1.0), "two streams")
+
+
 @pytest.mark.parametrize("kind,ta,tb,m,n,k", [
     ("fp16", 0, 0, 8192, 1024, 8192),    # 128 tiles on 74 CTA pairs (one rank's share of 8192^3 over eight GPUs): 1.73 waves
     ("bf16", 0, 1, 2048, 4096, 2048),    # the same tile count, short k (16 stages), K-contiguous B
