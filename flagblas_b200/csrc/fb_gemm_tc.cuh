@@ -1507,53 +1507,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // the other workers' parts of the whole tile (their flags were awaited above)
             part_first = sk_first; n_parts = sk_last - sk_first + 1;
           } else {
-          // A tile whose k range `sk_group` workers share, all of them finishing a part of its columns: this worker
-          // parks its sums of the other workers' columns in its slot, raises its flag, waits for theirs, adds
-          // their sums of its own columns to its accumulator and stores those.  Every worker reads 1 / sk_group of
-          // what a single owner would, and the k ranges are equal.
-          const int g = p.sk_group, mine = item.part;
-          const int s_lo = mine * kSteps / g, s_hi = (mine + 1) * kSteps / g;  // the steps (128 bytes of a row) it finishes
-          c_lo = s_lo * kLoads; c_hi = s_hi * kLoads;
-          float4* park = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot) + sk_row;
+            // A tile whose k range `sk_group` workers share, all of them finishing a part of its columns: this worker
+            // parks its sums of the other workers' columns in its slot, raises its flag, waits for theirs, adds
+            // their sums of its own columns to its accumulator and stores those.  Every worker reads 1 / sk_group of
+            // what a single owner would, and the k ranges are equal.
+            const int g = p.sk_group, mine = item.part;
+            const int s_lo = mine * kSteps / g, s_hi = (mine + 1) * kSteps / g;  // the steps (128 bytes of a row) it finishes
+            c_lo = s_lo * kLoads; c_hi = s_hi * kLoads;
+            float4* park = reinterpret_cast<float4*>(p.sk_partials + worker * kSkSlot) + sk_row;
 #pragma unroll 1
-          for (int c = 0; c < kChunksTotal; ++c) {
-            if (c >= c_lo && c < c_hi) continue;
-            uint32_t r[32];
-            tmem_ld_32x32(t_row + c * 32, r);
-            tmem_ld_wait();
+            for (int c = 0; c < kChunksTotal; ++c) {
+              if (c >= c_lo && c < c_hi) continue;
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + c * 32, r);
+              tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              __stcg(park + static_cast<size_t>(c * 8 + q) * Cfg::kTileM,
-                     make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
-                                 __uint_as_float(r[q * 4 + 3])));
-          }
-          __threadfence();  // the partial sums are visible GPU-wide before the flag says so
-          __syncwarp();
-          const int flag_pos = static_cast<int>(cta_rank) * 4 + lane_group;
-          uint32_t good = 1;
-          if (lane == 0) {
-            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + worker * 8 + flag_pos), "r"(p.sk_epoch) : "memory");
-            const long long w0 = clock64();
-            for (int v = item.first; v < item.first + g && good; ++v) {
-              if (v == worker) continue;
-              while (true) {
-                int f;
-                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.sk_flags + v * 8 + flag_pos) : "memory");
-                if (f == p.sk_epoch) break;
-                if (*abort_flag) { good = 0; break; }
-                if (clock64() - w0 > FB_WAIT_LIMIT_CYCLES) {
-                  *abort_flag = 1;
-                  atomicCAS(&g_fb_status, 0, DEV_TIMEOUT_STREAMK_PARTIAL);
-                  good = 0;
-                  break;
+              for (int q = 0; q < 8; ++q)
+                __stcg(park + static_cast<size_t>(c * 8 + q) * Cfg::kTileM,
+                       make_float4(__uint_as_float(r[q * 4 + 0]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                   __uint_as_float(r[q * 4 + 3])));
+            }
+            __threadfence();  // the partial sums are visible GPU-wide before the flag says so
+            __syncwarp();
+            const int flag_pos = static_cast<int>(cta_rank) * 4 + lane_group;
+            uint32_t good = 1;
+            if (lane == 0) {
+              asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + worker * 8 + flag_pos), "r"(p.sk_epoch) : "memory");
+              const long long w0 = clock64();
+              for (int v = item.first; v < item.first + g && good; ++v) {
+                if (v == worker) continue;
+                while (true) {
+                  int f;
+                  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.sk_flags + v * 8 + flag_pos) : "memory");
+                  if (f == p.sk_epoch) break;
+                  if (*abort_flag) { good = 0; break; }
+                  if (clock64() - w0 > FB_WAIT_LIMIT_CYCLES) {
+                    *abort_flag = 1;
+                    atomicCAS(&g_fb_status, 0, DEV_TIMEOUT_STREAMK_PARTIAL);
+                    good = 0;
+                    break;
+                  }
+                  __nanosleep(64);
                 }
-                __nanosleep(64);
               }
             }
-          }
-          good = __shfl_sync(0xffffffffu, good, 0);
-          if (!good) ok = false;
-          part_first = item.first; part_skip = worker; n_parts = g - 1;
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) ok = false;
+            part_first = item.first; part_skip = worker; n_parts = g - 1;
           }
           if (c_hi > c_lo && FB_STORES_ON(p) && ok) {
             start_parts();
