@@ -673,6 +673,23 @@ def main():
 
     # ---- sustained: the same step back to back for at least two seconds (the clock sags under load), with the SM
     # clock sampled over that window
+    # ---- context: cuBLAS (torch.matmul) on the same box, operands and loop length, after the timed region
+    cublas_tflops = None
+    if world == 1 and m * n <= 8192 * 8192:
+        try:
+            time.sleep(0.3)
+            opA, opB = (A.t() if ta else A), (B.t() if tb else B)
+            tmp = torch.empty((m, n), device=dev, dtype=dt)
+            torch.backends.cuda.matmul.allow_tf32 = kind == "tf32"
+            for _ in range(3):
+                torch.matmul(opA, opB, out=tmp)
+            cublas_tflops = flops / (timed(lambda: torch.matmul(opA, opB, out=tmp), min(args.steps, 20)) * 1e-3) / 1e12
+            torch.backends.cuda.matmul.allow_tf32 = False
+            del tmp
+            time.sleep(0.3)
+        except Exception:
+            cublas_tflops = None
+
     sustained = None
     if not args.no_sustained:
         n_sus = max(args.steps, int(2200.0 / ms_step) + 1)
@@ -778,6 +795,7 @@ def main():
             "config": dense_config(args.workload, world, args.gather),
             "roofline": {"bound": bound, "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                          "frac": value / world / peak, "traffic": traffic, "peak_source": peak_src,
+                         "cublas_same_operands_tflops": cublas_tflops,
                          "frac_of_nominal_2250": value / world / 2250.0 if kind in ("fp16", "bf16") else None, "per_gpu": True},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "checked_against_device_result": e2e_checked},
