@@ -146,6 +146,11 @@ struct TcGemmParams {
   // staging blocks, which transposed tiles do not use -- holds more stages: such calls stream every group's weights
   // once and are bound by how many bytes a CTA keeps in flight towards HBM.
   int small_m;
+  // Dense mode, one row block of fewer than 128 rows, A with k contiguous: A's copies fetch only `a_rows` rows (a
+  // multiple of 8) per k-slab and the slabs lie that close together in the stage, so that the TMA unit moves no
+  // rows of zeros.  The MMA still reads 128 rows from each slab's start; what it finds past `a_rows` belongs to
+  // other slabs and ends up in accumulator rows past m that nobody reads.  0 = whole 128-row slots.
+  int a_rows;
   uint32_t idesc_swapped;  // instruction descriptor of such a block with N = 0 (the block's row count is added per tile)
   float* sk_partials;  // [workers][BLOCK_N / 4 units][tile rows][4]
   int* sk_flags;       // [slots][8]: one word per CTA of the pair and epilogue warp; a contributor's warp stores the
@@ -162,10 +167,15 @@ struct TcGemmParams {
   // programmatic dependent and must wait for it before the first copy.
   int wait_prior;
   // Cluster split-K (dense mode, 128-row tiles, `cluster_k` = 2, 4 or 8 = the launch's cluster size): the CTAs of a
-  // cluster share one output tile and take consecutive parts of its k range.  Each leaves its fp32 sums in its own
-  // shared memory; after a cluster barrier every CTA adds, over distributed shared memory and in rank order, the
-  // 128 / cluster_k rows it is responsible for and writes them out.  No scratch memory, no second kernel.
+  // cluster share one output tile and take consecutive parts of its k range, and CTA r finishes the r-th
+  // BLOCK_N / cluster_k columns of the tile from everybody's fp32 sums, added in rank order.  No scratch memory, no
+  // second kernel.  `cluster_push` != 0: every CTA sends its sums straight from TMEM into a receiving area in the
+  // shared memory of the CTA that finishes them (`cluster_rows` rows per 16-byte column unit; the launch keeps the
+  // operand ring clear of that area); 0: every CTA parks its sums in its own operand ring and the finishing CTA
+  // reads them over distributed shared memory (see cluster_finish_tile).
   int cluster_k;
+  int cluster_push;
+  int cluster_rows;
   // Profiling switches, honoured only by builds with -DFB_PROFILING_SWITCHES (results are meaningless when set):
   // bit 0 = issue no MMA, bit 1 = issue no TMA copy, bit 2 = store nothing.
   int debug;
@@ -467,14 +477,117 @@ __device__ __forceinline__ void epilogue_tile_tma(uint32_t t_row, uint8_t* block
 //      alpha, beta and the cast, and stores them;
 //   4. cluster barrier: nobody leaves while a peer may still read its shared memory.
 // Layout of a parked tile: [128 rows][BLOCK_N] fp32, 16-byte units XOR-swizzled by the row.
+//
+// Push form (p.cluster_push): reads over distributed shared memory are round trips and each cluster barrier waits
+// for the slowest CTA, so the sums travel as asynchronous stores that count themselves in at the receiver:
+//   1. set-up: every CTA initialises `recv_bar`, expects the bytes of all senders on it and arrives at the
+//      cluster barrier; the matching wait here returns at once;
+//   2. every CTA reads its sums of the valid rows from TMEM and sends each 16-byte unit (st.async) to the CTA that
+//      finishes its column, itself included; the receiving area `recv` lies outside the operand ring, so nobody
+//      has to ask whether the receiver is done with its operands;
+//   3. every CTA waits (bounded, status 108) until its barrier has counted all bytes in, adds the senders' regions
+//      in rank order from its own shared memory, applies alpha, beta and the cast, and stores.
+// No CTA touches a peer's memory after its own stores, and none leaves before everything sent to it has landed.
+// Layout of the receiving area: [cluster_k senders][BLOCK_N / 4 / cluster_k units][p.cluster_rows rows] x 16 bytes,
+// the row XOR-ed with the unit's low bits: a warp's 32 rows of one unit are 512 consecutive bytes on the way in, and
+// the eight units of a row fall into different banks on the way out.
 template <class OutT, int BLOCK_N>
-__device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint32_t parked, uint32_t tmem_base,
+__device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint32_t parked, uint32_t recv,
+                                                    uint64_t* recv_bar, const WaitCtl& wctl, uint32_t tmem_base,
                                                     int tile, bool store) {
   constexpr int kUnits = BLOCK_N / 4;  // 16-byte units (four fp32 sums) per row
   constexpr uint32_t kPitch = BLOCK_N * 4;
   const int parts = p.cluster_k;
   const uint32_t rank = cluster_ctarank();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int tm, tn;
+  swizzled_tile(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+  const Problem& pr = p.prob;
+  // a CTA's share: BLOCK_N / parts columns of every valid row (a column slice spreads the work evenly over the
+  // cluster however few of the 128 rows exist)
+  const int slice_units = kUnits / parts;
+  const int rows_valid = min(kBlockM, pr.m - tm * kBlockM);
+  // alpha, beta, the cast and the store of the four sums of unit `u` of local row `lrow`
+  auto put_unit = [&](int lrow, int u, float (&v)[4]) {
+    const int row = tm * kBlockM + lrow, col = tn * BLOCK_N + u * 4;
+    OutT* orow = reinterpret_cast<OutT*>(pr.out) + static_cast<size_t>(row) * pr.ldo + col;
+    const OutT* crow = reinterpret_cast<const OutT*>(pr.cin) + static_cast<size_t>(row) * pr.ldcin + col;
+    const int valid = min(4, pr.n - col);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] *= p.alpha;
+      if (p.beta != 0.f && j < valid) v[j] += p.beta * to_f32(crow[j]);
+    }
+    if (pr.vec_ok && valid == 4) {
+      if constexpr (sizeof(OutT) == 4) {
+        *reinterpret_cast<float4*>(orow) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+        *reinterpret_cast<uint2*>(orow) = make_uint2(pack2(from_f32<OutT>(v[0]), from_f32<OutT>(v[1])),
+                                                     pack2(from_f32<OutT>(v[2]), from_f32<OutT>(v[3])));
+      }
+    } else {
+      for (int j = 0; j < valid; ++j) orow[j] = from_f32<OutT>(v[j]);
+    }
+  };
+
+  if (p.cluster_push) {
+    const int unit_shift = __ffs(slice_units) - 1;  // slice_units is a power of two
+    const uint32_t unit_pitch = static_cast<uint32_t>(p.cluster_rows) << 4;
+    const uint32_t region = static_cast<uint32_t>(slice_units) * unit_pitch;  // what one sender leaves here
+    const uint32_t bar_addr = smem_u32(recv_bar);
+    // pairs with the arrival at the end of set-up, long ago: every CTA of the cluster has initialised its barrier
+    cluster_wait_acquire();
+    tc_fence_after();
+    {
+      const int quadrant = warp & 3, half = warp >> 2;
+      const int lrow = quadrant * 32 + lane;
+      constexpr int kChunks = BLOCK_N / 64;  // 32-column chunks per column half
+      if (quadrant * 32 < rows_valid) {
+#pragma unroll 1
+        for (int cc = 0; cc < kChunks; ++cc) {
+          const int c = half * kChunks + cc;
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(c * 32), r);
+          tmem_ld_wait();
+          if (lrow < rows_valid) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int gu = c * 8 + q, dst = gu >> unit_shift, u = gu & (slice_units - 1);
+              const uint32_t local = recv + rank * region + static_cast<uint32_t>(u) * unit_pitch +
+                                     static_cast<uint32_t>((lrow ^ (u & 7)) << 4);
+              st_async_v4(mapa_shared(local, static_cast<uint32_t>(dst)), mapa_shared(bar_addr, static_cast<uint32_t>(dst)),
+                          r[q * 4 + 0], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[7] = clock64();  // timeline: sums sent
+    const bool landed = mbar_wait<true>(recv_bar, 0, wctl, 108);
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[8] = clock64();  // timeline: sums landed
+    if (store && landed) {
+#pragma unroll 2
+      for (int i = threadIdx.x; i < rows_valid * slice_units; i += kNumThreads) {
+        const int lrow = i >> unit_shift, u0 = i & (slice_units - 1);
+        const int u = static_cast<int>(rank) * slice_units + u0;
+        if (tn * BLOCK_N + u * 4 >= pr.n) continue;
+        const uint32_t off = recv + static_cast<uint32_t>(u0) * unit_pitch + static_cast<uint32_t>((lrow ^ (u0 & 7)) << 4);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < parts) {
+            const uint4 x = ld_shared_v4(off + static_cast<uint32_t>(q) * region);
+            v[0] += __uint_as_float(x.x); v[1] += __uint_as_float(x.y);
+            v[2] += __uint_as_float(x.z); v[3] += __uint_as_float(x.w);
+          }
+        put_unit(lrow, u, v);
+      }
+    }
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64();  // timeline: rows stored
+    return;
+  }
 
   tc_fence_after();
   {
@@ -501,21 +614,13 @@ __device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint3
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[8] = clock64();  // timeline: cluster barrier passed
 
   if (store) {
-    int tm, tn;
-    swizzled_tile(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-    const Problem& pr = p.prob;
-    // this CTA's share: BLOCK_N / parts columns of every valid row (a column slice spreads the work evenly
-    // over the cluster however few of the 128 rows exist)
-    const int slice_units = kUnits / parts;
-    const int rows_valid = min(kBlockM, pr.m - tm * kBlockM);
     uint32_t peer[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) peer[q] = mapa_shared(parked, static_cast<uint32_t>(q < parts ? q : 0));
 #pragma unroll 2
     for (int i = threadIdx.x; i < rows_valid * slice_units; i += kNumThreads) {
       const int lrow = i / slice_units, u = static_cast<int>(rank) * slice_units + i % slice_units;
-      const int row = tm * kBlockM + lrow, col = tn * BLOCK_N + u * 4;
-      if (col >= pr.n) continue;
+      if (tn * BLOCK_N + u * 4 >= pr.n) continue;
       const uint32_t off = static_cast<uint32_t>(lrow) * kPitch + static_cast<uint32_t>((u ^ (lrow & 7)) << 4);
       float4 x[8];
 #pragma unroll
@@ -525,24 +630,7 @@ __device__ __forceinline__ void cluster_finish_tile(const TcGemmParams& p, uint3
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         if (q < parts) { v[0] += x[q].x; v[1] += x[q].y; v[2] += x[q].z; v[3] += x[q].w; }
-      OutT* orow = reinterpret_cast<OutT*>(pr.out) + static_cast<size_t>(row) * pr.ldo + col;
-      const OutT* crow = reinterpret_cast<const OutT*>(pr.cin) + static_cast<size_t>(row) * pr.ldcin + col;
-      const int valid = min(4, pr.n - col);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[j] *= p.alpha;
-        if (p.beta != 0.f && j < valid) v[j] += p.beta * to_f32(crow[j]);
-      }
-      if (pr.vec_ok && valid == 4) {
-        if constexpr (sizeof(OutT) == 4) {
-          *reinterpret_cast<float4*>(orow) = make_float4(v[0], v[1], v[2], v[3]);
-        } else {
-          *reinterpret_cast<uint2*>(orow) = make_uint2(pack2(from_f32<OutT>(v[0]), from_f32<OutT>(v[1])),
-                                                       pack2(from_f32<OutT>(v[2]), from_f32<OutT>(v[3])));
-        }
-      } else {
-        for (int j = 0; j < valid; ++j) orow[j] = from_f32<OutT>(v[j]);
-      }
+      put_unit(lrow, u, v);
     }
   }
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[10] = clock64();  // timeline: rows stored
@@ -892,7 +980,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* ctl = smem;
   uint8_t* ring = smem + Cfg::kCtlBytes;
   uint8_t* epi_staging = ring + kStages * Cfg::kStageBytes;
-  const uint32_t a_slot_bytes = p.small_m ? kSmallMSlot * kSwizzleBytes : Cfg::kABytes;  // one k-slab of A in a stage
+  // one k-slab of A in a stage
+  const uint32_t a_slot_bytes = p.small_m ? kSmallMSlot * kSwizzleBytes
+                                          : (p.a_rows ? static_cast<uint32_t>(p.a_rows) * kSwizzleBytes : Cfg::kABytes);
   uint8_t* smem_a = ring;
   uint8_t* smem_b = ring + static_cast<uint32_t>(p.stages) * p.ks * a_slot_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctl);
@@ -901,6 +991,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  uint64_t* recv_bar = reinterpret_cast<uint64_t*>(tmem_holder + 2);  // cluster split-K, push form
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -925,6 +1016,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&tmem_full_bar[a], 1);
       mbar_init(&tmem_empty_bar[a], PAIR ? 8 : 4);  // epilogue warps of every CTA that reads this accumulator
     }
+    mbar_init(recv_bar, 1);  // (one arrival, by the first epilogue warp, which also says how many bytes to expect)
     fence_mbar_init();
     if (!grouped) {
       prefetch_tensormap(&tmA);
@@ -947,6 +1039,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     cluster_wait_acquire();
   } else {
     __syncthreads();
+    // (the barrier initialisations above were released to the cluster by fence_mbar_init; the wait is in
+    // cluster_finish_tile)
+    if (p.cluster_push) cluster_arrive_relaxed();
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
@@ -1036,7 +1131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int kb_begin = item.sb, kb_end = item.se;
         // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
         const uint32_t a_slab_bytes = p.small_m ? a_slot_bytes
-                                                : (swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : Cfg::kABytes);
+                                                : (swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : a_slot_bytes);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (by_hand) {
@@ -1262,6 +1357,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     long long prof_ewait = 0, prof_ebody = 0;
     uint32_t epi_seq = 0;  // steps this warp has passed through its staging blocks (TMA-store epilogue)
+    if (!PAIR && p.cluster_push && threadIdx.x == kEpiWarp0 * 32) {
+      // cluster split-K, push form: the fp32 sums of all CTAs of the cluster for this CTA's columns of the valid
+      // rows arrive in this CTA's receiving area; the arrival that lets the phase end comes with the byte count
+      int tm, tn;
+      swizzled_tile(static_cast<int>(blockIdx.x) / p.cluster_k, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>(min(kBlockM, p.prob.m - tm * kBlockM)) * BLOCK_N * 4u);
+    }
     for (int idx = 0; ok; ++idx) {
       WorkItem item;
       item.kind = ITEM_FULL;
@@ -1637,8 +1739,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     cluster_wait_acquire();
   } else {
     if (p.cluster_k > 1)
-      cluster_finish_tile<OutT, BLOCK_N>(p, smem_u32(ring), tmem_base, static_cast<int>(blockIdx.x) / p.cluster_k,
-                                         !*abort_flag);
+      cluster_finish_tile<OutT, BLOCK_N>(p, smem_u32(ring),
+                                         smem_u32(epi_staging) + Cfg::kEpiBytes - static_cast<uint32_t>(p.cluster_rows) * BLOCK_N * 4u,
+                                         recv_bar, wctl, tmem_base, static_cast<int>(blockIdx.x) / p.cluster_k, !*abort_flag);
   }
   if (warp == 2) {
     tc_fence_after();

@@ -453,11 +453,30 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   pp.debug = 0;
 #endif
   int max_stages = Cfg::kStages / static_cast<int>(p.ks);  // a stage holds ks slabs
+  if (p.a_rows) {
+    // short A slots: more stages fit the ring
+    max_stages = Cfg::kStages * Cfg::kStageBytes / (static_cast<int>(p.ks) * (p.a_rows * kSwizzleBytes + Cfg::kBBytes));
+    if (max_stages > kMaxRing) max_stages = kMaxRing;
+  }
   if (p.small_m) {
     // small-M plan: 32-row A slots, and the ring runs on into the (unused) epilogue staging blocks
     max_stages = (Cfg::kStages * Cfg::kStageBytes + Cfg::kEpiBytes) /
                  (static_cast<int>(p.ks) * (kSmallMSlot * kSwizzleBytes + Cfg::kBBytes));
     if (max_stages > kMaxRing) max_stages = kMaxRing;
+  }
+  if (pp.cluster_k > 1 && pp.cluster_push) {
+    // The receiving area of the push form takes the epilogue staging blocks, which a cluster split-K call does not
+    // use, and, where it is larger, the end of the operand ring; with fewer than two stages left the CTAs read
+    // each other's parked sums instead.
+    pp.cluster_rows = p.prob.m >= kBlockM ? kBlockM : (p.prob.m + 31) / 32 * 32;
+    const int recv = BLOCK_N * pp.cluster_rows * 4;
+    if (recv > Cfg::kEpiBytes) {
+      const int left = (Cfg::kStages * Cfg::kStageBytes - (recv - Cfg::kEpiBytes)) / (static_cast<int>(p.ks) * Cfg::kStageBytes);
+      // (measured: 128 x 4096 x 14336 with two stages of three left, 31.4 -> 37.5 us: the shorter ring costs the k
+      // loop more than the push saves; FLAGBLAS_B200_CLUSTER_PUSH=2 takes the ring's end regardless)
+      if (left >= 2 && pp.cluster_push == 2) max_stages = left < max_stages ? left : max_stages;
+      else pp.cluster_push = 0;
+    }
   }
   pp.stages = env_int("FLAGBLAS_B200_STAGES", max_stages);
   if (pp.stages < 1 || pp.stages > max_stages) pp.stages = max_stages;
@@ -735,6 +754,7 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
   if (force_bn == 0 && force_pair != 1 && stages >= min_stages && !gpu_is_full && (force_split != 0 || force_cluster != 0)) {
     const int cand[3] = {256, 128, 64};
     const double eff[3] = {1.0, 0.6, 0.35};
+    const int push_cost = env_int("FLAGBLAS_B200_CLUSTER_PUSH", 1) != 0 ? env_int("FLAGBLAS_B200_PLAN_PUSH_COST", 1) : 0;
     double best = 1e300;
     int best_bn = 0, best_sp = 1, best_ck = 1;
     for (int i = 0; i < 3; ++i) {
@@ -754,7 +774,13 @@ static DensePlan plan_dense(long long m, long long n, long long k, int esz, int 
           // measured: two cluster barriers and parking the sums ~0.8 us more than a plain epilogue, and the
           // reads over distributed shared memory run at ~16 bytes per clock per SM
           const double rows = static_cast<double>(m < kBlockM ? m : kBlockM);
-          if (sp > 1) cost += in_cluster ? 350.0 + 0.054 * rows * cand[i] : 2300.0 + 2.1e-4 * static_cast<double>(m) * n * sp * 4.0;
+          // (sent instead of read where the receiving area fits the idle epilogue staging blocks, see launch_tc:
+          // 64 x 4096 x 4096, 3.8 k cycles from the last MMA to the exit against 6.7 k)
+          // (only up to 32 rows: charging less for 33 to 128 rows moved 96 .. 128 x 28672 x 8192 to 64-wide tiles,
+          // 91 -> 98 us)
+          const bool pushed = m <= 32 && 32 * cand[i] * 4 <= 8 * kEpiStageBytes && push_cost != 0;
+          const double in_cluster_cost = pushed ? 200.0 + 0.03 * rows * cand[i] : 350.0 + 0.054 * rows * cand[i];
+          if (sp > 1) cost += in_cluster ? in_cluster_cost : 2300.0 + 2.1e-4 * static_cast<double>(m) * n * sp * 4.0;
           if (cost < best) { best = cost; best_bn = cand[i]; best_sp = in_cluster ? 1 : sp; best_ck = in_cluster ? sp : 1; }
         }
       }
@@ -1284,13 +1310,18 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   CUtensorMap ma, mb;
   const bool atom32 = esz == 4;  // MN-major fp32 operands use the 32-byte-atom swizzle
   const uint64_t kslabs = (static_cast<uint64_t>(k) + span - 1) / span;
+  // A single row block of few rows of a k-contiguous A: copies of only those rows, rounded up to the 8 rows of a
+  // swizzle pattern, and slots to match (TcGemmParams::a_rows).  The TMA unit is what bounds the k loop of such
+  // calls (~250 cycles + bytes / 120 per copy), and half or more of a 128-row box would be zeros.
+  const int a_rows = (!pair && !a_mn && m < kBlockM - 8 && env_int("FLAGBLAS_B200_A_ROWS", 1) != 0)
+                         ? static_cast<int>((m + 7) / 8 * 8) : kBlockM;
   auto encode_maps = [&](bool a3, bool b3, int nks) -> int {
     int rc;
     if (a3) {
       if (a_mn) rc = encode_3d(&ma, dtype, A, span, k, m / span, lda * esz, kSwizzleBytes, span, span * nks, kBlockM / span, atom32);
-      else rc = encode_3d(&ma, dtype, A, span, m, kslabs, lda * esz, kSwizzleBytes, span, kBlockM, nks, false);
+      else rc = encode_3d(&ma, dtype, A, span, m, kslabs, lda * esz, kSwizzleBytes, span, a_rows, nks, false);
     } else if (a_mn) rc = encode_2d(&ma, dtype, A, m, k, lda * esz, span, span, atom32);
-    else rc = encode_2d(&ma, dtype, A, k, m, lda * esz, span, kBlockM);
+    else rc = encode_2d(&ma, dtype, A, k, m, lda * esz, span, a_rows);
     if (rc) return rc;
     if (b3) {
       if (b_mn) rc = encode_3d(&mb, dtype, B, span, k, n / span, ldb * esz, kSwizzleBytes, span, span * nks, b_rows / span, atom32);
@@ -1325,7 +1356,8 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
   p.idesc = make_idesc(idesc_fmt(dtype), a_mn, b_mn, tile_m, block_n > 256 ? 256 : block_n);
   p.block_k = span * ks;
   p.ks = ks;
-  p.a = make_geom(esz, kBlockM, a_mn, ks, use_a3d);
+  p.a = make_geom(esz, a_rows, a_mn, ks, use_a3d);
+  p.a_rows = a_rows < kBlockM ? a_rows : 0;
   p.b = make_geom(esz, b_rows, b_mn, ks, use_b3d);
   p.num_groups = 0;
   p.wide_merged = wide_merged ? 1 : 0;
@@ -1356,6 +1388,7 @@ int fb_gemm(int dtype, int transa, int transb, int64_t m, int64_t n, int64_t k, 
     while (ck > 1 && k_stages < ck) ck /= 2;
     if (ck > 1) {
       p.cluster_k = ck;
+      p.cluster_push = env_int("FLAGBLAS_B200_CLUSTER_PUSH", 1);
       tiles *= ck;
     }
   }

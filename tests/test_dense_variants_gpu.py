@@ -210,12 +210,16 @@ def test_single_wave_of_wide_tiles(kind, ta, tb, m, n, k, monkeypatch):
     ("tf32", 1, 1, 300, 520, 8192, 0.5),     # CTA-pair tiles, ragged
     ("bf16", 0, 1, 1024, 1024, 1024, 0.5),   # small square problem: 128-row tiles in clusters instead of CTA pairs
     ("bf16", 1, 0, 100, 264, 1024, 0.0),     # k barely long enough, ragged rows and columns
+    ("tf32", 0, 1, 40, 520, 2048, 0.5),      # TF32 with k-contiguous A: five 8-row groups per A slot
+    ("fp16", 0, 0, 7, 300, 512, 0.0),        # fewer rows than one 8-row group
+    ("bf16", 0, 1, 119, 256, 4096, 0.5),     # the most rows that still shorten the A slots (120)
 ])
 def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
     """Shapes with few output tiles and a long k are cut along k.  The parts are added either by the CTAs of a
-    cluster over distributed shared memory (2, 4 or 8 parts) or by a second kernel from fp32 scratch.  Same
-    tolerance as every dense test; whole-k tiles, every forced cluster size and a forced part count of the
-    scratch method must agree with the automatic plan."""
+    cluster over distributed shared memory (2, 4 or 8 parts; sent to the finishing CTA or read by it) or by a second
+    kernel from fp32 scratch, and A's stage slots hold only as many rows as exist.  Same tolerance as every dense
+    test; whole-k tiles, every forced cluster size in both forms, a forced part count of the scratch method and
+    128-row A slots must agree with the automatic plan."""
     A, lda, B, ldb, C, ldc = make_dense(kind, ta, tb, m, n, k, seed=41, scale=0.25)
     Ad, Bd = A.to(DEV), B.to(DEV)
     op = getattr(fb, KINDS[kind][1])
@@ -226,25 +230,36 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
         opA, opB = trunc(opA), trunc(opB)
     ref = (1.5 * (opA @ opB) + beta * C.to(DEV).double()).float().cpu()
     sc = result_scale(k, A, B, 1.5) + abs(beta)
-    # (FLAGBLAS_B200_SPLITK, FLAGBLAS_B200_CLUSTER_K, FLAGBLAS_B200_PAIR); None = unset
-    modes = {"auto": (None, None, None), "whole-k": ("0", "0", None), "scratch-3": ("3", "0", None),
-             "scratch-auto": (None, "0", None), "cluster-2": ("0", "2", "0"), "cluster-4": ("0", "4", "0"),
-             "cluster-8": ("0", "8", "0")}
+    # switches of each mode (the others unset).  FLAGBLAS_B200_CLUSTER_PUSH=0: the finishing CTA reads its peers'
+    # shared memory instead of being sent the sums; FLAGBLAS_B200_A_ROWS=0: 128-row A slots however few rows exist
+    names = ("FLAGBLAS_B200_SPLITK", "FLAGBLAS_B200_CLUSTER_K", "FLAGBLAS_B200_PAIR", "FLAGBLAS_B200_CLUSTER_PUSH",
+             "FLAGBLAS_B200_A_ROWS")
+    cluster = lambda parts, **more: dict(FLAGBLAS_B200_SPLITK="0", FLAGBLAS_B200_CLUSTER_K=str(parts),  # noqa: E731
+                                         FLAGBLAS_B200_PAIR="0", **more)
+    modes = {"auto": {}, "whole-k": dict(FLAGBLAS_B200_SPLITK="0", FLAGBLAS_B200_CLUSTER_K="0"),
+             "scratch-3": dict(FLAGBLAS_B200_SPLITK="3", FLAGBLAS_B200_CLUSTER_K="0"),
+             "scratch-auto": dict(FLAGBLAS_B200_CLUSTER_K="0"),
+             "cluster-2": cluster(2), "cluster-4": cluster(4), "cluster-8": cluster(8),
+             "cluster-2-read": cluster(2, FLAGBLAS_B200_CLUSTER_PUSH="0"),
+             "cluster-4-read": cluster(4, FLAGBLAS_B200_CLUSTER_PUSH="0", FLAGBLAS_B200_A_ROWS="0"),
+             "cluster-8-read": cluster(8, FLAGBLAS_B200_CLUSTER_PUSH="0"),
+             "auto-whole-a-slots": dict(FLAGBLAS_B200_A_ROWS="0"),
+             "cluster-4-whole-a-slots": cluster(4, FLAGBLAS_B200_A_ROWS="0")}
     for mode, envs in modes.items():
-        for name, val in zip(("FLAGBLAS_B200_SPLITK", "FLAGBLAS_B200_CLUSTER_K", "FLAGBLAS_B200_PAIR"), envs):
-            if val is None:
-                monkeypatch.delenv(name, raising=False)
+        for name in names:
+            if name in envs:
+                monkeypatch.setenv(name, envs[name])
             else:
-                monkeypatch.setenv(name, val)
+                monkeypatch.delenv(name, raising=False)
         fb.reload_env()
         Cd = C.to(DEV) if beta != 0 else torch.full_like(C, float("nan")).to(DEV)
         op(ta, tb, m, n, k, 1.5, Ad, lda, Bd, ldb, beta, Cd, ldc)
         torch.cuda.synchronize()
         assert fb.device_status() == 0
         assert_parity(Cd.float().cpu(), ref, KINDS[kind][2], sc, "split-k %s %s %dx%dx%d" % (mode, kind, m, n, k))
+    for name in names:
+        monkeypatch.delenv(name, raising=False)
     monkeypatch.setenv("FLAGBLAS_B200_CLUSTER_K", "0")
-    monkeypatch.delenv("FLAGBLAS_B200_SPLITK", raising=False)
-    monkeypatch.delenv("FLAGBLAS_B200_PAIR", raising=False)
     fb.reload_env()
     need = fb.c_operators.gemm_workspace_bytes(fb._lib.FB_BF16, 0, 1, 16, 4096, 4096, 256, 4096, 512, 4096)
     assert need >= 2 * 16 * 4096 * 4          # without clusters the first shape's plan asks for scratch for >= 2 parts
