@@ -225,13 +225,31 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 // Grouped-M raster: walk `group_m` row-tiles down before stepping one column-tile right.
 __device__ __forceinline__ void swizzled_tile(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  if (tiles_m == 1) {  // one row of tiles: the same answer without the divisions (these sit before a call's first copy)
+    tm = 0;
+    tn = t;
+    return;
+  }
+  // (integer divisions cost well over a hundred cycles each here; a whole group of a power-of-two height, the
+  // usual case, needs only the first)
   const int width = group_m * tiles_n;
-  const int gid = t / width;
+  const int gid = t < width ? 0 : t / width;
   const int first_m = gid * group_m;
   const int gsz = min(tiles_m - first_m, group_m);
   const int r = t - gid * width;
-  tm = first_m + r % gsz;
-  tn = r / gsz;
+  if (gsz == group_m && (group_m & (group_m - 1)) == 0) {
+    tm = first_m + (r & (group_m - 1));
+    tn = r >> (31 - __clz(group_m));
+  } else {
+    tm = first_m + r % gsz;
+    tn = r / gsz;
+  }
+}
+
+// x / d and x % d for d = 2, 3 or 4 (the sharers of a stream-K tail tile) without a division instruction.
+__device__ __forceinline__ void div_small(int x, int d, int& quot, int& rem) {
+  quot = d == 2 ? x >> 1 : (d == 4 ? x >> 2 : (d == 3 ? x / 3 : x / d));
+  rem = x - quot * d;
 }
 
 // Epilogue for 32 consecutive columns of one row held in `acc` (fp32 bits).
@@ -660,9 +678,10 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
   if (p.cluster_k > 1) {
     // the grid is exactly tiles x cluster_k CTAs: one work item each, the cluster rank picks the k part
     if (idx > 0) return false;
-    it.tile = worker / p.cluster_k;
-    it.part = worker % p.cluster_k;
-    const int base = stages / p.cluster_k, rem = stages % p.cluster_k;
+    const int shift = 31 - __clz(p.cluster_k), mask = p.cluster_k - 1;  // (2, 4 or 8 parts)
+    it.tile = worker >> shift;
+    it.part = worker & mask;
+    const int base = stages >> shift, rem = stages & mask;
     it.sb = it.part * base + min(it.part, rem);
     it.se = it.sb + base + (it.part < rem ? 1 : 0);
     it.kind = ITEM_CLUSTER;
@@ -760,7 +779,8 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
   }
   if (idx > p.sk_dp) return false;
   // the tail: tile `tl` is shared by workers tl * sk_group .. + sk_group - 1
-  const int tl = worker / p.sk_group, j = worker % p.sk_group;
+  int tl, j;
+  div_small(worker, p.sk_group, tl, j);
   if (tl >= p.sk_rem) return false;  // more workers than tail parts: this one is done
   it.tile = p.sk_dp * workers + tl;
   if (p.sk_group == 2) {
@@ -779,7 +799,8 @@ __device__ __forceinline__ bool dense_work_item(const TcGemmParams& p, int worke
   }
   // Three or four sharers: equal parts of the k range, and every sharer finishes a part of the tile's columns
   // (1024 x 1536 x 4096, three sharers: 24.3 - 25.5 us against 25.8 - 26.9 with one owner adding two parked parts).
-  const int base = stages / p.sk_group, extra = stages % p.sk_group;
+  int base, extra;
+  div_small(stages, p.sk_group, base, extra);
   it.sb = j * base + min(j, extra);
   it.se = it.sb + base + (j < extra ? 1 : 0);
   it.kind = ITEM_SHARED;
@@ -1053,7 +1074,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // kernel, the caller's previous kernel): all of the above overlapped with its tail; global memory only from here.
   grid_dependency_wait();
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
-  const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);  // k-stages per dense tile
+  // k-stages per dense tile (block_k is a power of two: 128 bytes of k times one or two slabs)
+  const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) >> (31 - __clz(static_cast<int>(p.block_k)));
 
   if (warp == 0 || warp == 3) {
     // ----------------------------------------------------------- producers
@@ -1126,7 +1148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // first row (A) / first column (B) of the operand slab this CTA fetches
         const int mn0 = load_a ? row_base + tm * tile_rows + static_cast<int>(cta_rank) * (swap_half ? swap_half : kBlockM)
                                : tn * BLOCK_N + static_cast<int>(cta_rank) * (p.wide_merged ? Cfg::kBRows : Cfg::kBRows / Cfg::kHalves);
-        const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+        const int k_blocks = (kk_total + static_cast<int>(p.block_k) - 1) >> (31 - __clz(static_cast<int>(p.block_k)));
         if (grouped && !grouped_range(p, k_blocks, role, sharers, item)) break;
         const int kb_begin = item.sb, kb_end = item.se;
         // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
@@ -1254,7 +1276,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (grouped) {
           while (g + 1 < p.num_groups && t >= __ldg(p.group_starts + g + 1)) ++g;
           const GroupRec& gr = p.groups[g];
-          const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+          const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) >> (31 - __clz(static_cast<int>(p.block_k)));
           if (PAIR && p.small_m) {
             const int tm = (t - gr.tile_start) / gr.tiles_n;
             swap_half = ((min(kSmallMRows, gr.m - tm * kSmallMRows) + 15) >> 4) << 3;
@@ -1391,7 +1413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         pr.vec_ok = gr.vec_ok;
         k_is_zero = gr.k == 0;
         row_base = gr.row_base;
-        const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) / static_cast<int>(p.block_k);
+        const int stages_g = (gr.k + static_cast<int>(p.block_k) - 1) >> (31 - __clz(static_cast<int>(p.block_k)));
         if (PAIR && p.small_m) {
           swap_rows = ((min(kSmallMRows, gr.m - tm * kSmallMRows) + 15) >> 4) << 4;
           tile_rows = kSmallMRows;

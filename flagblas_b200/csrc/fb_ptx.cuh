@@ -31,6 +31,7 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_TEST_FLAG = 105,       // self-test: a wait on a flag nothing sets
   DEV_TIMEOUT_PEER = 106,            // 2-CTA pair handshake
   DEV_TIMEOUT_STREAMK_PARTIAL = 107, // stream-K owner waiting for another worker's partial sums
+  DEV_TIMEOUT_CLUSTER_SUMS = 108,    // cluster split-K: a CTA waiting for the sums its cluster peers send it
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -1890,6 +1890,8 @@ const char* fb_status_string(int status) {
     case DEV_TIMEOUT_EPI_TMEM_FULL: return "device: epilogue timed out waiting for an accumulator";
     case DEV_TIMEOUT_TEST_FLAG: return "device: self-test wait timed out (expected)";
     case DEV_TIMEOUT_PEER: return "device: CTA-pair handshake timed out";
+    case DEV_TIMEOUT_STREAMK_PARTIAL: return "device: timed out waiting for another worker's partial sums of a shared tile";
+    case DEV_TIMEOUT_CLUSTER_SUMS: return "device: timed out waiting for the sums of the other CTAs of a split-k cluster";
     case DEV_GROUP_MISALIGNED: return "device: a group's A / B address or pitch is not a multiple of the element size; group skipped";
     default: return "unknown status";
   }
