@@ -158,6 +158,16 @@ def _time(fn, torch, steps=10, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    # calls of a few microseconds: ten of them end before the clocks have left their idle state and before the
+    # launch queue holds more than one call, so such workloads run until about 2 ms have been timed (at most 400 calls)
+    t0 = time.perf_counter()
+    fn()
+    torch.cuda.synchronize()
+    once = time.perf_counter() - t0
+    steps = max(steps, min(400, int(2e-3 / max(once, 1e-6))))
+    for _ in range(min(steps, 50)):
+        fn()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
