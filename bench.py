@@ -236,9 +236,13 @@ def other_configs(fb, torch, dev):
             # back to back its 32 MiB of weights stay in the 126 MB L2: the HBM roofline applies to launches that
             # find L2 cold, timed one by one with L2 rewritten in between
             cold = _time_cold(lambda: fn(ta, tb, m, n, k, alpha, A, A.shape[1], B, B.shape[1], beta, C, n), torch, dev)
+            # context: cuBLAS (torch.matmul) on the same operands, timed the same two ways
+            opB = B.t() if tb else B
+            cublas_ms = _time(lambda: torch.matmul(A, opB, out=C), torch)
+            cublas_cold = _time_cold(lambda: torch.matmul(A, opB, out=C), torch, dev)
             rec.update(bound="latency (operands L2-resident between back-to-back launches)", ms_l2_cold=cold,
                        gbs_l2_cold=nbytes / (cold * 1e-3) / 1e9, frac=nbytes / (cold * 1e-3) / 1e9 / hbm, peak=hbm,
-                       frac_is="HBM roofline of the L2-cold launches")
+                       frac_is="HBM roofline of the L2-cold launches", cublas_ms=cublas_ms, cublas_ms_l2_cold=cublas_cold)
         elif kind == "tf32":
             # no measured TF32 figure exists: the denominator is assumed, half the measured 16-bit rate; cuBLAS's
             # TF32 GEMM on the same operands is timed beside it as context
