@@ -243,6 +243,8 @@ def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
              "cluster-2-read": cluster(2, FLAGBLAS_B200_CLUSTER_PUSH="0"),
              "cluster-4-read": cluster(4, FLAGBLAS_B200_CLUSTER_PUSH="0", FLAGBLAS_B200_A_ROWS="0"),
              "cluster-8-read": cluster(8, FLAGBLAS_B200_CLUSTER_PUSH="0"),
+             "cluster-2-sent-into-ring": cluster(2, FLAGBLAS_B200_CLUSTER_PUSH="2"),   # receiving area: the ring's end
+             "cluster-4-sent-into-ring": cluster(4, FLAGBLAS_B200_CLUSTER_PUSH="2", FLAGBLAS_B200_A_ROWS="0"),
              "auto-whole-a-slots": dict(FLAGBLAS_B200_A_ROWS="0"),
              "cluster-4-whole-a-slots": cluster(4, FLAGBLAS_B200_A_ROWS="0")}
     for mode, envs in modes.items():
