@@ -18,14 +18,27 @@ N_CHOICES = [8, 64, 120, 256, 264, 512, 1000, 1536, 2048, 4096, 5000]
 K_CHOICES = [64, 128, 192, 520, 1024, 2048, 4096, 6144, 8200, 16384]
 
 
-@pytest.mark.parametrize("chunk", range(6))
+# one row block of few rows: A's stage slots shrink to the rows that exist, long k is cut over the CTAs of a cluster,
+# which send each other their sums or read them depending on the tile's size
+SKINNY_M = [2, 3, 7, 8, 9, 16, 24, 31, 33, 40, 63, 64, 65, 96, 100, 112, 119, 120, 121, 127, 128]
+SKINNY_N = [64, 120, 256, 264, 512, 1000, 1536, 2048, 4096, 5000, 6144, 8192]
+SKINNY_K = [128, 520, 1024, 2048, 4096, 6144, 8200, 16384]
+
+
+@pytest.mark.parametrize("chunk", list(range(6)) + ["skinny-0", "skinny-1", "skinny-2"])
 def test_random_shapes_match_fp64_product(chunk):
+    skinny = isinstance(chunk, str)
+    if skinny:
+        chunk = 10 + int(chunk[-1])
     rnd = random.Random(1000 + chunk)
     for case in range(25):
         kind = rnd.choice(["bf16", "fp16", "tf32"])
         dt, opname, rtol = KINDS[kind][0], KINDS[kind][1], KINDS[kind][2]
         ta, tb = rnd.randint(0, 1), rnd.randint(0, 1)
-        m, n, k = rnd.choice(M_CHOICES), rnd.choice(N_CHOICES), rnd.choice(K_CHOICES)
+        if skinny:
+            m, n, k = rnd.choice(SKINNY_M), rnd.choice(SKINNY_N), rnd.choice(SKINNY_K)
+        else:
+            m, n, k = rnd.choice(M_CHOICES), rnd.choice(N_CHOICES), rnd.choice(K_CHOICES)
         if kind == "tf32":
             k = max(32, k // 2)
         per16 = 16 // (4 if kind == "tf32" else 2)
