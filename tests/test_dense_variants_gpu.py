@@ -213,6 +213,8 @@ def test_single_wave_of_wide_tiles(kind, ta, tb, m, n, k, monkeypatch):
     ("tf32", 0, 1, 40, 520, 2048, 0.5),      # TF32 with k-contiguous A: five 8-row groups per A slot
     ("fp16", 0, 0, 7, 300, 512, 0.0),        # fewer rows than one 8-row group
     ("bf16", 0, 1, 119, 256, 4096, 0.5),     # the most rows that still shorten the A slots (120)
+    ("bf16", 0, 1, 64, 6144, 2048, 0.0),     # 64 rows of 256-wide tiles: too large a tile to be sent, short A slots
+    ("fp16", 0, 1, 96, 4096, 4096, 0.5),     # the same with 96 rows of 128-wide tiles
 ])
 def test_split_k_for_skinny_shapes(kind, ta, tb, m, n, k, beta, monkeypatch):
     """Shapes with few output tiles and a long k are cut along k.  The parts are added either by the CTAs of a
