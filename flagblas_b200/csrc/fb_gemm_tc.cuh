@@ -1068,11 +1068,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_holder;
   if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) p.prof[4] = clock64();  // timeline: set-up done
 
-  // Grouped calls are launched as programmatic dependents of the table builder: everything above ran
-  // while it was still working; its table and tensor maps may be read only from here on.
   // Every launch is a programmatic dependent of whatever precedes it on the stream (the table builder, a packing
-  // kernel, the caller's previous kernel): all of the above overlapped with its tail; global memory only from here.
-  grid_dependency_wait();
+  // kernel, the caller's previous kernel): all of the above overlapped with its tail, and global memory may be
+  // touched only after the wait.  A grouped call reads the builder's table right away.  A dense call puts the wait
+  // off: its producer threads work out their first tile first and wait just before the first copy, its epilogue
+  // warps wait before they wait for an accumulator, and the other warps touch no global memory (the whole-CTA
+  // finish of a cluster split-K call comes after all of these).
+  if (grouped) grid_dependency_wait();
   const int num_tiles = grouped ? *p.total_tiles : p.tiles_m * p.tiles_n;
   // k-stages per dense tile (block_k is a power of two: 128 bytes of k times one or two slabs)
   const int dense_stages = (p.k + static_cast<int>(p.block_k) - 1) >> (31 - __clz(static_cast<int>(p.block_k)));
@@ -1154,6 +1156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // bytes of A per k-slab that this CTA puts into the stage (fewer rows in a transposed partial block)
         const uint32_t a_slab_bytes = p.small_m ? a_slot_bytes
                                                 : (swap_half ? static_cast<uint32_t>(swap_half) * kSwizzleBytes : a_slot_bytes);
+        if (!grouped && idx == 0) grid_dependency_wait();
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           const long long c0 = p.prof ? clock64() : 0;
           if (by_hand) {
@@ -1379,6 +1382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     long long prof_ewait = 0, prof_ebody = 0;
     uint32_t epi_seq = 0;  // steps this warp has passed through its staging blocks (TMA-store epilogue)
+    if (!grouped) grid_dependency_wait();
     if (!PAIR && p.cluster_push && threadIdx.x == kEpiWarp0 * 32) {
       // cluster split-K, push form: the fp32 sums of all CTAs of the cluster for this CTA's columns of the valid
       // rows arrive in this CTA's receiving area; the arrival that lets the phase end comes with the byte count
