@@ -264,9 +264,9 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
   float* Bs = pipe_smem + kPipeStages * kAFloats;
 
   // launched as a programmatic dependent of whatever precedes it on the stream: its own dependents may be scheduled
-  // from here on, and nothing is read or written before the predecessor has completed
+  // from here on, and nothing is read or written before the predecessor has completed (the wait comes after the tile
+  // arithmetic, just before the first load: its divisions overlap the predecessor's tail)
   grid_launch_dependents();
-  grid_dependency_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int parts = (p.ksplit == 2 || p.ksplit == 4) ? p.ksplit : 1;  // CTAs of one cluster that share the tile's k range
@@ -291,6 +291,7 @@ __global__ void __launch_bounds__(256, 2) sgemm_pipe_kernel(const SimtParams p) 
   };
 
   const int k_iters = k_end > k_begin ? (k_end - k_begin + kPipeK - 1) / kPipeK : 0;
+  grid_dependency_wait();
 #pragma unroll
   for (int s = 0; s < kPipeStages - 1; ++s) {
     if (s < k_iters) {
